@@ -1,0 +1,67 @@
+// Shared helpers of the hand-written sm_100a kernels: element types, loads/stores that widen
+// to float, block reductions, and the launch-status convention of the exported C entry points.
+//
+// Every exported function is `extern "C"`, takes raw device pointers plus sizes and the CUDA
+// stream as a `void*`, launches asynchronously on that stream and returns 0 on success or a
+// negative code for a refused argument / a positive `cudaError_t` for a failed launch.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define PKV_EXPORT extern "C" __attribute__((visibility("default")))
+
+// element type codes used across the C interface
+#define PKV_F32 0
+#define PKV_BF16 1
+
+// refusal codes (negative so that they never collide with cudaError_t values)
+#define PKV_ERR_DTYPE (-2)
+#define PKV_ERR_SIZE (-3)
+#define PKV_ERR_ALIGN (-4)
+#define PKV_ERR_LIMIT (-5)
+
+namespace pkv {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a thread block (any multiple of 32 threads up to 1024). `scratch` holds 32 floats.
+// The order of additions depends only on the block size, never on the data or the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float total = (lane < nwarps) ? scratch[lane] : 0.0f;
+  total = warp_sum(total);
+  return total;
+}
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+}  // namespace pkv

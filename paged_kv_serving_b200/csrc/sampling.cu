@@ -1,0 +1,224 @@
+// Token sampling on the device: greedy, temperature and nucleus (top-p), one block per row.
+//
+// The procedure restates the reference (rouviere-german/paged-kv-serving,
+// src/paged_kv_serving/engine/sampling.py:28-74):
+//   greedy        argmax, the lowest id on ties (rows whose temperature is below the threshold)
+//   temperature   scaled = logits / T in float32; p = exp(double(scaled - max)) / sum -> float32
+//   nucleus       tokens in descending probability (lower id first among equals) are kept up to
+//                 and including the one whose cumulative mass (float64) reaches top_p; the rest
+//                 are zeroed and the kept ones renormalised
+//   draw          cum = cumulative sum in float64 in id order; draw = u * cum[-1]; the token is
+//                 the first id whose cumulative mass exceeds the draw
+// The uniform number u comes from the request's own generator on the host
+// (src/paged_kv_serving/engine/sequence.py:165-170), one per sampled token, so a request's
+// output does not depend on the batch it was sampled in.
+//
+// `probs` is scratch memory of n_rows * vocab floats: the kernel writes the (filtered)
+// probabilities there and reads them back in later passes.
+#include "common.cuh"
+
+namespace pkv {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+struct ArgMax {
+  float v;
+  int i;
+};
+
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ double block_sum_d(double v, double* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum_d(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  double t = lane < (SAMPLE_THREADS >> 5) ? scratch[lane] : 0.0;
+  t = warp_sum_d(t);
+  return t;  // the same value in every thread
+}
+
+// exclusive prefix sum over the block in thread order; returns the exclusive prefix of this
+// thread and stores the block total in *total.
+__device__ double block_scan_d(double v, double* scratch, double* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  double inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    double w = scratch[lane];
+    double winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double n = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += n;
+    }
+    scratch[lane] = winc - w;       // exclusive prefix of each warp
+    if (lane == 31) scratch[32] = winc;
+  }
+  __syncthreads();
+  *total = scratch[32];
+  return scratch[warp] + (inc - v);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, long long row_stride, const float* __restrict__ temperature,
+              const float* __restrict__ top_p, const double* __restrict__ uniform, float* __restrict__ probs,
+              int32_t* __restrict__ out, int vocab, float greedy_below) {
+  __shared__ double scratch_d[33];
+  __shared__ ArgMax scratch_a[32];
+  __shared__ float shared_f;
+  __shared__ int shared_i;
+  const int r = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = logits + (size_t)r * row_stride;
+  const float temp = temperature[r];
+
+  // ---- maximum (and its lowest index) of the row ----
+  ArgMax best = {-INFINITY, 0x7fffffff};
+  for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+    const float v = row[i];
+    if (v > best.v) best = {v, i};
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (lane == 0) scratch_a[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    best = scratch_a[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgMax other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = better(best, other);
+    }
+    if (lane == 0) {
+      shared_f = best.v;
+      shared_i = best.i == 0x7fffffff ? 0 : best.i;
+    }
+  }
+  __syncthreads();
+  if (temp < greedy_below) {
+    if (tid == 0) out[r] = shared_i;
+    return;
+  }
+
+  // ---- probabilities: float32 scaling, float64 exponentials ----
+  const float scaled_max = shared_f / temp;  // division is monotone: the scaled maximum
+  float* p = probs + (size_t)r * vocab;
+  double part = 0.0;
+  for (int i = tid; i < vocab; i += SAMPLE_THREADS) part += exp((double)(row[i] / temp - scaled_max));
+  const double denom = block_sum_d(part, scratch_d);
+  for (int i = tid; i < vocab; i += SAMPLE_THREADS)
+    p[i] = (float)(exp((double)(row[i] / temp - scaled_max)) / denom);
+  __syncthreads();
+
+  const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  const int c0 = min(tid * chunk, vocab), c1 = min(c0 + chunk, vocab);
+
+  // ---- nucleus filter ----
+  const float tp = top_p[r];
+  if (tp < 1.0f) {
+    const double target = (double)tp;
+    // largest probability value v with mass{p >= v} >= top_p, by bisection on the bit pattern
+    unsigned lo = 0u, hi = 0x7f800001u;
+    while (hi - lo > 1u) {
+      const unsigned mid = lo + ((hi - lo) >> 1);
+      const float thr = __uint_as_float(mid);
+      double mass = 0.0;
+      for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+        const float v = p[i];
+        if (v >= thr) mass += (double)v;
+      }
+      mass = block_sum_d(mass, scratch_d);
+      if (mass >= target) lo = mid; else hi = mid;
+    }
+    const float pstar = __uint_as_float(lo);
+    double above = 0.0;
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+      const float v = p[i];
+      if (v > pstar) above += (double)v;
+    }
+    above = block_sum_d(above, scratch_d);
+    // ties at pstar are kept in id order until the cumulative mass reaches top_p
+    long long need = 1;
+    if (pstar > 0.0f) {
+      need = (long long)ceil((target - above) / (double)pstar);
+      if (need < 1) need = 1;
+      while (need > 1 && above + (double)(need - 1) * (double)pstar >= target) --need;
+      while (above + (double)need * (double)pstar < target && need < vocab) ++need;
+    } else {
+      need = vocab;  // the whole mass is below top_p: everything is kept
+    }
+    double ties = 0.0;
+    for (int i = c0; i < c1; ++i) ties += (p[i] == pstar) ? 1.0 : 0.0;
+    double tie_total;
+    double rank = block_scan_d(ties, scratch_d, &tie_total);
+    double kept = 0.0;
+    for (int i = c0; i < c1; ++i) {
+      const float v = p[i];
+      bool keep = v > pstar;
+      if (v == pstar) {
+        keep = rank < (double)need;
+        rank += 1.0;
+      }
+      if (keep) kept += (double)v; else p[i] = 0.0f;
+    }
+    const float total = (float)block_sum_d(kept, scratch_d);
+    if (total > 0.0f)
+      for (int i = c0; i < c1; ++i) p[i] = p[i] / total;
+    __syncthreads();
+  }
+
+  // ---- inverse CDF in id order ----
+  double mine = 0.0;
+  for (int i = c0; i < c1; ++i) mine += (double)p[i];
+  double total;
+  const double before = block_scan_d(mine, scratch_d, &total);
+  const double draw = uniform[r] * total;
+  if (tid == 0) shared_i = vocab - 1;
+  __syncthreads();
+  if (c1 > c0 && before <= draw && before + mine > draw) {
+    double c = before;
+    int token = c1 - 1;
+    for (int i = c0; i < c1; ++i) {
+      c += (double)p[i];
+      if (c > draw) { token = i; break; }
+    }
+    shared_i = token;
+  }
+  __syncthreads();
+  if (tid == 0) out[r] = shared_i;
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+PKV_EXPORT int pkv_sample(const float* logits, long long row_stride, const float* temperature, const float* top_p,
+                          const double* uniform, float* probs, int32_t* out, int n_rows, int vocab,
+                          float greedy_below, void* stream) {
+  if (n_rows <= 0) return 0;
+  if (vocab <= 0 || row_stride < vocab) return PKV_ERR_SIZE;
+  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, temperature, top_p, uniform,
+                                                                    probs, out, vocab, greedy_below);
+  return launch_status();
+}

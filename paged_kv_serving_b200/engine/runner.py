@@ -1,0 +1,259 @@
+"""The step function: one ragged batch in, logits at the wanted places out.
+
+``ModelRunner.step`` is the single host -> GPU boundary of the engine. It flattens the batch to
+one token axis, ships every integer array of the step in one copy, writes the keys and values of
+every token it is given, runs the model's layer calls in their listed order and returns float32
+logits for the wanted places only. Nothing here knows about prompts versus decoding: a portion
+of a prompt, a single decoded token and a recomputation are the same operation
+(reference: src/paged_kv_serving/engine/runner.py:161-227).
+
+The runner also owns the bytes behind page numbers (``CacheStorage``), which is what
+copy-on-write and state-slot copies act on (reference: src/paged_kv_serving/engine/runner.py:128-133).
+"""
+
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from paged_kv_serving_b200 import ops
+from paged_kv_serving_b200.cache.manager import GroupSpec, plan_groups
+from paged_kv_serving_b200.cache.pages import NULL_PAGE
+from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+from paged_kv_serving_b200.models.decoder import DecoderModel
+from paged_kv_serving_b200.ops import gemm
+from paged_kv_serving_b200.parts.base import CacheBinding, GroupView, IntArena, StepContext
+
+__all__ = ["CacheStorage", "ModelRunner", "StepResult"]
+
+
+class CacheStorage:
+    """Device memory of the cache: per page group one key pool and one value pool shaped
+    ``[layers of the group, pages, kv heads, page_size, head_dim]``, and per state entry a
+    tensor ``[slots, *shape]``."""
+
+    def __init__(self, groups: list[GroupSpec], state_entries: list, *, num_blocks: int, block_size: int,
+                 dtype: torch.dtype, device: torch.device, num_state_slots: int) -> None:
+        self.groups = groups
+        self.num_blocks = num_blocks
+        self.block_size = block_size
+        self.k_pools: list[torch.Tensor] = []
+        self.v_pools: list[torch.Tensor] = []
+        self.location: dict[int, tuple[int, int]] = {}
+        for g, spec in enumerate(groups):
+            shape = (len(spec.entries), num_blocks, spec.n_kv_heads, block_size, spec.head_dim)
+            self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+            for index, entry in enumerate(spec.entries):
+                self.location[entry] = (g, index)
+        self.states: list[torch.Tensor] = []
+        self.state_index: dict[int, int] = {}
+        for entry, request in state_entries:
+            state_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[request.dtype]
+            self.state_index[entry] = len(self.states)
+            self.states.append(torch.zeros((max(1, num_state_slots), *request.shape), dtype=state_dtype, device=device))
+
+    @property
+    def cache_bytes(self) -> int:
+        pools = sum(t.numel() * t.element_size() for t in (*self.k_pools, *self.v_pools))
+        return pools + sum(t.numel() * t.element_size() for t in self.states)
+
+    def copy_page(self, group: int, source: int, destination: int) -> None:
+        if source == destination:
+            raise ValueError("a page is never copied onto itself")
+        self.k_pools[group][:, destination].copy_(self.k_pools[group][:, source])
+        self.v_pools[group][:, destination].copy_(self.v_pools[group][:, source])
+
+    def copy_state(self, source_slot: int, destination_slot: int) -> None:
+        for state in self.states:
+            state[destination_slot].copy_(state[source_slot])
+
+    def clear_state(self, slots: list[int]) -> None:
+        if slots and self.states:
+            index = torch.tensor(slots, dtype=torch.long, device=self.states[0].device)
+            for state in self.states:
+                state.index_fill_(0, index, 0)
+
+    def reset(self) -> None:
+        for tensor in (*self.k_pools, *self.v_pools, *self.states):
+            tensor.zero_()
+
+    def fill(self, value: float) -> None:
+        """Overwrite every page with ``value`` (tests poison the pool with it)."""
+        for tensor in (*self.k_pools, *self.v_pools):
+            tensor.fill_(value)
+
+    def page_fingerprint(self, group: int, page: int) -> bytes:
+        digest = hashlib.blake2b(digest_size=16)
+        for pool in (self.k_pools[group], self.v_pools[group]):
+            digest.update(pool[:, page].contiguous().view(torch.uint8).cpu().numpy().tobytes())
+        return digest.digest()
+
+
+@dataclass(slots=True)
+class StepResult:
+    """Logits of one step: ``logits[i]`` belongs to ``rows[i] = (seq_id, place in its entry)``."""
+
+    logits: torch.Tensor | None        # float32 [R, vocab] on the device, or None when R == 0
+    rows: list[tuple[str, int]]
+    num_tokens: int
+    h2d_bytes: int
+
+    def by_sequence(self) -> dict[str, np.ndarray]:
+        """Host rows keyed by sequence id (the last wanted place of each entry)."""
+        if self.logits is None:
+            return {}
+        host = self.logits.cpu().numpy()
+        return {seq_id: host[i] for i, (seq_id, _) in enumerate(self.rows)}
+
+
+class ModelRunner:
+    """Owns the cache storage of one model and runs ragged batches against it."""
+
+    def __init__(self, model: DecoderModel, *, num_blocks: int, block_size: int, max_running_seqs: int = 64) -> None:
+        if num_blocks < 1 or block_size < 1:
+            raise ValueError("num_blocks and block_size must be >= 1")
+        if not torch.cuda.is_available():
+            raise RuntimeError("paged_kv_serving_b200 runs on a CUDA GPU only; there is no CPU path")
+        self.model = model
+        self.num_blocks = num_blocks
+        self.block_size = block_size
+        self.order = model.layout.resolved_order()
+        self.groups, self.state_entries = plan_groups(model.layout.cache_entries())
+        self.num_state_slots = max_running_seqs if self.state_entries else 0
+        self.storage = CacheStorage(self.groups, self.state_entries, num_blocks=num_blocks, block_size=block_size,
+                                    dtype=model.dtype, device=model.device, num_state_slots=self.num_state_slots)
+        self.bindings: list[CacheBinding | None] = []
+        for call in self.order:
+            if call.cache is None:
+                self.bindings.append(None)
+            elif call.cache in self.storage.location:
+                g, index = self.storage.location[call.cache]
+                self.bindings.append(CacheBinding(call.cache, group=g, index=index, write=call.write))
+            else:
+                self.bindings.append(CacheBinding(call.cache, state=self.storage.state_index[call.cache], write=call.write))
+        self._status = torch.zeros((1,), dtype=torch.int32, device=model.device)
+        self.steps_run = 0
+
+    # --- storage behind the cache manager -------------------------------------------------
+
+    @property
+    def num_groups(self) -> int:
+        return len(self.groups)
+
+    @property
+    def cache_bytes(self) -> int:
+        return self.storage.cache_bytes
+
+    @property
+    def capacity_tokens(self) -> int:
+        return self.num_blocks * self.block_size
+
+    def copy_page(self, group: int, source: int, destination: int) -> None:
+        self.storage.copy_page(group, source, destination)
+
+    def copy_state(self, source_slot: int, destination_slot: int) -> None:
+        self.storage.copy_state(source_slot, destination_slot)
+
+    def reset_cache(self) -> None:
+        self.storage.reset()
+
+    # --- the step ------------------------------------------------------------------------
+
+    def _validate(self, batch: ExecutionBatch) -> None:
+        config = self.model.layout
+        for entry in batch.entries:
+            ids = entry.token_ids
+            if min(ids) < 0 or max(ids) >= config.vocab_size:
+                raise ValueError(f"sequence {entry.seq_id}: token id outside the vocabulary")
+            if entry.context_len > config.max_positions:
+                raise ValueError(f"sequence {entry.seq_id}: position beyond max_seq_len")
+            if len(entry.block_tables) != len(self.groups):
+                raise ValueError(f"sequence {entry.seq_id}: {len(entry.block_tables)} page tables for "
+                                 f"{len(self.groups)} page groups")
+            first_page = entry.first_position // self.block_size
+            last_page = (entry.context_len - 1) // self.block_size
+            for table in entry.block_tables:
+                if last_page >= len(table):
+                    raise ValueError(f"sequence {entry.seq_id}: position {entry.context_len - 1} has no page in the table")
+                for page in table[first_page:last_page + 1]:
+                    if page == NULL_PAGE or not 0 <= page < self.num_blocks:
+                        raise ValueError(f"sequence {entry.seq_id}: a written position has no valid page")
+            if self.state_entries and entry.state_slot is None:
+                raise ValueError(f"sequence {entry.seq_id}: the model keeps per-request state but no slot was given")
+
+    def _context(self, batch: ExecutionBatch) -> tuple[StepContext, list[tuple[str, int]]]:
+        entries = batch.entries
+        lens = [e.num_tokens for e in entries]
+        total = sum(lens)
+        arena = IntArena()
+        tokens = np.fromiter((t for e in entries for t in e.token_ids), dtype=np.int32, count=total)
+        starts = np.zeros(len(entries) + 1, dtype=np.int64)
+        np.cumsum(lens, out=starts[1:])
+        first = np.asarray([e.first_position for e in entries], dtype=np.int64)
+        seq_of_token = np.repeat(np.arange(len(entries)), lens)
+        positions = np.arange(total, dtype=np.int64) - starts[seq_of_token] + first[seq_of_token]
+        arena.add(StepContext.TOKEN_IDS, tokens)
+        arena.add(StepContext.POSITIONS, positions)
+        arena.add(StepContext.SEQ_STARTS, starts)
+        arena.add(StepContext.FIRST_POS, first)
+        arena.add(StepContext.CONTEXT_LENS, first + np.asarray(lens))
+        arena.add(StepContext.STATE_SLOTS, [e.state_slot if e.state_slot is not None else 0 for e in entries])
+        rows: list[tuple[str, int]] = []
+        row_index: list[int] = []
+        for e, start in zip(entries, starts[:-1]):
+            for place in e.logits_at:
+                rows.append((e.seq_id, place))
+                row_index.append(int(start) + place)
+        arena.add(StepContext.LOGITS_ROWS, row_index if row_index else [0])
+        views = []
+        for g in range(len(self.groups)):
+            width = max(len(e.block_tables[g]) for e in entries)
+            table = np.full((len(entries), width), NULL_PAGE, dtype=np.int32)
+            for i, e in enumerate(entries):
+                table[i, :len(e.block_tables[g])] = e.block_tables[g]
+            page_of_token = table[seq_of_token, positions // self.block_size].astype(np.int64)
+            slots = page_of_token * self.block_size + positions % self.block_size
+            table_name, slots_name = f"group{g}/block_table", f"group{g}/slots"
+            arena.add(table_name, table)
+            arena.add(slots_name, slots)
+            views.append(GroupView(self.storage.k_pools[g], self.storage.v_pools[g], self.block_size,
+                                   self.groups[g].window, table_name, slots_name))
+        ctx = StepContext(dtype=self.model.dtype, device=self.model.device, num_tokens=total, num_seqs=len(entries),
+                          seq_lens=lens, first_positions=[e.first_position for e in entries], arena=arena,
+                          groups=views, states=self.storage.states)
+        return ctx, rows
+
+    def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None) -> StepResult:
+        """Run one batch: writes the cache for every token given, returns logits where wanted."""
+        if not batch.entries:
+            return StepResult(None, [], 0, 0)
+        self._validate(batch)
+        ctx, rows = self._context(batch)
+        model = self.model
+        for call, binding in zip(self.order, self.bindings):
+            model.layout.blocks[call.layer].plan_step(ctx, binding)
+        ctx.arena.upload(model.device)
+        if clear_state_slots:
+            self.storage.clear_state(clear_state_slots)
+        hidden = ops.embedding_gather(model.embedding, ctx.ints(StepContext.TOKEN_IDS), self._status)
+        delta = None
+        for call, binding in zip(self.order, self.bindings):
+            delta = model.layout.blocks[call.layer].forward(hidden, delta, ctx, binding)
+        self.steps_run += 1
+        if not rows:
+            return StepResult(None, [], ctx.num_tokens, ctx.arena.bytes_uploaded)
+        normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
+        logits = gemm.matmul(normed, model.head.t(), out_dtype=torch.float32)
+        return StepResult(logits, rows, ctx.num_tokens, ctx.arena.bytes_uploaded)
+
+    def execute(self, batch: ExecutionBatch) -> dict[str, np.ndarray]:
+        """The reference's executor interface (src/paged_kv_serving/engine/engine.py:64-73):
+        host float32 rows keyed by sequence id."""
+        result = self.step(batch).by_sequence()
+        if int(self._status.item()) != 0:
+            raise RuntimeError("a kernel saw a token id outside the embedding table")
+        return result

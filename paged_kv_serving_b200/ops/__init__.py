@@ -1,0 +1,194 @@
+"""Python bindings of the hand-written CUDA kernels (``csrc/*.cu``), through ``ctypes``.
+
+Every wrapper takes torch tensors that live on the GPU, checks what the kernel relies on
+(dtype, contiguity, sizes), launches on torch's current stream and raises on a refused argument
+or a failed launch. Nothing here falls back to a library or to the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from paged_kv_serving_b200.ops.build import build_all, library, library_names
+
+__all__ = [
+    "add_rmsnorm", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather",
+    "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul",
+]
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+_ERRORS = {
+    -2: "unsupported element type", -3: "refused size", -4: "refused alignment",
+    -5: "size beyond the kernel's limit",
+}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise TypeError(f"kernels take float32 or bfloat16 tensors, not {dtype}") from None
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise ValueError(f"{what}: {_ERRORS.get(status, f'refused (code {status})')}")
+    raise RuntimeError(f"{what}: CUDA error {status} at launch")
+
+
+def _ptr(tensor: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(tensor: torch.Tensor, dtype: torch.dtype | None, name: str) -> None:
+    if not tensor.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and tensor.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, found {tensor.dtype}")
+    if not tensor.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+_SIGNATURES_SET: set[tuple[str, str]] = set()
+
+
+def _fn(lib_name: str, fn_name: str, argtypes: list):
+    lib = library(lib_name)
+    fn = getattr(lib, fn_name)
+    if (lib_name, fn_name) not in _SIGNATURES_SET:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _SIGNATURES_SET.add((lib_name, fn_name))
+    return fn
+
+
+# ---------------------------------------------------------------------------------------------
+
+
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """``table[ids]`` widened to float32. An id outside the table sets ``status[0]`` to 1."""
+    _need(table, None, "table"); _need(ids, torch.int32, "ids"); _need(status, torch.int32, "status")
+    vocab, d = table.shape
+    out = torch.empty((ids.numel(), d), dtype=torch.float32, device=table.device)
+    fn = _fn("elementwise", "pkv_embedding_gather",
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), ids.numel(), d, vocab,
+              _ptr(status), _stream()), "embedding_gather")
+    return out
+
+
+def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``hidden += delta`` (in place, float32) and the RMS-normalised rows in ``out_dtype``.
+
+    With ``rows`` only those rows are normalised and returned, and ``hidden`` is left untouched.
+    """
+    _need(hidden, torch.float32, "hidden"); _need(weight, torch.float32, "weight")
+    n, d = hidden.shape
+    if weight.numel() != d:
+        raise ValueError(f"norm weight has {weight.numel()} elements, the stream is {d} wide")
+    if delta is not None:
+        _need(delta, None, "delta")
+        if delta.shape != hidden.shape:
+            raise ValueError("delta and hidden differ in shape")
+    n_rows = n
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        n_rows = rows.numel()
+    out = torch.empty((n_rows, d), dtype=out_dtype, device=hidden.device)
+    fn = _fn("elementwise", "pkv_add_rmsnorm",
+             [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(weight),
+              float(eps), _ptr(out), dtype_code(out_dtype), _ptr(rows), n_rows, d, _stream()), "add_rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, clip: float) -> torch.Tensor:
+    """``silu(gate) * up`` for a fused ``[T, 2*ff]`` input whose first half of columns is the gate."""
+    _need(gate_up, None, "gate_up")
+    n, two_ff = gate_up.shape
+    ff = two_ff // 2
+    out = torch.empty((n, ff), dtype=gate_up.dtype, device=gate_up.device)
+    fn = _fn("elementwise", "pkv_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(gate_up), _ptr(out), dtype_code(gate_up.dtype), n, ff, float(clip), _stream()), "silu_mul")
+    return out
+
+
+def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None,
+                  k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor | None,
+                  n_heads: int, n_kv: int, head_dim: int, page_size: int) -> None:
+    """Rotate q and k of ``qkv [T, (H+2KV)*hd]`` by position (q in place) and write k, v to the
+    pools ``[pages, KV, page_size, hd]`` at ``slots`` (``None``: rotate q only, store nothing)."""
+    _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions")
+    _need(k_pool, None, "k_pool"); _need(v_pool, None, "v_pool")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise ValueError("qkv width does not match (n_heads + 2*n_kv) * head_dim")
+    if cos is not None:
+        _need(cos, torch.float32, "cos"); _need(sin, torch.float32, "sin")
+        if cos.shape[1] != head_dim // 2:
+            raise ValueError("rotary tables must be [positions, head_dim/2]")
+    if slots is not None:
+        _need(slots, torch.int32, "slots")
+    fn = _fn("elementwise", "pkv_rope_kv_store",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(qkv), dtype_code(qkv.dtype), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_pool), _ptr(v_pool),
+              dtype_code(k_pool.dtype), _ptr(slots), n, n_heads, n_kv, head_dim, page_size,
+              0 if slots is None else 1, _stream()), "rope_kv_store")
+
+
+def attention_rows_per_block() -> int:
+    lib = library("attention_generic")
+    lib.pkv_attention_generic_rows_per_block.restype = c_int
+    return int(lib.pkv_attention_generic_rows_per_block())
+
+
+def paged_attention_generic(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                            block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
+                            work_seq: torch.Tensor, work_row0: torch.Tensor, n_heads: int, n_kv: int,
+                            head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+    """Causal attention of the (rotated) queries in ``qkv`` over the paged cache; ``[T, H*hd]``."""
+    _need(qkv, None, "qkv"); _need(k_pool, None, "k_pool"); _need(v_pool, None, "v_pool")
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("work_row0", work_row0)):
+        _need(t, torch.int32, name)
+    n = qkv.shape[0]
+    out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    fn = _fn("attention_generic", "pkv_paged_attention_generic",
+             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), dtype_code(qkv.dtype), _ptr(k_pool), _ptr(v_pool),
+              dtype_code(k_pool.dtype), _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos),
+              _ptr(work_seq), _ptr(work_row0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window),
+              float(scale), _stream()), "paged_attention_generic")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
+           greedy_below: float, probs: torch.Tensor | None = None) -> torch.Tensor:
+    """One token id per row of ``logits [R, V]`` (float32); ``uniform`` is float64, one per row."""
+    _need(logits, torch.float32, "logits"); _need(temperature, torch.float32, "temperature")
+    _need(top_p, torch.float32, "top_p"); _need(uniform, torch.float64, "uniform")
+    rows, vocab = logits.shape
+    if probs is None:
+        probs = torch.empty((rows, vocab), dtype=torch.float32, device=logits.device)
+    else:
+        _need(probs, torch.float32, "probs")
+        if probs.numel() < rows * vocab:
+            raise ValueError("probs scratch is smaller than the logits")
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    fn = _fn("sampling", "pkv_sample",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), _ptr(temperature), _ptr(top_p), _ptr(uniform), _ptr(probs), _ptr(out),
+              rows, vocab, float(greedy_below), _stream()), "sample")
+    return out

@@ -1,0 +1,16 @@
+"""Layer parts: norm, position encoding, mixer, feed-forward and their arrangement in a block."""
+
+from paged_kv_serving_b200.parts.attention import PagedAttention
+from paged_kv_serving_b200.parts.base import (
+    CacheBinding, GroupView, IntArena, PagedKVRequest, ParamSpec, Part, StateRequest, StepContext,
+)
+from paged_kv_serving_b200.parts.block import PreNormBlock
+from paged_kv_serving_b200.parts.feed_forward import SwiGLU
+from paged_kv_serving_b200.parts.norms import RMSNorm
+from paged_kv_serving_b200.parts.position import NoPositionEncoding, PositionEncoding, RotaryEncoding
+
+__all__ = [
+    "CacheBinding", "GroupView", "IntArena", "NoPositionEncoding", "PagedAttention", "PagedKVRequest",
+    "ParamSpec", "Part", "PositionEncoding", "PreNormBlock", "RMSNorm", "RotaryEncoding", "StateRequest",
+    "StepContext", "SwiGLU",
+]

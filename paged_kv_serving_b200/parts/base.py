@@ -1,0 +1,177 @@
+"""What every part of a layer has in common, and what a step hands to the parts.
+
+A part (norm, position encoding, mixer, feed-forward, block) is built from explicit sizes and
+constants, declares the tensors it needs (``param_specs``), receives them once (``load``) and
+then transforms activations step by step. A part never looks at a model configuration and never
+knows which model it is in. A mixer may ask the cache manager for paged key/value storage
+(``PagedKVRequest``) or for a fixed-size state per running request (``StateRequest``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+import torch
+
+__all__ = [
+    "CacheBinding", "GroupView", "IntArena", "PagedKVRequest", "ParamSpec", "Part", "StateRequest",
+    "StepContext",
+]
+
+
+@dataclass(frozen=True, slots=True)
+class ParamSpec:
+    """Shape and role of one tensor. ``matrix``: an operand of a matrix product, held in the
+    engine's compute type; ``vector``: an element-wise parameter, held in float32;
+    ``int_table``: an integer table, held in int32."""
+
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+
+    def __post_init__(self) -> None:
+        if self.kind not in ("matrix", "vector", "int_table"):
+            raise ValueError(f"unknown parameter kind {self.kind!r}")
+
+
+@dataclass(frozen=True, slots=True)
+class PagedKVRequest:
+    """Paged keys and values for one layer call: ``window=None`` keeps every key, a number keeps
+    only the last ``window`` positions (older pages are given back)."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True, slots=True)
+class StateRequest:
+    """A fixed-size state per running request, e.g. ``shape=(heads, dim)``; zeroed when a request
+    (re)starts from position zero."""
+
+    shape: tuple[int, ...]
+    dtype: str = "float32"
+
+
+class Part:
+    """Base class of all parts. Sub-classes override what they need."""
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {}
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        """Receive the tensors named by ``param_specs`` (already on the device, already in the
+        type their kind asks for). A part may re-lay them out for its kernels here."""
+        for name, tensor in params.items():
+            setattr(self, name, tensor)
+
+    def sub_parts(self) -> dict[str, "Part"]:
+        """Named children whose tensors are prefixed with their name."""
+        return {}
+
+    def cache_request(self) -> PagedKVRequest | StateRequest | None:
+        return None
+
+    def plan_step(self, ctx: "StepContext", binding: "CacheBinding | None") -> None:
+        """Called once per layer call before a step's kernels run, on the host: a part that needs
+        integer arrays on the device (work lists, tables) adds them to ``ctx.arena`` here, so that
+        everything a step needs crosses to the device in one copy."""
+
+
+class IntArena:
+    """Collects the int32 arrays of one step on the host and uploads them in a single copy."""
+
+    def __init__(self) -> None:
+        self._arrays: dict[str, np.ndarray] = {}
+        self._device: dict[str, torch.Tensor] = {}
+        self.uploaded = False
+        self.bytes_uploaded = 0
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._arrays
+
+    def add(self, name: str, values: Any, shape: tuple[int, ...] | None = None) -> None:
+        if self.uploaded:
+            raise RuntimeError("the step's integer arrays were already uploaded")
+        array = np.ascontiguousarray(np.asarray(values, dtype=np.int32))
+        if shape is not None:
+            array = array.reshape(shape)
+        self._arrays[name] = array
+
+    def upload(self, device: torch.device) -> None:
+        names = list(self._arrays)
+        sizes = [self._arrays[n].size for n in names]
+        # every array starts on a 16-byte boundary (4 int32)
+        offsets, total = [], 0
+        for size in sizes:
+            offsets.append(total)
+            total += (size + 3) // 4 * 4
+        host = torch.empty((max(total, 4),), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        view = host.numpy()
+        for name, offset, size in zip(names, offsets, sizes):
+            view[offset:offset + size] = self._arrays[name].reshape(-1)
+        dev = host.to(device, non_blocking=True)
+        self._pinned = host  # keep alive until the copy has run
+        for name, offset, size in zip(names, offsets, sizes):
+            self._device[name] = dev[offset:offset + size].view(self._arrays[name].shape)
+        self.uploaded = True
+        self.bytes_uploaded = total * 4
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self._device[name]
+
+    def host(self, name: str) -> np.ndarray:
+        return self._arrays[name]
+
+
+@dataclass(frozen=True, slots=True)
+class CacheBinding:
+    """Where one layer call finds its cache: ``group``/``index`` select a layer's pages inside a
+    page group (or ``state`` a state tensor); ``write=False`` reads what another call wrote."""
+
+    entry: int
+    group: int | None = None
+    index: int | None = None
+    state: int | None = None
+    write: bool = True
+
+
+@dataclass(slots=True)
+class GroupView:
+    """One page group as a step sees it."""
+
+    k_pool: torch.Tensor          # [layers of the group, pages, KV, page_size, hd]
+    v_pool: torch.Tensor
+    page_size: int
+    window: int | None
+    table_name: str               # arena names of this group's arrays
+    slots_name: str
+
+
+@dataclass(slots=True)
+class StepContext:
+    """Everything the parts may read during one step."""
+
+    dtype: torch.dtype
+    device: torch.device
+    num_tokens: int
+    num_seqs: int
+    seq_lens: list[int]                # tokens of each entry in this step
+    first_positions: list[int]         # absolute position of each entry's first token
+    arena: IntArena
+    groups: list[GroupView] = field(default_factory=list)
+    states: list[torch.Tensor] = field(default_factory=list)   # [slots, *shape] per state entry
+    scratch: dict[str, Any] = field(default_factory=dict)
+
+    # the arrays every step has (names in the arena)
+    TOKEN_IDS = "token_ids"
+    POSITIONS = "positions"
+    SEQ_STARTS = "seq_starts"
+    FIRST_POS = "first_pos"
+    CONTEXT_LENS = "context_lens"
+    STATE_SLOTS = "state_slots"
+    LOGITS_ROWS = "logits_rows"
+
+    def ints(self, name: str) -> torch.Tensor:
+        return self.arena[name]

@@ -1,0 +1,74 @@
+"""Shared pieces of the tests: the two tiny configurations, model builders, trace drivers."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import plain_model
+
+# Two tiny configurations of the architecture that differ in every size and option
+# (head counts and groups, sizes that are no power of two, layers, vocabulary, eps, rope base,
+# tied or separate head). Page sizes differ too (see PAGE_SIZE).
+TINY_A = {
+    "architecture": "LlamaToyDecoder", "vocab_size": 256, "d_model": 64, "n_layers": 2, "n_heads": 4,
+    "n_kv_heads": 2, "head_dim": 16, "d_ff": 172, "max_seq_len": 128, "rope_theta": 10000.0,
+    "norm_eps": 1e-5, "tie_embeddings": False,
+}
+TINY_B = {
+    "architecture": "LlamaToyDecoder", "vocab_size": 384, "d_model": 96, "n_layers": 3, "n_heads": 3,
+    "n_kv_heads": 3, "head_dim": 32, "d_ff": 256, "max_seq_len": 256, "rope_theta": 500000.0,
+    "norm_eps": 1e-6, "tie_embeddings": True,
+}
+# A third shape for longer sequences: head size 48 (a step of 16, no power of two), 6 query heads
+# in 2 groups of 3, a vocabulary and widths that are no powers of two.
+TINY_C = {
+    "architecture": "LlamaToyDecoder", "vocab_size": 331, "d_model": 120, "n_layers": 2, "n_heads": 6,
+    "n_kv_heads": 2, "head_dim": 48, "d_ff": 200, "max_seq_len": 1024, "rope_theta": 50000.0,
+    "norm_eps": 3e-6, "tie_embeddings": True,
+}
+PAGE_SIZE = {"A": 4, "B": 8, "C": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+WEIGHT_SEED = {"A": 0, "B": 2, "C": 5}
+
+# Tolerances, fixed before any GPU run. float32: the reference's own bound for paged against
+# dense logits (tests/property/test_equivalence.py:33-34 of the reference). bfloat16: activations
+# carry 8 bits of mantissa (relative 2^-8 per rounding); with a few roundings per layer on logits
+# of magnitude ~1 the bound is 3% of the largest logit of the compared rows plus a small floor.
+F32_ATOL = 1e-4
+
+
+def bf16_atol(reference: np.ndarray) -> float:
+    return 0.03 * float(np.abs(reference).max()) + 2e-3
+
+
+def tensors_for(name: str, dtype: str, std: float = 0.08, norm_jitter: float = 0.1) -> dict[str, np.ndarray]:
+    """Random float32 tensors of a tiny configuration; for bfloat16 the matrices are rounded so
+    that the plain implementation and the engine hold exactly the same values."""
+    tensors = plain_model.random_tensors(CONFIGS[name], WEIGHT_SEED[name], std=std, norm_jitter=norm_jitter)
+    if dtype == "bfloat16":
+        tensors = {k: (plain_model.round_to_bfloat16(v) if v.ndim == 2 else v) for k, v in tensors.items()}
+    return tensors
+
+
+def build_model(config: dict, tensors: dict[str, np.ndarray], dtype: str):
+    from paged_kv_serving_b200.config import ModelConfig
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+
+    torch_tensors = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in tensors.items()}
+    return DecoderModel.from_tensors(ModelConfig.from_dict(config), torch_tensors, dtype=dtype, device="cuda")
+
+
+def random_tokens(config: dict, count: int, seed: int) -> list[int]:
+    return [int(t) for t in np.random.default_rng(seed).integers(0, config["vocab_size"], size=count)]
+
+
+def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what: str) -> None:
+    atol = F32_ATOL if dtype == "float32" else bf16_atol(want)
+    gap = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    worst = float(gap.max())
+    if not worst <= atol:
+        row, col = np.unravel_index(int(gap.argmax()), gap.shape)
+        first_bad = int(np.argmax(gap.max(axis=-1) > atol))
+        raise AssertionError(f"{what}: max |gap| {worst:.3e} > {atol:.3e} at row {row}, column {col}; "
+                             f"first row beyond the bound: {first_bad}")

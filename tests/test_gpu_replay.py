@@ -1,0 +1,146 @@
+"""The engine against the plain implementation, through the replay session (``-m gpu``).
+
+Every request is replayed whole, with the last 32 tokens decoded one by one, in portions of
+changing size down to two tokens, and mixed with other requests in a pool so small that pages
+are used again; in float32 and in bfloat16; on tiny configurations that differ in every size.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import helpers
+import plain_model
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ("float32", "bfloat16")
+LENGTHS = {"A": 100, "B": 150, "C": 300}
+
+
+def _session(name, dtype, max_tokens):
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    tensors = helpers.tensors_for(name, dtype)
+    model = helpers.build_model(helpers.CONFIGS[name], tensors, dtype)
+    session = ReplaySession(model, max_tokens=max_tokens, block_size=helpers.PAGE_SIZE[name])
+    session.runner.storage.fill(float("nan"))   # stale pages must never be read
+    return session, tensors
+
+
+def _reference(name, tensors, tokens):
+    return plain_model.forward(helpers.CONFIGS[name], tensors, tokens)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("A", "B", "C"))
+def test_whole_prompt_every_position(name, dtype):
+    session, tensors = _session(name, dtype, 512)
+    tokens = helpers.random_tokens(helpers.CONFIGS[name], LENGTHS[name], seed=11)
+    got = session.step([{"id": "r", "tokens": tokens, "want": list(range(len(tokens)))}], end=["r"])
+    helpers.assert_close(got, _reference(name, tensors, tokens), dtype, f"{name} whole")
+    session.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("A", "B", "C"))
+def test_bulk_then_last_32_one_by_one(name, dtype):
+    session, tensors = _session(name, dtype, 512)
+    tokens = helpers.random_tokens(helpers.CONFIGS[name], LENGTHS[name], seed=12)
+    want = _reference(name, tensors, tokens)
+    bulk = len(tokens) - 32
+    got = [session.step([{"id": "r", "tokens": tokens[:bulk], "want": [bulk - 1]}])]
+    for i in range(bulk, len(tokens)):
+        got.append(session.step([{"id": "r", "tokens": [tokens[i]], "want": [0]}]))
+    helpers.assert_close(np.concatenate(got), want[bulk - 1:], dtype, f"{name} bulk+decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("A", "B", "C"))
+def test_portions_of_changing_size(name, dtype):
+    session, tensors = _session(name, dtype, 512)
+    tokens = helpers.random_tokens(helpers.CONFIGS[name], LENGTHS[name], seed=13)
+    want = _reference(name, tensors, tokens)
+    sizes, cycle, at = [], [7, 3, 11, 2, 5, 2, 13, 1, 4], 0
+    while sum(sizes) < len(tokens):
+        sizes.append(min(cycle[at % len(cycle)], len(tokens) - sum(sizes)))
+        at += 1
+    start, rows, got = 0, [], []
+    for size in sizes:
+        out = session.step([{"id": "r", "tokens": tokens[start:start + size], "want": [0, size - 1] if size > 1 else [0]}])
+        rows += [start, start + size - 1] if size > 1 else [start]
+        got.append(out)
+        start += size
+    helpers.assert_close(np.concatenate(got), want[rows], dtype, f"{name} portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("A", "B"))
+def test_mixed_requests_with_page_reuse(name, dtype):
+    """Up to four live requests; portions of some beside decoded tokens of others; the pool
+    (256 tokens) is smaller than what all requests need together, so pages are used again."""
+    config = helpers.CONFIGS[name]
+    session, tensors = _session(name, dtype, 256)
+    lengths = [60, 50, 64, 40, 64, 30, 55, 48]
+    prompts = [helpers.random_tokens(config, n, seed=100 + i) for i, n in enumerate(lengths)]
+    wants = [_reference(name, tensors, p) for p in prompts]
+    rng = np.random.default_rng(7)
+    progress = [0] * len(prompts)
+    waiting = list(range(len(prompts)))
+    live: list[int] = []
+    pages_seen: set[int] = set()
+    reused = False
+    step = 0
+    while waiting or live:
+        while waiting and len(live) < 4 and sum(-(-lengths[i] // 64) * 64 for i in live) + 64 <= 256:
+            live.append(waiting.pop(0))
+        entries, finished, checks = [], [], []
+        for i in live:
+            remaining = lengths[i] - progress[i]
+            decode_phase = remaining <= 8
+            size = 1 if decode_phase else int(min(remaining - 8, rng.integers(2, 14)))
+            chunk = prompts[i][progress[i]:progress[i] + size]
+            want = [size - 1]
+            entries.append({"id": f"q{i}", "tokens": chunk, "want": want})
+            checks.append((i, progress[i] + size - 1))
+            progress[i] += size
+            if progress[i] == lengths[i]:
+                finished.append(i)
+        got = session.step(entries, end=[f"q{i}" for i in finished])
+        for row, (i, position) in enumerate(checks):
+            helpers.assert_close(got[row:row + 1], wants[i][position:position + 1], dtype,
+                                 f"{name} mixed step {step} request {i} position {position}")
+        for sequence in session.live.values():
+            for page in sequence.block_table:
+                pages_seen.add(page)
+        for i in finished:
+            live.remove(i)
+        session.check_invariants()
+        step += 1
+    total_pages_needed = sum(-(-n // helpers.PAGE_SIZE[name]) for n in lengths)
+    assert total_pages_needed > session.num_blocks, "the scenario must need more pages than the pool has"
+    assert session.cache.num_free_blocks == session.num_blocks
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_and_single_token_prompt(dtype):
+    session, tensors = _session("B", dtype, 256)
+    tokens = helpers.random_tokens(helpers.TINY_B, 5, seed=14)
+    want = _reference("B", tensors, tokens)
+    got = [session.step([{"id": "one", "tokens": tokens[:1], "want": [0]}])]
+    got.append(session.step([{"id": "one", "tokens": tokens[1:3], "want": [0, 1]}]))
+    got.append(session.step([{"id": "one", "tokens": tokens[3:], "want": [0, 1]}], end=["one"]))
+    helpers.assert_close(np.concatenate(got), want, dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype):
+    """A short prompt, then 400 tokens decoded one by one, in config C (pages of 16)."""
+    session, tensors = _session("C", dtype, 512)
+    tokens = helpers.random_tokens(helpers.TINY_C, 420, seed=15)
+    want = _reference("C", tensors, tokens)
+    got = [session.step([{"id": "r", "tokens": tokens[:20], "want": [19]}])]
+    for i in range(20, len(tokens)):
+        got.append(session.step([{"id": "r", "tokens": [tokens[i]], "want": [0]}]))
+    helpers.assert_close(np.concatenate(got), want[19:], dtype, "long decoding")
