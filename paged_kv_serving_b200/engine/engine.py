@@ -297,6 +297,10 @@ class Engine:
         producers: list[Sequence] = []
         for item in plan.scheduled:
             sequence = item.sequence
+            state = self._requests.get(sequence.request.request_id)
+            if state is not None:  # noted while the sequence still holds its pages
+                state.cached_prompt_tokens = max(state.cached_prompt_tokens,
+                                                 sequence.cached_prefix_blocks * self.config.block_size)
             sequence.num_computed_tokens += item.num_tokens
             self.cache.publish_full_blocks(sequence)
             self.cache.release_behind_window(sequence)
@@ -397,8 +401,6 @@ class Engine:
             state.finished[sequence.sample_index] = SampleOutput(
                 sequence.sample_index, tuple(sequence.output_token_ids),
                 sequence.finish_reason or FinishReason.LENGTH, sequence.preemption_count)
-            state.cached_prompt_tokens = max(state.cached_prompt_tokens,
-                                             sequence.cached_prefix_blocks * self.config.block_size)
             if state.complete:
                 request = state.request
                 del self._requests[request.request_id]

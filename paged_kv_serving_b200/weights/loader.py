@@ -84,5 +84,7 @@ def read_model_folder(folder: str | Path, expect_manifest_sha256: str | None = N
     for name in (CONFIG_FILE, WEIGHTS_FILE):
         if not (folder / name).is_file():
             raise FileNotFoundError(f"model folder {folder} has no {name}")
-    config = ModelConfig.from_json_file(folder / CONFIG_FILE)
+    from paged_kv_serving_b200.config import load_config
+
+    config = load_config(folder / CONFIG_FILE)
     return config, read_safetensors(folder / WEIGHTS_FILE)

@@ -1,0 +1,290 @@
+"""Each kernel alone against a plain float32 reference, at other sizes than the engine's tests
+use (``-m gpu``). Inputs are made so that faults show: a far key that dominates the softmax,
+queries at page and window edges, unused slots filled with NaN."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype, scale=1.0):
+    return 2e-5 * scale if dtype == "float32" else 2e-2 * scale
+
+
+def dev(array, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(array)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def as_np(tensor):
+    return tensor.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_gather(dtype):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(0)
+    table = rng.standard_normal((1000, 200)).astype(np.float32)
+    table_d = dev(table, DTYPES[dtype])
+    ids = rng.integers(0, 1000, size=77).astype(np.int32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.embedding_gather(table_d, dev(ids), status)
+    assert out.dtype == torch.float32
+    assert np.array_equal(as_np(out), as_np(table_d)[ids])
+    assert int(status.item()) == 0
+    bad = ids.copy()
+    bad[5] = 1000
+    ops.embedding_gather(table_d, dev(bad), status)
+    assert int(status.item()) == 1                      # recorded, and nothing outside the table was read
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000, 4096, 11008])
+def test_add_rmsnorm(dtype, width):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(width)
+    hidden = (rng.standard_normal((9, width)) * 3).astype(np.float32)
+    delta = rng.standard_normal((9, width)).astype(np.float32)
+    weight = (1 + 0.2 * rng.standard_normal(width)).astype(np.float32)
+    delta_d = dev(delta, DTYPES[dtype])
+    delta_seen = as_np(delta_d)
+    hidden_d = dev(hidden)
+    out = ops.add_rmsnorm(hidden_d, delta_d, dev(weight), 1e-5, DTYPES[dtype])
+    summed = hidden + delta_seen
+    assert np.allclose(as_np(hidden_d), summed, atol=1e-6)          # the stream is updated in float32
+    assert np.abs(as_np(out) - plain_model.rms_norm(summed, weight, 1e-5)).max() <= tol(dtype, 4)
+    # no delta: the stream stays; rows: only those rows, stream untouched
+    before = as_np(hidden_d).copy()
+    rows = np.array([7, 0, 3], dtype=np.int32)
+    picked = ops.add_rmsnorm(hidden_d, delta_d, dev(weight), 1e-5, DTYPES[dtype], rows=dev(rows))
+    assert np.array_equal(as_np(hidden_d), before)
+    want = plain_model.rms_norm(before[rows] + delta_seen[rows], weight, 1e-5)
+    assert np.abs(as_np(picked) - want).max() <= tol(dtype, 4)
+    plain = ops.add_rmsnorm(hidden_d, None, dev(weight), 1e-5, torch.float32)
+    assert np.abs(as_np(plain) - plain_model.rms_norm(before, weight, 1e-5)).max() <= 2e-5
+    assert np.array_equal(as_np(hidden_d), before)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(1)
+    ff = 300
+    x = (rng.standard_normal((13, 2 * ff)) * 4).astype(np.float32)
+    x[0, :4] = [-100.0, 100.0, -60.0, 60.0]
+    x_d = dev(x, DTYPES[dtype])
+    seen = as_np(x_d)
+    out = ops.silu_mul(x_d, 60.0)
+    want = plain_model.silu(seen[:, :ff]) * seen[:, ff:]
+    assert np.isfinite(as_np(out)).all()
+    assert np.abs(as_np(out) - want).max() <= tol(dtype, np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rope_kv_store(dtype):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(2)
+    heads, kv, hd, page, pages, tokens = 5, 5, 48, 4, 9, 11
+    cos, sin = plain_model.rope_tables(64, hd, 1234.5)
+    qkv = rng.standard_normal((tokens, (heads + 2 * kv) * hd)).astype(np.float32)
+    positions = rng.integers(0, 64, size=tokens).astype(np.int32)
+    slots = rng.permutation(pages * page)[:tokens].astype(np.int32)
+    slots[3] = -1
+    qkv_d = dev(qkv, DTYPES[dtype])
+    seen = as_np(qkv_d).copy()
+    k_pool = torch.full((pages, kv, page, hd), float("nan"), dtype=DTYPES[dtype], device="cuda")
+    v_pool = torch.full((pages, kv, page, hd), float("nan"), dtype=DTYPES[dtype], device="cuda")
+    ops.rope_kv_store(qkv_d, dev(positions), dev(cos), dev(sin), k_pool, v_pool, dev(slots), heads, kv, hd, page)
+    q = seen[:, :heads * hd].reshape(tokens, heads, hd)
+    k = seen[:, heads * hd:(heads + kv) * hd].reshape(tokens, kv, hd)
+    v = seen[:, (heads + kv) * hd:].reshape(tokens, kv, hd)
+    q_rot = plain_model.apply_rope(q, positions, cos, sin)
+    k_rot = plain_model.apply_rope(k, positions, cos, sin)
+    got_q = as_np(qkv_d)[:, :heads * hd].reshape(tokens, heads, hd)
+    assert np.abs(got_q - q_rot).max() <= tol(dtype, 4)
+    assert np.array_equal(as_np(qkv_d)[:, heads * hd:], seen[:, heads * hd:])      # k, v columns are only read
+    kp, vp = as_np(k_pool), as_np(v_pool)
+    written = np.zeros((pages, page), dtype=bool)
+    for t in range(tokens):
+        if slots[t] < 0:
+            continue
+        p, o = divmod(int(slots[t]), page)
+        written[p, o] = True
+        assert np.abs(kp[p, :, o] - k_rot[t]).max() <= tol(dtype, 4)
+        assert np.abs(vp[p, :, o] - v[t]).max() <= tol(dtype, 1e-3)
+    untouched = np.broadcast_to(~written[:, None, :], (pages, kv, page))
+    assert np.isnan(kp[untouched]).all() and np.isnan(vp[untouched]).all()        # nothing else was touched
+    # without tables: q untouched, k stored unrotated; without slots: nothing stored
+    qkv_d2 = dev(qkv, DTYPES[dtype])
+    ops.rope_kv_store(qkv_d2, dev(positions), None, None, k_pool, v_pool, dev(slots), heads, kv, hd, page)
+    assert np.array_equal(as_np(qkv_d2), seen)
+    p, o = divmod(int(slots[0]), page)
+    assert np.array_equal(as_np(k_pool)[p, :, o], k[0])
+
+
+def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True):
+    """Random sequences already in the cache (``contexts`` tokens each), of which the last
+    ``queries`` tokens are this step's queries. Returns device inputs and the plain answer."""
+    from paged_kv_serving_b200 import ops
+
+    torch_dtype = DTYPES[dtype]
+    total_pages = sum(-(-c // page) for c in contexts) + 3
+    order = rng.permutation(total_pages)
+    k_pool = torch.full((total_pages, kv, page, hd), float("nan"), dtype=torch_dtype, device="cuda")
+    v_pool = torch.full((total_pages, kv, page, hd), float("nan"), dtype=torch_dtype, device="cuda")
+    tables, q_rows, wants, starts, firsts = [], [], [], [0], []
+    width = max(-(-c // page) for c in contexts)
+    used = 0
+    for context, n_q in zip(contexts, queries):
+        q = rng.standard_normal((context, heads, hd)).astype(np.float32)
+        k = rng.standard_normal((context, kv, hd)).astype(np.float32)
+        v = rng.standard_normal((context, kv, hd)).astype(np.float32)
+        if spike and context > 40:
+            # one far key stands out for the last query: dropping or misplacing it changes the answer
+            far = 3 if window is None else max(0, context - window)
+            k[far, :, :] = 0.0
+            k[far, :, 0] = 6.0
+            q[context - 1, :, 0] = 6.0
+        q = torch.from_numpy(q).to(torch_dtype).float().numpy()
+        k = torch.from_numpy(k).to(torch_dtype).float().numpy()
+        v = torch.from_numpy(v).to(torch_dtype).float().numpy()
+        n_pages = -(-context // page)
+        table = order[used:used + n_pages]
+        used += n_pages
+        for position in range(context):
+            p, o = table[position // page], position % page
+            k_pool[p, :, o] = torch.from_numpy(k[position]).to(torch_dtype).cuda()
+            v_pool[p, :, o] = torch.from_numpy(v[position]).to(torch_dtype).cuda()
+        tables.append(np.concatenate([table, np.full(width - n_pages, -1)]))
+        full = plain_model.causal_attention(q, k, v, 1.0 / math.sqrt(hd), window=window)
+        wants.append(full[context - n_q:].reshape(n_q, heads * hd))
+        q_rows.append(q[context - n_q:].reshape(n_q, heads * hd))
+        starts.append(starts[-1] + n_q)
+        firsts.append(context - n_q)
+    q_all = np.concatenate(q_rows)
+    qkv = np.concatenate([q_all, np.full((q_all.shape[0], 2 * kv * hd), np.nan, dtype=np.float32)], axis=1)
+    rows_per_block = ops.attention_rows_per_block()
+    group = heads // kv
+    work_seq, work_row0 = [], []
+    for s, n_q in enumerate(queries):
+        for row0 in range(0, n_q * group, rows_per_block):
+            work_seq.append(s)
+            work_row0.append(row0)
+    out = ops.paged_attention_generic(
+        dev(qkv, torch_dtype), k_pool, v_pool, dev(np.stack(tables).astype(np.int32)),
+        dev(np.asarray(starts, dtype=np.int32)), dev(np.asarray(firsts, dtype=np.int32)),
+        dev(np.asarray(work_seq, dtype=np.int32)), dev(np.asarray(work_row0, dtype=np.int32)),
+        heads, kv, hd, page, window or 0, 1.0 / math.sqrt(hd))
+    return as_np(out), np.concatenate(wants)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv, hd, page", [(8, 1, 16, 1), (6, 2, 48, 4), (3, 3, 128, 16), (16, 2, 256, 8),
+                                                   (9, 3, 80, 5)])
+def test_paged_attention_generic(dtype, heads, kv, hd, page):
+    rng = np.random.default_rng(hd + page)
+    got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
+                                contexts=[300, 1, 65, 33, 128], queries=[1, 1, 65, 2, 17], dtype=dtype)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol(dtype, 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 32, 33, 100])
+def test_paged_attention_window_edges(dtype, window):
+    rng = np.random.default_rng(window)
+    got, want = _attention_case(rng, heads=4, kv=2, hd=32, page=8, window=window,
+                                contexts=[200, 64, 31], queries=[1, 64, 31], dtype=dtype)
+    assert np.abs(got - want).max() <= tol(dtype, 2)
+
+
+def test_attention_refuses_what_it_cannot_do():
+    from paged_kv_serving_b200 import ops
+
+    z = torch.zeros((1, 3 * 258), device="cuda")
+    pool = torch.zeros((1, 1, 1, 258), device="cuda")
+    i = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    one = torch.zeros((2,), dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError, match="limit"):
+        ops.paged_attention_generic(z, pool, pool, i, one, one[:1], one[:1], one[:1], 1, 1, 258, 1, 0, 1.0)
+    with pytest.raises(ValueError, match="size"):
+        ops.paged_attention_generic(z, pool, pool, i, one, one[:1], one[:1], one[:1], 3, 2, 6, 1, 0, 1.0)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.silu_mul(torch.zeros(2, 4), 60.0)
+
+
+def test_sampling_kernel_greedy_ties_and_distribution():
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(3)
+    vocab = 1237
+    logits = rng.standard_normal((6, vocab)).astype(np.float32) * 2
+    logits[0, [900, 17, 400]] = 9.0                       # a tie: the lowest id wins
+    logits[1, vocab - 1] = 50.0
+    temperature = np.array([0.0, 1e-6, 0.8, 1.3, 0.8, 0.5], dtype=np.float32)
+    top_p = np.array([1.0, 0.3, 1.0, 0.9, 0.35, 1.0], dtype=np.float32)
+    logits_d = dev(logits)
+    for trial in range(40):
+        u = rng.random(6)
+        ids = ops.sample(logits_d, dev(temperature), dev(top_p), dev(u), 1e-5).cpu().numpy()
+        assert ids[0] == 17 and ids[1] == vocab - 1
+        for row in range(2, 6):
+            want = plain_model.sample_token(logits[row], float(temperature[row]), float(top_p[row]), float(u[row]))
+            if ids[row] != want:
+                # allowed only when the draw sits on a boundary of the cumulative distribution
+                p = plain_model.sample_distribution(logits[row], float(temperature[row]), float(top_p[row]))
+                cum = np.cumsum(p, dtype=np.float64)
+                draw = u[row] * cum[-1]
+                assert min(abs(cum[ids[row]] - draw), abs(cum[want] - draw)) < 1e-6, (trial, row, ids[row], want)
+
+
+def test_sampling_kernel_nucleus_keeps_the_crossing_token_and_ties_by_id():
+    from paged_kv_serving_b200 import ops
+
+    vocab = 64
+    logits = np.full((2, vocab), -30.0, dtype=np.float32)
+    logits[0, [5, 9, 11, 40]] = np.log([0.4, 0.3, 0.2, 0.1]).astype(np.float32)
+    logits[1, :8] = 0.0                                     # eight equal tokens: ids 0..3 reach 0.5
+    temperature = np.array([1.0, 1.0], dtype=np.float32)
+    top_p = np.array([0.65, 0.5], dtype=np.float32)
+    seen = [set(), set()]
+    for u in np.linspace(0.0005, 0.9995, 200):
+        ids = ops.sample(dev(logits), dev(temperature), dev(top_p), dev(np.array([u, u])), 1e-5).cpu().numpy()
+        for row in range(2):
+            want = plain_model.sample_token(logits[row], 1.0, float(top_p[row]), float(u))
+            assert ids[row] == want
+            seen[row].add(int(ids[row]))
+    assert seen[0] == {5, 9} and seen[1] == {0, 1, 2, 3}
+
+
+def test_sampling_kernel_large_vocabulary():
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(5)
+    vocab = 128256
+    logits = (rng.standard_normal((3, vocab)) * 3).astype(np.float32)
+    temperature = np.array([0.0, 0.7, 0.7], dtype=np.float32)
+    top_p = np.array([1.0, 1.0, 0.8], dtype=np.float32)
+    u = np.array([0.0, 0.37, 0.93])
+    ids = ops.sample(dev(logits), dev(temperature), dev(top_p), dev(u), 1e-5).cpu().numpy()
+    assert ids[0] == int(np.argmax(logits[0]))
+    for row in (1, 2):
+        want = plain_model.sample_token(logits[row], 0.7, float(top_p[row]), float(u[row]))
+        if ids[row] != want:
+            p = plain_model.sample_distribution(logits[row], 0.7, float(top_p[row]))
+            cum = np.cumsum(p, dtype=np.float64)
+            assert min(abs(cum[ids[row]] - u[row] * cum[-1]), abs(cum[want] - u[row] * cum[-1])) < 1e-6
