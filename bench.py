@@ -1,0 +1,287 @@
+"""Measurement of the engine on one B200: decode and prefill throughput against the roofline.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of the Llama-3-8B shape (the third configuration of the
+baseline list) with random bfloat16 weights: 8 sequences, each with a 1,024-token random prompt
+in the cache, decode one token per step. A "step" is one decode step of the whole batch. One JSON
+line is printed with
+
+* ``value``      decoded tokens a second, timed on the device with CUDA events over K steps
+* ``e2e``        the same through the Python entry point (``Engine.step``): host token ids in,
+                 sampled ids out, with the host-to-device and device-to-host bytes of a step
+* ``prefill``    one 2,048-token prompt in one step: tokens a second, milliseconds and the
+                 fraction of the bfloat16 matrix peak its flops reach
+* ``roofline``   the bytes a decode step must read (every weight once, the cache of the live
+                 requests) over its time, against the measured copy bandwidth
+* ``points``     decode tokens a second at batch 1 and 64
+
+Peaks come from ``MEASURED_PEAKS.json`` beside this file when it exists, else from the fallback
+figures of this pool. Weights of a step (16 GB) are far larger than L2, so nothing is flushed
+between steps. With ``--gpus`` above 1 the program says that it measures one GPU only and exits 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "decode tok/s at batch 8, Llama-3-8B shape, 1024-token prompts"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            data = json.loads(path.read_text())
+            return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+        except (ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self) -> None:
+        self.process = None
+        self.samples: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> None:
+        if self.process is None:
+            return
+        self.process.terminate()
+        try:
+            out, _ = self.process.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+            out, _ = self.process.communicate()
+        self.samples += [line for line in out.splitlines() if line.strip()]
+        self.process = None
+
+    def summary(self) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        for line in self.samples:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(self.NAMES, parts[2:6]):
+                if value.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def scattered_tables(num_seqs: int, pages_per_seq: int) -> list[tuple[int, ...]]:
+    """Page tables that interleave the sequences' pages, so that no sequence is contiguous."""
+    return [tuple(j * num_seqs + i for j in range(pages_per_seq)) for i in range(num_seqs)]
+
+
+def run(args) -> dict:
+    import numpy as np
+    import torch
+
+    from paged_kv_serving_b200 import ops
+    from paged_kv_serving_b200.config import EngineConfig
+    from paged_kv_serving_b200.config.presets import PRESETS, preset
+    from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+    from paged_kv_serving_b200.engine.engine import Engine
+    from paged_kv_serving_b200.engine.runner import ModelRunner
+    from paged_kv_serving_b200.engine.sequence import Request, SamplingParams
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+    from paged_kv_serving_b200.sampling.sampler import Sampler
+
+    peaks = load_peaks()
+    full_layers = PRESETS[args.model]["n_layers"]
+    layers = args.layers or full_layers
+    config = preset(args.model, n_layers=layers)
+    torch.cuda.set_device(0)
+    model = DecoderModel.from_random(config, seed=0, dtype="bfloat16", device="cuda:0")
+    rng = np.random.default_rng(1)
+    prompt_len, block, batch = args.prompt_len, 16, args.batch
+    max_batch = max(batch, 64 if not args.skip_points else batch)
+    decode_room = args.warmup + args.steps + 8
+    pages_per_seq = -(-(prompt_len + 3 * decode_room) // block)
+    prefill_pages = -(-args.prefill_tokens // block)
+    runner = ModelRunner(model, num_blocks=max_batch * pages_per_seq + prefill_pages, block_size=block,
+                         max_running_seqs=max_batch)
+    sampler = Sampler(model.device)
+    tables = scattered_tables(max_batch, pages_per_seq)
+    prompts = rng.integers(0, config.vocab_size, size=(max_batch, prompt_len + 4 * decode_room))
+    greedy = SamplingParams(max_new_tokens=1)
+    clocks = ClockSampler()
+
+    def timed(fn, repeat: int) -> float:
+        """Milliseconds for ``repeat`` calls of fn(i), on the device."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(repeat):
+            fn(i)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop)
+
+    # ---- prefill: one 2,048-token prompt in one step, time to its last logits -----------------
+    prefill_table = tuple(range(max_batch * pages_per_seq, max_batch * pages_per_seq + prefill_pages))
+    prefill_ids = tuple(int(t) for t in rng.integers(0, config.vocab_size, size=args.prefill_tokens))
+    prefill_batch = ExecutionBatch((BatchEntry("prefill", prefill_ids, 0, (prefill_table,), (args.prefill_tokens - 1,)),))
+    for _ in range(3):
+        runner.step(prefill_batch)
+    clocks.start()
+    prefill_ms = timed(lambda i: runner.step(prefill_batch), 3) / 3
+    t = args.prefill_tokens
+    gemm_flops = 2.0 * t * layers * (config.d_model * (config.q_width + 2 * config.kv_width)
+                                     + config.q_width * config.d_model + 3 * config.d_model * config.d_ff)
+    gemm_flops += 2.0 * config.d_model * config.vocab_size
+    attention_flops = 4.0 * layers * config.n_heads * config.head_dim * (t * (t + 1) / 2)
+    prefill_flops = gemm_flops + attention_flops
+    prefill = {"value": t / (prefill_ms / 1e3), "tokens": t, "ms": prefill_ms,
+               "frac": prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+
+    # ---- fill the cache of every sequence (not timed) ------------------------------------------
+    per_step = max(1, 4096 // prompt_len)
+    for first in range(0, max_batch, per_step):
+        entries = tuple(BatchEntry(f"s{i}", tuple(int(x) for x in prompts[i, :prompt_len]), 0, (tables[i],), ())
+                        for i in range(first, min(max_batch, first + per_step)))
+        runner.step(ExecutionBatch(entries))
+    torch.cuda.synchronize()
+
+    # ---- decode, timed on the device ------------------------------------------------------------
+    weight_bytes = model.weight_bytes_read_per_step()
+    kv_bytes_per_token = sum(2 * len(g.entries) * g.n_kv_heads * g.head_dim * 2 for g in runner.groups)
+
+    def decode(num_seqs: int, warmup: int, steps: int, offset: int):
+        """``steps`` decode steps of the first ``num_seqs`` sequences; returns (ms, launches)."""
+        def one(k):
+            position = prompt_len + offset + k
+            entries = tuple(BatchEntry(f"s{i}", (int(prompts[i, position]),), position, (tables[i],), (0,))
+                            for i in range(num_seqs))
+            result = runner.step(ExecutionBatch(entries))
+            sampler.sample(result.logits, [greedy] * num_seqs, [None] * num_seqs)
+        for k in range(warmup):
+            one(k)
+        before = ops.launch_count()
+        ms = timed(lambda k: one(warmup + k), steps)
+        return ms, ops.launch_count() - before
+
+    points = {}
+    offset = 0
+    if not args.skip_points:
+        for name, size in (("decode_b1", 1), ("decode_b64", 64)):
+            ms, _ = decode(size, 3, min(args.steps, 32), offset)
+            offset += 3 + min(args.steps, 32)
+            points[name] = size * min(args.steps, 32) / (ms / 1e3)
+    decode_ms, launches = decode(batch, args.warmup, args.steps, offset)
+    offset += args.warmup + args.steps
+    ms_per_step = decode_ms / args.steps
+    value = batch * args.steps / (decode_ms / 1e3)
+    mean_context = prompt_len + offset - args.steps / 2
+    step_bytes = weight_bytes + batch * mean_context * kv_bytes_per_token
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"]}
+    del runner
+    torch.cuda.empty_cache()
+
+    # ---- end to end through the Python entry point ----------------------------------------------
+    new_tokens = args.warmup + args.steps + 4
+    engine = Engine(model, EngineConfig(
+        block_size=block, num_blocks=batch * (-(-(prompt_len + new_tokens) // block) + 1), max_batched_tokens=4096,
+        max_running_seqs=batch, max_prompt_tokens=prompt_len, max_new_tokens=new_tokens,
+        max_context_tokens=prompt_len + new_tokens, enable_prefix_cache=False, dtype="bfloat16", watermark=0.0))
+    for i in range(batch):
+        engine.submit(Request(f"e{i}", tuple(int(x) for x in prompts[i, :prompt_len]),
+                              SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)))
+    while any(not s.is_decoding for s in engine.live_sequences()):
+        engine.step()
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h2d = d2h = 0
+    started = time.perf_counter()
+    produced = 0
+    for _ in range(args.steps):
+        out = engine.step()
+        produced += len(out.tokens)
+        h2d += engine.h2d_bytes_last_step
+        d2h += engine.d2h_bytes_last_step
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - started
+    clocks.stop()
+    e2e = {"value": produced / elapsed, "unit": "tok/s", "h2d_bytes_per_step": h2d // args.steps,
+           "d2h_bytes_per_step": d2h // args.steps, "ms_per_step": 1e3 * elapsed / args.steps}
+
+    return {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform random token ids, random N(0, 0.02) weights", "impl": "ours",
+        "config": {
+            "model": f"{args.model}-shape", "n_layers": layers, "n_layers_full": full_layers, "d_model": config.d_model,
+            "n_heads": config.n_heads, "n_kv_heads": config.n_kv_heads, "head_dim": config.head_dim,
+            "d_ff": config.d_ff, "vocab_size": config.vocab_size, "global_batch": batch, "seq_len": prompt_len,
+            "kv_block_size": block, "prefill_tokens": args.prefill_tokens, "parallelism": "single-gpu",
+            "l2": "weights read each step (GBs) exceed L2; no flush", "peaks": peaks["source"],
+        },
+        "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
+        "clocks": clocks.summary(),
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--model", default="llama-3-8b")
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the preset (0: all)")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--prompt-len", type=int, default=1024)
+    parser.add_argument("--prefill-tokens", type=int, default=2048)
+    parser.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference does not install offline (its build backend uv_build is absent) and is a "
+                          "NumPy CPU engine whose ModelConfig cannot express the benchmark's grouped-query, untied "
+                          "8B configuration"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: this engine is single-GPU by design, --gpus {args.gpus} is not run")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    print(json.dumps(run(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

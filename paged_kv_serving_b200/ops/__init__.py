@@ -16,7 +16,7 @@ from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
     "add_rmsnorm", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather",
-    "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul",
+    "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul",
 ]
 
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
@@ -33,8 +33,17 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise TypeError(f"kernels take float32 or bfloat16 tensors, not {dtype}") from None
 
 
+#: Number of kernel launches issued through this module since import (or the last reset).
+LAUNCHES = {"count": 0}
+
+
+def launch_count() -> int:
+    return LAUNCHES["count"]
+
+
 def _check(status: int, what: str) -> None:
     if status == 0:
+        LAUNCHES["count"] += 1
         return
     if status < 0:
         raise ValueError(f"{what}: {_ERRORS.get(status, f'refused (code {status})')}")

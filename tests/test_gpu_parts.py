@@ -58,7 +58,9 @@ def test_rmsnorm_part_and_swiglu_part(dtype):
     x = rounded(rng.standard_normal((tokens, width)).astype(np.float32), dtype)
     got = ff.forward(dev(x, DTYPES[dtype]), None).float().cpu().numpy()
     want = plain_model.swiglu(x, gate, up, down)
-    assert np.abs(got - want).max() <= (1e-5 if dtype == "float32" else 3e-2 * np.abs(want).max() + 1e-3)
+    # bounds relative to the output's magnitude (sums of ~150 products): float32 rounding, or bfloat16's 2^-8
+    scale = float(np.abs(want).max())
+    assert np.abs(got - want).max() <= (2e-6 * scale + 1e-6 if dtype == "float32" else 3e-2 * scale + 1e-3)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -207,10 +209,10 @@ def test_toy_mixer_with_state_and_toy_position_encoding_register_build_and_step(
             helpers.assert_close(got[1:], want_b[20 + i - 35:21 + i - 35], "float32", f"toy decode b {i}")
     held = [page for page in session.live["a"].block_table if page >= 0]
     assert len(held) <= 16 // 4 + 2, "pages behind the window must have been given back"
-    session.step([], end=["a", "b"]) if False else [session.cache.free(s) for s in session.live.values()]
+    session.step([], end=["a", "b"])
     session.check_invariants()
+    assert session.cache.num_free_blocks == session.num_blocks and session.cache.state_slots.num_free == 64
     # a slot that is taken again starts from a cleared state
-    session.live.clear()
     got = session.step([{"id": "c", "tokens": b[:20], "want": [19]}])
     helpers.assert_close(got, want_b[19:20], "float32", "toy reused slot")
 
