@@ -15,7 +15,8 @@ import torch
 from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
-    "add_rmsnorm", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather",
+    "add_rmsnorm", "attention_bf16_rows", "attention_bf16_supports", "attention_decode_bf16",
+    "attention_prefill_bf16", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather",
     "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul",
 ]
 
@@ -181,6 +182,69 @@ def paged_attention_generic(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
               _ptr(work_seq), _ptr(work_row0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window),
               float(scale), _stream()), "paged_attention_generic")
     return out
+
+
+def attention_bf16_supports(head_dim: int, q_row_stride: int) -> bool:
+    """Whether the tensor-core bfloat16 attention kernels take this head size and row stride."""
+    lib = library("attention_bf16")
+    lib.pkv_attention_bf16_supports.restype = c_int
+    lib.pkv_attention_bf16_supports.argtypes = [c_int, c_int]
+    return bool(lib.pkv_attention_bf16_supports(int(head_dim), int(q_row_stride)))
+
+
+def attention_bf16_rows() -> tuple[int, int]:
+    """``(query rows per prefill block, most rows of a decode entry per key/value head)``."""
+    lib = library("attention_bf16")
+    lib.pkv_attention_bf16_rows.restype = c_int
+    lib.pkv_attention_bf16_rows.argtypes = [c_int]
+    return int(lib.pkv_attention_bf16_rows(0)), int(lib.pkv_attention_bf16_rows(1))
+
+
+def attention_prefill_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                           block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
+                           work_seq: torch.Tensor, work_q0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                           page_size: int, window: int, scale: float) -> None:
+    """Tensor-core attention for runs of queries; writes the rows of its work items into ``out``."""
+    for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("work_q0", work_q0)):
+        _need(t, torch.int32, name)
+    fn = _fn("attention_bf16", "pkv_attention_prefill_bf16",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+              block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_q0),
+              work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), float(scale), _stream()),
+           "attention_prefill_bf16")
+
+
+def attention_decode_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                          block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
+                          work_seq: torch.Tensor, max_entry_tokens: int, n_heads: int, n_kv: int, head_dim: int,
+                          page_size: int, window: int, scale: float, num_splits: int,
+                          scratch: torch.Tensor | None) -> None:
+    """Split-KV tensor-core attention for entries of a few rows. With ``num_splits > 1`` the
+    partial results pass through ``scratch`` (float32, ``T * H * num_splits * (hd + 2)`` values)."""
+    for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq)):
+        _need(t, torch.int32, name)
+    total_rows = qkv.shape[0] * n_heads
+    if num_splits > 1:
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < total_rows * num_splits * (head_dim + 2):
+            raise ValueError("attention scratch is too small for this many splits")
+    fn = _fn("attention_bf16", "pkv_attention_decode_bf16",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+              block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), work_seq.numel(),
+              int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(num_splits),
+              _ptr(scratch), total_rows, _stream()), "attention_decode_bf16")
+    if num_splits > 1:
+        LAUNCHES["count"] += 1   # the merge kernel
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,

@@ -15,6 +15,15 @@ from paged_kv_serving_b200.parts.position import PositionEncoding
 
 __all__ = ["PagedAttention"]
 
+_SM_COUNT: dict[str, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    key = str(device)
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[key]
+
 
 @register_part("mixer", "attention")
 class PagedAttention(Part):
@@ -47,6 +56,7 @@ class PagedAttention(Part):
         self.window = window
         self.qkv_proj: torch.Tensor | None = None
         self.out_proj: torch.Tensor | None = None
+        self._fast_ok: bool | None = None
 
     @property
     def group_size(self) -> int:
@@ -67,7 +77,54 @@ class PagedAttention(Part):
     def _work_names(self) -> tuple[str, str]:
         return (f"attention/work_seq/g{self.group_size}", f"attention/work_row0/g{self.group_size}")
 
+    def _fast(self, ctx: StepContext) -> bool:
+        """Whether the tensor-core bfloat16 kernels serve this mixer in this step."""
+        if ctx.dtype != torch.bfloat16:
+            return False
+        if self._fast_ok is None:
+            qkv_width = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+            self._fast_ok = ops.attention_bf16_supports(self.head_dim, qkv_width)
+        return self._fast_ok
+
+    def _plan_fast(self, ctx: StepContext) -> None:
+        """Work lists of the bfloat16 kernels: entries of at most 16 rows per key/value head go
+        to the split-KV decode kernel, longer ones are cut into blocks of 64 queries for the
+        prefill kernel (heaviest blocks first)."""
+        key = f"attention/fast/g{self.group_size}"
+        if key in ctx.scratch:
+            return
+        block_rows, decode_rows = ops.attention_bf16_rows()
+        lens = np.asarray(ctx.seq_lens, dtype=np.int64)
+        first = np.asarray(ctx.first_positions, dtype=np.int64)
+        small = lens * self.group_size <= decode_rows
+        decode_entries = np.nonzero(small)[0]
+        large = np.nonzero(~small)[0]
+        blocks = (lens[large] + block_rows - 1) // block_rows
+        work_seq = np.repeat(large, blocks)
+        starts = np.cumsum(blocks) - blocks
+        work_q0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * block_rows
+        cost = first[work_seq] + work_q0
+        order = np.argsort(-cost, kind="stable")
+        num_splits = 1
+        if len(decode_entries):
+            longest = int((first[decode_entries] + lens[decode_entries]).max())
+            tiles = max(1, -(-longest // 64))
+            blocks_per_split = len(decode_entries) * self.n_kv_heads
+            num_splits = int(min(tiles, 32, max(1, -(-2 * _sm_count(ctx.device) // blocks_per_split))))
+        names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq")}
+        ctx.arena.add(names["prefill_seq"], work_seq[order] if len(order) else [0])
+        ctx.arena.add(names["prefill_q0"], work_q0[order] if len(order) else [0])
+        ctx.arena.add(names["decode_seq"], decode_entries if len(decode_entries) else [0])
+        ctx.scratch[key] = {
+            "names": names, "n_prefill": int(len(order)), "n_decode": int(len(decode_entries)),
+            "max_small_tokens": int(lens[decode_entries].max()) if len(decode_entries) else 0,
+            "num_splits": num_splits,
+        }
+
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        if self._fast(ctx):
+            self._plan_fast(ctx)
+            return
         seq_name, row_name = self._work_names()
         if seq_name in ctx.arena:
             return
@@ -95,9 +152,35 @@ class PagedAttention(Part):
         slots = ctx.ints(group.slots_name) if binding.write else None
         ops.rope_kv_store(qkv, positions, cos, sin, k_pool, v_pool, slots,
                           self.n_heads, self.n_kv_heads, self.head_dim, group.page_size)
+        if self._fast(ctx):
+            attended = self._attend_fast(qkv, ctx, group, k_pool, v_pool)
+            return gemm.matmul(attended, self.out_proj)
         seq_name, row_name = self._work_names()
         attended = ops.paged_attention_generic(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.head_dim,
             group.page_size, self.window or 0, self.scale)
         return gemm.matmul(attended, self.out_proj)
+
+    def _attend_fast(self, qkv, ctx: StepContext, group, k_pool, v_pool) -> torch.Tensor:
+        plan = ctx.scratch[f"attention/fast/g{self.group_size}"]
+        names = plan["names"]
+        out = torch.empty((qkv.shape[0], self.n_heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
+        table, starts, first = ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS)
+        if plan["n_prefill"]:
+            ops.attention_prefill_bf16(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["prefill_seq"]),
+                                       ctx.ints(names["prefill_q0"]), self.n_heads, self.n_kv_heads, self.head_dim,
+                                       group.page_size, self.window or 0, self.scale)
+        if plan["n_decode"]:
+            splits = plan["num_splits"]
+            scratch = None
+            if splits > 1:
+                size = qkv.shape[0] * self.n_heads * splits * (self.head_dim + 2)
+                scratch = ctx.scratch.get("attention/split_scratch")
+                if scratch is None or scratch.numel() < size:
+                    scratch = torch.empty((size,), dtype=torch.float32, device=qkv.device)
+                    ctx.scratch["attention/split_scratch"] = scratch
+            ops.attention_decode_bf16(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["decode_seq"]),
+                                      plan["max_small_tokens"], self.n_heads, self.n_kv_heads, self.head_dim,
+                                      group.page_size, self.window or 0, self.scale, splits, scratch)
+        return out

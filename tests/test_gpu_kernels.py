@@ -136,7 +136,7 @@ def test_rope_kv_store(dtype):
     assert np.array_equal(as_np(k_pool)[p, :, o], k[0])
 
 
-def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True):
+def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True, fast=False, splits=1):
     """Random sequences already in the cache (``contexts`` tokens each), of which the last
     ``queries`` tokens are this step's queries. Returns device inputs and the plain answer."""
     from paged_kv_serving_b200 import ops
@@ -177,8 +177,27 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
         firsts.append(context - n_q)
     q_all = np.concatenate(q_rows)
     qkv = np.concatenate([q_all, np.full((q_all.shape[0], 2 * kv * hd), np.nan, dtype=np.float32)], axis=1)
-    rows_per_block = ops.attention_rows_per_block()
     group = heads // kv
+    if fast:
+        block_rows, decode_rows = ops.attention_bf16_rows()
+        out = torch.full((q_all.shape[0], heads * hd), float("nan"), dtype=torch_dtype, device="cuda")
+        small = [s for s, n_q in enumerate(queries) if n_q * group <= decode_rows]
+        large = [(s, q0) for s, n_q in enumerate(queries) if n_q * group > decode_rows for q0 in range(0, n_q, block_rows)]
+        common = (dev(np.stack(tables).astype(np.int32)), dev(np.asarray(starts, dtype=np.int32)),
+                  dev(np.asarray(firsts, dtype=np.int32)))
+        qkv_d = dev(qkv, torch_dtype)
+        if large:
+            ops.attention_prefill_bf16(qkv_d, out, k_pool, v_pool, *common,
+                                       dev(np.asarray([s for s, _ in large], dtype=np.int32)),
+                                       dev(np.asarray([q for _, q in large], dtype=np.int32)),
+                                       heads, kv, hd, page, window or 0, 1.0 / math.sqrt(hd))
+        if small:
+            scratch = torch.full((q_all.shape[0] * heads * splits * (hd + 2),), float("nan"), device="cuda")
+            ops.attention_decode_bf16(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
+                                      max(queries[s] for s in small), heads, kv, hd, page, window or 0,
+                                      1.0 / math.sqrt(hd), splits, scratch if splits > 1 else None)
+        return as_np(out), np.concatenate(wants)
+    rows_per_block = ops.attention_rows_per_block()
     work_seq, work_row0 = [], []
     for s, n_q in enumerate(queries):
         for row0 in range(0, n_q * group, rows_per_block):
@@ -212,6 +231,32 @@ def test_paged_attention_window_edges(dtype, window):
     assert np.abs(got - want).max() <= tol(dtype, 2)
 
 
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("heads, kv, hd, page", [(8, 1, 16, 1), (6, 2, 48, 4), (3, 3, 128, 16), (32, 8, 128, 16),
+                                                   (16, 2, 64, 8), (9, 3, 80, 5), (4, 4, 112, 3), (8, 4, 32, 16),
+                                                   (10, 2, 96, 7)])
+def test_attention_bf16_tensor_core_kernels(heads, kv, hd, page, splits):
+    """The prefill kernel (long runs of queries, block edges at 64 and 65 queries, a run that
+    starts deep inside the context) and the split-KV decode kernel (one to a few queries) in
+    one ragged batch, against the plain implementation."""
+    rng = np.random.default_rng(hd * page + splits)
+    got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
+                                contexts=[300, 1, 65, 33, 128, 200, 64, 513], queries=[1, 1, 65, 2, 17, 150, 64, 1],
+                                dtype="bfloat16", fast=True, splits=splits)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("window", [1, 7, 63, 64, 65, 100])
+def test_attention_bf16_tensor_core_kernels_window_edges(window):
+    rng = np.random.default_rng(window)
+    got, want = _attention_case(rng, heads=4, kv=2, hd=32, page=8, window=window,
+                                contexts=[200, 64, 31, 140, 300], queries=[1, 64, 31, 3, 130],
+                                dtype="bfloat16", fast=True, splits=2)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
 def test_attention_refuses_what_it_cannot_do():
     from paged_kv_serving_b200 import ops
 
@@ -225,6 +270,13 @@ def test_attention_refuses_what_it_cannot_do():
         ops.paged_attention_generic(z, pool, pool, i, one, one[:1], one[:1], one[:1], 3, 2, 6, 1, 0, 1.0)
     with pytest.raises(ValueError, match="CUDA tensor"):
         ops.silu_mul(torch.zeros(2, 4), 60.0)
+    assert not ops.attention_bf16_supports(24, 72) and not ops.attention_bf16_supports(256, 768)
+    assert ops.attention_bf16_supports(48, 144)
+    b = torch.zeros((1, 3 * 24), dtype=torch.bfloat16, device="cuda")
+    pool_b = torch.zeros((1, 1, 1, 24), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="limit"):
+        ops.attention_prefill_bf16(b, b[:, :24].contiguous(), pool_b, pool_b, i, one, one[:1], one[:1], one[:1],
+                                   1, 1, 24, 1, 0, 1.0)
 
 
 def test_sampling_kernel_greedy_ties_and_distribution():
