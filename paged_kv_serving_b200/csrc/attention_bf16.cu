@@ -29,6 +29,7 @@ constexpr int AT_BN = 64;       // keys per tile
 constexpr int AT_THREADS = 128;
 constexpr int AT_PAD = 8;       // bf16 elements of padding per shared-memory row (16 bytes)
 constexpr int DEC_ROWS = 16;    // rows of one decode entry per key/value head
+constexpr int PAGE_CACHE = 2048; // block-table entries a block keeps in shared memory
 
 struct AttnParams {
   const bf16* qkv;              // [T, q_row_stride]; queries of head h at column h * HD
@@ -42,7 +43,7 @@ struct AttnParams {
   const int32_t* first_pos;     // [S] absolute position of each entry's first token
   const int32_t* work_a;        // prefill: entry of each work item; decode: entry of each item
   const int32_t* work_b;        // prefill: first query (inside the entry) of each work item
-  int n_heads, n_kv, page_size, window;
+  int n_heads, n_kv, page_size, page_shift, window;   // page_shift: log2(page_size), or -1
   float scale_log2;             // scale * log2(e)
   int num_splits;               // decode only
   float* part_o;                // decode scratch [T*H, splits, HD]
@@ -77,19 +78,47 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // Load `rows` keys (or values) starting at absolute position `base` into a padded tile.
 // Positions outside [lo, hi) and positions whose page was given back are zero-filled.
+// The block-table entries of a block's key range, copied to shared memory once: a lookup per
+// 16-byte copy from global memory would put a memory latency in front of every copy.
+struct PageLookup {
+  const int32_t* table;      // the entry's block table in global memory
+  const int32_t* cached;     // shared-memory copy of entries [first, first + count), or null
+  int first;
+  int page_size, page_shift;
+  __device__ __forceinline__ int entry_of(int pos) const { return page_shift >= 0 ? pos >> page_shift : pos / page_size; }
+  __device__ __forceinline__ int page_of(int pos, int& offset) const {
+    const int e = entry_of(pos);
+    offset = pos - e * page_size;
+    return cached ? cached[e - first] : table[e];
+  }
+};
+
+__device__ __forceinline__ PageLookup make_page_lookup(int32_t* cache, const int32_t* table, int lo, int hi,
+                                                       int page_size, int page_shift) {
+  PageLookup look{table, nullptr, 0, page_size, page_shift};
+  if (hi <= lo) return look;
+  const int first = look.entry_of(lo), count = look.entry_of(hi - 1) - first + 1;
+  if (count <= PAGE_CACHE) {
+    for (int i = threadIdx.x; i < count; i += AT_THREADS) cache[i] = table[first + i];
+    look.cached = cache;
+    look.first = first;
+  }
+  return look;   // the caller synchronises the block before the first lookup
+}
+
 template <int HD>
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* pool, const int32_t* table, int base, int lo,
-                                             int hi, int kvh, int n_kv, int page_size) {
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* pool, const PageLookup& look, int base, int lo,
+                                             int hi, int kvh, int n_kv) {
   constexpr int LD = HD + AT_PAD;
   constexpr int CHUNKS = HD / 8;
   for (int idx = threadIdx.x; idx < AT_BN * CHUNKS; idx += AT_THREADS) {
     const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
     const int pos = base + row;
     bf16* dst = tile + row * LD + chunk * 8;
-    int page = -1;
-    if (pos >= lo && pos < hi) page = table[pos / page_size];
+    int page = -1, offset = 0;
+    if (pos >= lo && pos < hi) page = look.page_of(pos, offset);
     if (page >= 0) {
-      const size_t at = (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * HD + chunk * 8;
+      const size_t at = (((size_t)page * n_kv + kvh) * look.page_size + offset) * HD + chunk * 8;
       cp_async16(dst, pool + at);
     } else {
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
@@ -124,7 +153,9 @@ __global__ void __launch_bounds__(AT_THREADS) attention_prefill_kernel(const Att
   const int key_hi = qpos_first + rows_valid;                                   // exclusive
   const int key_lo = p.window > 0 ? max(0, qpos_first - p.window + 1) : 0;
   const int tile_begin = key_lo / AT_BN, tile_end = (key_hi - 1) / AT_BN;       // inclusive
-  const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+  __shared__ int32_t page_cache[PAGE_CACHE];
+  const PageLookup look = make_page_lookup(page_cache, p.block_table + (size_t)s * p.table_stride, key_lo, key_hi,
+                                           p.page_size, p.page_shift);
 
   // queries of this block
   for (int idx = threadIdx.x; idx < AT_BM * (HD / 8); idx += AT_THREADS) {
@@ -135,8 +166,9 @@ __global__ void __launch_bounds__(AT_THREADS) attention_prefill_kernel(const Att
     else
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
   }
-  load_kv_tile<HD>(k_s, p.k_pool, table, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
-  load_kv_tile<HD>(v_s, p.v_pool, table, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
+  __syncthreads();   // the page cache is filled
+  load_kv_tile<HD>(k_s, p.k_pool, look, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv);
+  load_kv_tile<HD>(v_s, p.v_pool, look, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv);
   cp_async_commit();
 
   // rows of this thread: warp*16 + g and + 8
@@ -155,8 +187,8 @@ __global__ void __launch_bounds__(AT_THREADS) attention_prefill_kernel(const Att
     const int stage = (tile - tile_begin) & 1;
     const int base = tile * AT_BN;
     if (tile < tile_end) {
-      load_kv_tile<HD>(k_s + (stage ^ 1) * AT_BN * LD, p.k_pool, table, base + AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
-      load_kv_tile<HD>(v_s + (stage ^ 1) * AT_BN * LD, p.v_pool, table, base + AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
+      load_kv_tile<HD>(k_s + (stage ^ 1) * AT_BN * LD, p.k_pool, look, base + AT_BN, key_lo, key_hi, kvh, p.n_kv);
+      load_kv_tile<HD>(v_s + (stage ^ 1) * AT_BN * LD, p.v_pool, look, base + AT_BN, key_lo, key_hi, kvh, p.n_kv);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -293,7 +325,10 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
   const int tiles_per_split = (tile_last - tile_first + p.num_splits) / p.num_splits;
   const int tile_begin = tile_first + split * tiles_per_split;
   const int tile_end = min(tile_last, tile_begin + tiles_per_split - 1);
-  const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+  __shared__ int32_t page_cache[PAGE_CACHE];
+  const PageLookup look = make_page_lookup(page_cache, p.block_table + (size_t)s * p.table_stride,
+                                           max(key_lo, tile_begin * AT_BN), min(key_hi, (tile_end + 1) * AT_BN),
+                                           p.page_size, p.page_shift);
 
   for (int idx = threadIdx.x; idx < DEC_ROWS * (HD / 8); idx += AT_THREADS) {
     const int row = idx / (HD / 8), chunk = idx - row * (HD / 8);
@@ -305,9 +340,10 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
+  __syncthreads();   // the page cache is filled
   if (tile_begin <= tile_end) {
-    load_kv_tile<HD>(k_s, p.k_pool, table, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
-    load_kv_tile<HD>(v_s, p.v_pool, table, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
+    load_kv_tile<HD>(k_s, p.k_pool, look, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv);
+    load_kv_tile<HD>(v_s, p.v_pool, look, tile_begin * AT_BN, key_lo, key_hi, kvh, p.n_kv);
   }
   cp_async_commit();
 
@@ -322,8 +358,8 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     const int stage = (tile - tile_begin) & 1;
     const int base = tile * AT_BN;
     if (tile < tile_end) {
-      load_kv_tile<HD>(k_s + (stage ^ 1) * AT_BN * LD, p.k_pool, table, base + AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
-      load_kv_tile<HD>(v_s + (stage ^ 1) * AT_BN * LD, p.v_pool, table, base + AT_BN, key_lo, key_hi, kvh, p.n_kv, p.page_size);
+      load_kv_tile<HD>(k_s + (stage ^ 1) * AT_BN * LD, p.k_pool, look, base + AT_BN, key_lo, key_hi, kvh, p.n_kv);
+      load_kv_tile<HD>(v_s + (stage ^ 1) * AT_BN * LD, p.v_pool, look, base + AT_BN, key_lo, key_hi, kvh, p.n_kv);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -465,7 +501,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 template <int HD>
 static int launch_prefill(const AttnParams& p, int n_work, cudaStream_t s) {
   const size_t smem = (size_t)(AT_BM + 4 * AT_BN) * (HD + AT_PAD) * sizeof(bf16);
-  if (smem > 48 * 1024) {
+  if (smem + (PAGE_CACHE + 256) * sizeof(int32_t) > 48 * 1024) {   // static shared memory counts toward the limit
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -476,7 +512,7 @@ static int launch_prefill(const AttnParams& p, int n_work, cudaStream_t s) {
 template <int HD>
 static int launch_decode(const AttnParams& p, int n_work, cudaStream_t s) {
   const size_t smem = (size_t)(DEC_ROWS + 4 * AT_BN) * (HD + AT_PAD) * sizeof(bf16);
-  if (smem > 48 * 1024) {
+  if (smem + (PAGE_CACHE + 256) * sizeof(int32_t) > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -500,6 +536,12 @@ using namespace pkv;
     case 128: CALL(128); break;          \
     default: return PKV_ERR_LIMIT;       \
   }
+
+static int log2_or_minus1(int v) {
+  for (int s = 0; s < 31; ++s)
+    if ((1 << s) == v) return s;
+  return -1;
+}
 
 static int check_common(int n_heads, int n_kv, int hd, int page_size, int window, int q_row_stride) {
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0 || window < 0) return PKV_ERR_SIZE;
@@ -525,7 +567,7 @@ PKV_EXPORT int pkv_attention_prefill_bf16(const void* qkv, int q_row_stride, voi
   const int bad = check_common(n_heads, n_kv, hd, page_size, window, q_row_stride);
   if (bad) return bad;
   AttnParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-               table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size, window,
+               table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size, log2_or_minus1(page_size), window,
                scale * 1.4426950408889634f, 1, nullptr, nullptr};
   cudaStream_t s = (cudaStream_t)stream;
 #define CALL(HD) return launch_prefill<HD>(p, n_work, s)
@@ -554,7 +596,7 @@ PKV_EXPORT int pkv_attention_decode_bf16(const void* qkv, int q_row_stride, void
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)total_rows * num_splits * hd : nullptr;
   AttnParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-               table_stride, seq_starts, first_pos, work_seq, nullptr, n_heads, n_kv, page_size, window,
+               table_stride, seq_starts, first_pos, work_seq, nullptr, n_heads, n_kv, page_size, log2_or_minus1(page_size), window,
                scale * 1.4426950408889634f, num_splits, part_o, part_ml};
   cudaStream_t s = (cudaStream_t)stream;
   int status = 0;

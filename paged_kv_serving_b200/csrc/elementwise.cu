@@ -63,9 +63,93 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const D* __restri
   }
 }
 
+// The same, for widths that are multiples of 4 and at most 4 * VEC_PER_THREAD * blockDim: every
+// thread keeps its part of the row in registers (one pass over memory, 16-byte accesses).
+constexpr int NORM_VEC_PER_THREAD = 4;
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+  return make_float4(fa.x, fa.y, fb.x, fb.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename D, typename O>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const D* __restrict__ delta,
+                                       const float* __restrict__ weight, float eps, O* __restrict__ out,
+                                       const int32_t* __restrict__ rows, int d) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* h = hidden + (size_t)src * d;
+  const D* dl = delta ? delta + (size_t)src * d : nullptr;
+  const int chunks = d >> 2;
+  float4 x[NORM_VEC_PER_THREAD];
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NORM_VEC_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      float4 v = load4(h + 4 * c);
+      if (dl) {
+        const float4 e = load4(dl + 4 * c);
+        v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+        if (!rows) store4(h + 4 * c, v);
+      }
+      x[i] = v;
+      sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  }
+  const float total = block_sum(sq, scratch);
+  const float root = sqrtf(total / (float)d + eps);
+  O* o = out + (size_t)r * d;
+#pragma unroll
+  for (int i = 0; i < NORM_VEC_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      const float4 w = load4(weight + 4 * c);
+      store4(o + 4 * c, make_float4((x[i].x / root) * w.x, (x[i].y / root) * w.y, (x[i].z / root) * w.z,
+                                    (x[i].w / root) * w.w));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // SiLU(gate) * up over a fused [T, 2*ff] input (gate columns first), output [T, ff]
 // ---------------------------------------------------------------------------------------------
+// ff a multiple of 8 (bfloat16) or 4 (float32): 16-byte accesses, one flat grid over all chunks
+template <typename A, int V>
+__global__ void silu_mul_vec_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, long long n_chunks,
+                                    float clip) {
+  const int chunks_per_row = ff / V;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
+    const long long t = c / chunks_per_row;
+    const int i = (int)(c - t * chunks_per_row) * V;
+    const A* g = gate_up + t * 2 * ff + i;
+    A* o = out + t * ff + i;
+#pragma unroll
+    for (int q = 0; q < V; q += 4) {
+      const float4 gv = load4(g + q), uv = load4(g + ff + q);
+      float4 r;
+      r.x = gv.x * (1.0f / (1.0f + expf(-fminf(fmaxf(gv.x, -clip), clip)))) * uv.x;
+      r.y = gv.y * (1.0f / (1.0f + expf(-fminf(fmaxf(gv.y, -clip), clip)))) * uv.y;
+      r.z = gv.z * (1.0f / (1.0f + expf(-fminf(fmaxf(gv.z, -clip), clip)))) * uv.z;
+      r.w = gv.w * (1.0f / (1.0f + expf(-fminf(fmaxf(gv.w, -clip), clip)))) * uv.w;
+      store4(o + q, r);
+    }
+  }
+}
+
 template <typename A>
 __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, float clip) {
   const int t = blockIdx.y;
@@ -135,6 +219,54 @@ __global__ void rope_kv_store_kernel(A* __restrict__ qkv, const int32_t* __restr
   }
 }
 
+// The same for head sizes that are multiples of 8: one block per token, every thread rotates 4
+// pairs (left[j..j+3], right[j..j+3]) or copies 4 values of v, with 8- or 16-byte accesses.
+template <typename A, typename C>
+__global__ void rope_kv_store_vec_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         C* __restrict__ k_pool, C* __restrict__ v_pool,
+                                         const int32_t* __restrict__ slots, int n_heads, int n_kv, int hd,
+                                         int page_size, int store) {
+  const int t = blockIdx.x;
+  const int half = hd >> 1;
+  const int quads = half >> 2;                       // groups of 4 pairs per head
+  const int pos = positions[t];
+  const int slot = store ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+  A* row = qkv + (size_t)t * (n_heads + 2 * n_kv) * hd;
+  const int rot_tasks = (n_heads + n_kv) * quads;
+  const int copy_tasks = slot >= 0 ? n_kv * (hd >> 2) : 0;
+  for (int task = threadIdx.x; task < rot_tasks + copy_tasks; task += blockDim.x) {
+    if (task < rot_tasks) {
+      const int head = task / quads, j = (task - head * quads) * 4;
+      const bool is_q = head < n_heads;
+      if (!is_q && slot < 0) continue;
+      A* hp = row + (size_t)head * hd;
+      float4 left = load4(hp + j), right = load4(hp + half + j);
+      float4 lo = left, hi = right;
+      if (cos_t) {
+        const float4 c = load4(cos_t + (size_t)pos * half + j), s = load4(sin_t + (size_t)pos * half + j);
+        lo = make_float4(left.x * c.x - right.x * s.x, left.y * c.y - right.y * s.y, left.z * c.z - right.z * s.z,
+                         left.w * c.w - right.w * s.w);
+        hi = make_float4(right.x * c.x + left.x * s.x, right.y * c.y + left.y * s.y, right.z * c.z + left.z * s.z,
+                         right.w * c.w + left.w * s.w);
+      }
+      if (is_q) {
+        if (cos_t) { store4(hp + j, lo); store4(hp + half + j, hi); }
+      } else {
+        C* dst = k_pool + (((size_t)page * n_kv + (head - n_heads)) * page_size + off) * hd;
+        store4(dst + j, lo);
+        store4(dst + half + j, hi);
+      }
+    } else {
+      const int c = task - rot_tasks;
+      const int kvh = c / (hd >> 2), j = (c - kvh * (hd >> 2)) * 4;
+      const float4 v = load4(row + (size_t)(n_heads + n_kv + kvh) * hd + j);
+      store4(v_pool + (((size_t)page * n_kv + kvh) * page_size + off) * hd + j, v);
+    }
+  }
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -157,6 +289,14 @@ PKV_EXPORT int pkv_embedding_gather(const void* table, int table_dtype, const in
 template <typename D, typename O>
 static int launch_add_rmsnorm(float* hidden, const void* delta, const float* weight, float eps, void* out,
                               const int32_t* rows, int n_rows, int d, cudaStream_t s) {
+  if (d % 4 == 0 && d <= 4 * NORM_VEC_PER_THREAD * 1024) {
+    const int chunks = d / 4;
+    int threads = ((chunks + 1) / 2 + 31) / 32 * 32;           // two chunks a thread where that fits
+    if (threads < 64) threads = 64;
+    if (threads > 1024) threads = 1024;
+    add_rmsnorm_vec_kernel<D, O><<<n_rows, threads, 0, s>>>(hidden, (const D*)delta, weight, eps, (O*)out, rows, d);
+    return launch_status();
+  }
   const size_t smem = (size_t)(d + 32) * sizeof(float);
   if (smem > 200 * 1024) return PKV_ERR_LIMIT;
   if (smem > 48 * 1024) {
@@ -189,6 +329,17 @@ PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tok
   if (n_tokens <= 0) return 0;
   if (ff <= 0) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
+  if ((dtype == PKV_BF16 && ff % 8 == 0) || (dtype == PKV_F32 && ff % 4 == 0)) {
+    const int v = dtype == PKV_BF16 ? 8 : 4;
+    const long long n_chunks = (long long)n_tokens * (ff / v);
+    long long blocks = (n_chunks + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == PKV_BF16)
+      silu_mul_vec_kernel<bf16, 8><<<(int)blocks, 256, 0, s>>>((const bf16*)gate_up, (bf16*)out, ff, n_chunks, clip);
+    else
+      silu_mul_vec_kernel<float, 4><<<(int)blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, ff, n_chunks, clip);
+    return launch_status();
+  }
   const int threads = 256;
   int bx = (ff + threads - 1) / threads;
   if (bx > 64) bx = 64;
@@ -214,6 +365,20 @@ PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positi
   if (n_heads <= 0 || n_kv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0) return PKV_ERR_SIZE;
   if (n_heads + 2 * n_kv > 65535) return PKV_ERR_LIMIT;
   cudaStream_t s = (cudaStream_t)stream;
+  if (hd % 8 == 0) {
+    const int tasks = (n_heads + n_kv) * (hd / 8) + n_kv * (hd / 4);
+    int vthreads = (tasks + 31) / 32 * 32;
+    if (vthreads > 512) vthreads = 512;
+#define PKV_ROPE_VEC(A, C) \
+  rope_kv_store_vec_kernel<A, C><<<n_tokens, vthreads, 0, s>>>((A*)qkv, positions, cos_t, sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
+    if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_ROPE_VEC(float, float);
+    else if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(bf16, bf16);
+    else if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(float, bf16);
+    else if (act_dtype == PKV_BF16 && cache_dtype == PKV_F32) PKV_ROPE_VEC(bf16, float);
+    else return PKV_ERR_DTYPE;
+#undef PKV_ROPE_VEC
+    return launch_status();
+  }
   int threads = ((hd / 2 + 31) / 32) * 32;
   if (threads > 256) threads = 256;
   dim3 grid(n_tokens, n_heads + 2 * n_kv);

@@ -113,7 +113,8 @@ class StepResult:
 class ModelRunner:
     """Owns the cache storage of one model and runs ragged batches against it."""
 
-    def __init__(self, model: DecoderModel, *, num_blocks: int, block_size: int, max_running_seqs: int = 64) -> None:
+    def __init__(self, model: DecoderModel, *, num_blocks: int, block_size: int, max_running_seqs: int = 64,
+                 use_graphs: bool = True) -> None:
         if num_blocks < 1 or block_size < 1:
             raise ValueError("num_blocks and block_size must be >= 1")
         if not torch.cuda.is_available():
@@ -137,6 +138,10 @@ class ModelRunner:
                 self.bindings.append(CacheBinding(call.cache, state=self.storage.state_index[call.cache], write=call.write))
         self._status = torch.zeros((1,), dtype=torch.int32, device=model.device)
         self.steps_run = 0
+        self.use_graphs = use_graphs
+        self._graph_safe = all(block.graph_safe for block in model.layout.blocks) and model.layout.final_norm.graph_safe
+        self._graphs: dict[tuple[int, int], dict] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if use_graphs else None
 
     # --- storage behind the cache manager -------------------------------------------------
 
@@ -185,8 +190,15 @@ class ModelRunner:
             if self.state_entries and entry.state_slot is None:
                 raise ValueError(f"sequence {entry.seq_id}: the model keeps per-request state but no slot was given")
 
-    def _context(self, batch: ExecutionBatch) -> tuple[StepContext, list[tuple[str, int]]]:
+    def _context(self, batch: ExecutionBatch, table_width: int | None = None,
+                 pad_to: int | None = None) -> tuple[StepContext, list[tuple[str, int]]]:
+        """Flatten a batch into the step's integer arrays. ``pad_to`` appends stand-in entries of
+        one token (no page, no store, token 0) up to that many entries and ``table_width`` fixes
+        the width of the block tables, so that a captured graph keeps its shapes."""
         entries = batch.entries
+        if pad_to is not None and len(entries) < pad_to:
+            filler = BatchEntry("", (0,), 0, tuple((NULL_PAGE,) for _ in self.groups), (0,), 0)
+            entries = entries + (filler,) * (pad_to - len(entries))
         lens = [e.num_tokens for e in entries]
         total = sum(lens)
         arena = IntArena()
@@ -212,11 +224,15 @@ class ModelRunner:
         views = []
         for g in range(len(self.groups)):
             width = max(len(e.block_tables[g]) for e in entries)
+            if table_width is not None:
+                if width > table_width:
+                    raise ValueError("a block table is wider than the captured graph allows")
+                width = table_width
             table = np.full((len(entries), width), NULL_PAGE, dtype=np.int32)
             for i, e in enumerate(entries):
                 table[i, :len(e.block_tables[g])] = e.block_tables[g]
             page_of_token = table[seq_of_token, positions // self.block_size].astype(np.int64)
-            slots = page_of_token * self.block_size + positions % self.block_size
+            slots = np.where(page_of_token >= 0, page_of_token * self.block_size + positions % self.block_size, -1)
             table_name, slots_name = f"group{g}/block_table", f"group{g}/slots"
             arena.add(table_name, table)
             arena.add(slots_name, slots)
@@ -227,28 +243,84 @@ class ModelRunner:
                           groups=views, states=self.storage.states)
         return ctx, rows
 
-    def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None) -> StepResult:
-        """Run one batch: writes the cache for every token given, returns logits where wanted."""
-        if not batch.entries:
-            return StepResult(None, [], 0, 0)
-        self._validate(batch)
-        ctx, rows = self._context(batch)
-        model = self.model
+    def _plan(self, ctx: StepContext) -> None:
         for call, binding in zip(self.order, self.bindings):
-            model.layout.blocks[call.layer].plan_step(ctx, binding)
-        ctx.arena.upload(model.device)
-        if clear_state_slots:
-            self.storage.clear_state(clear_state_slots)
+            self.model.layout.blocks[call.layer].plan_step(ctx, binding)
+
+    def _forward(self, ctx: StepContext, want_logits: bool) -> torch.Tensor | None:
+        """The kernels of one step, launched on the current stream; nothing here reads device
+        data on the host, so the whole sequence can be captured in a CUDA graph."""
+        model = self.model
         hidden = ops.embedding_gather(model.embedding, ctx.ints(StepContext.TOKEN_IDS), self._status)
         delta = None
         for call, binding in zip(self.order, self.bindings):
             delta = model.layout.blocks[call.layer].forward(hidden, delta, ctx, binding)
-        self.steps_run += 1
-        if not rows:
-            return StepResult(None, [], ctx.num_tokens, ctx.arena.bytes_uploaded)
+        if not want_logits:
+            return None
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
-        logits = gemm.matmul(normed, model.head.t(), out_dtype=torch.float32)
+        return gemm.matmul(normed, model.head.t(), out_dtype=torch.float32)
+
+    def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None) -> StepResult:
+        """Run one batch: writes the cache for every token given, returns logits where wanted.
+
+        A batch of single decoded tokens (every entry one token whose logits are wanted) replays
+        a CUDA graph captured for its size class; the logits tensor of such a step is reused by
+        the next one, so the caller reads it before stepping again.
+        """
+        if not batch.entries:
+            return StepResult(None, [], 0, 0)
+        self._validate(batch)
+        self.steps_run += 1
+        if self.use_graphs and self._graph_safe and not clear_state_slots and \
+                all(e.num_tokens == 1 and e.logits_at == (0,) for e in batch.entries):
+            return self._step_graph(batch)
+        ctx, rows = self._context(batch)
+        self._plan(ctx)
+        ctx.arena.upload(self.model.device)
+        if clear_state_slots:
+            self.storage.clear_state(clear_state_slots)
+        logits = self._forward(ctx, bool(rows))
         return StepResult(logits, rows, ctx.num_tokens, ctx.arena.bytes_uploaded)
+
+    # --- decode steps as CUDA graphs -----------------------------------------------------
+
+    GRAPH_BATCH_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    GRAPH_TABLE_STEP = 32     # block tables of a graph are this many pages wide, or a multiple
+
+    def _step_graph(self, batch: ExecutionBatch) -> StepResult:
+        count = len(batch.entries)
+        size = next((b for b in self.GRAPH_BATCH_SIZES if b >= count), None)
+        if size is None:
+            size = -(-count // 256) * 256
+        widest = max(len(t) for e in batch.entries for t in e.block_tables) if self.groups else 1
+        width = -(-widest // self.GRAPH_TABLE_STEP) * self.GRAPH_TABLE_STEP
+        ctx, rows = self._context(batch, table_width=width, pad_to=size)
+        ctx.planning_context_len = width * self.block_size
+        self._plan(ctx)
+        rows = rows[:count]
+        key = (size, width)
+        entry = self._graphs.get(key)
+        if entry is not None and entry["signature"] == ctx.arena.signature():
+            ctx.arena.upload(self.model.device, into=entry["ints"])
+            entry["graph"].replay()
+            ops.LAUNCHES["count"] += entry["launches"]     # the kernels of this module that the graph holds
+            return StepResult(entry["logits"][:count], rows, count, ctx.arena.bytes_uploaded)
+        # first step of this size class: run it eagerly on a buffer that stays, then capture the
+        # same launches (a capture records, it does not run) for the steps that follow
+        ints = torch.empty((ctx.arena.total_ints(),), dtype=torch.int32, device=self.model.device)
+        ctx.arena.upload(self.model.device, into=ints)
+        logits = self._forward(ctx, True)
+        torch.cuda.synchronize(self.model.device)
+        graph = torch.cuda.CUDAGraph()
+        ctx.scratch = {k: v for k, v in ctx.scratch.items() if not isinstance(v, torch.Tensor)}
+        before = ops.launch_count()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            captured = self._forward(ctx, True)
+        launches = ops.launch_count() - before
+        ops.LAUNCHES["count"] = before                     # a capture records launches, it runs none
+        self._graphs[key] = {"graph": graph, "ints": ints, "logits": captured, "signature": ctx.arena.signature(),
+                             "launches": launches}
+        return StepResult(logits[:count], rows, count, ctx.arena.bytes_uploaded)
 
     def execute(self, batch: ExecutionBatch) -> dict[str, np.ndarray]:
         """The reference's executor interface (src/paged_kv_serving/engine/engine.py:64-73):

@@ -39,6 +39,11 @@ class PagedAttention(Part):
     ``out_proj`` is ``(H * hd, width)``.
     """
 
+    @property
+    def graph_safe(self) -> bool:
+        return self.position.graph_safe
+
+
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PositionEncoding, scale: float | None = None, window: int | None = None) -> None:
         if n_heads % n_kv_heads:
@@ -108,6 +113,8 @@ class PagedAttention(Part):
         num_splits = 1
         if len(decode_entries):
             longest = int((first[decode_entries] + lens[decode_entries]).max())
+            if ctx.planning_context_len is not None:
+                longest = ctx.planning_context_len
             tiles = max(1, -(-longest // 64))
             blocks_per_split = len(decode_entries) * self.n_kv_heads
             num_splits = int(min(tiles, 32, max(1, -(-2 * _sm_count(ctx.device) // blocks_per_split))))

@@ -73,6 +73,10 @@ class Part:
     def cache_request(self) -> PagedKVRequest | StateRequest | None:
         return None
 
+    #: True when ``forward`` only launches work on the current stream (no host reads of device
+    #: data, no host-dependent control flow), so that a step may be captured in a CUDA graph.
+    graph_safe = False
+
     def plan_step(self, ctx: "StepContext", binding: "CacheBinding | None") -> None:
         """Called once per layer call before a step's kernels run, on the host: a part that needs
         integer arrays on the device (work lists, tables) adds them to ``ctx.arena`` here, so that
@@ -99,7 +103,16 @@ class IntArena:
             array = array.reshape(shape)
         self._arrays[name] = array
 
-    def upload(self, device: torch.device) -> None:
+    def signature(self) -> tuple:
+        """Names and shapes in order: two arenas with equal signatures have the same layout."""
+        return tuple((name, array.shape) for name, array in self._arrays.items())
+
+    def total_ints(self) -> int:
+        return max(4, sum((a.size + 3) // 4 * 4 for a in self._arrays.values()))
+
+    def upload(self, device: torch.device, into: torch.Tensor | None = None) -> None:
+        """Copy every array to the device in one transfer: into a fresh buffer, or into ``into``
+        (an int32 device tensor of ``total_ints()`` elements that a captured graph reads)."""
         names = list(self._arrays)
         sizes = [self._arrays[n].size for n in names]
         # every array starts on a 16-byte boundary (4 int32)
@@ -111,7 +124,13 @@ class IntArena:
         view = host.numpy()
         for name, offset, size in zip(names, offsets, sizes):
             view[offset:offset + size] = self._arrays[name].reshape(-1)
-        dev = host.to(device, non_blocking=True)
+        if into is None:
+            dev = host.to(device, non_blocking=True)
+        else:
+            if into.numel() < host.numel() or into.dtype != torch.int32:
+                raise ValueError("the static integer buffer does not fit this step's arrays")
+            dev = into
+            dev[:host.numel()].copy_(host, non_blocking=True)
         self._pinned = host  # keep alive until the copy has run
         for name, offset, size in zip(names, offsets, sizes):
             self._device[name] = dev[offset:offset + size].view(self._arrays[name].shape)
@@ -163,6 +182,9 @@ class StepContext:
     groups: list[GroupView] = field(default_factory=list)
     states: list[torch.Tensor] = field(default_factory=list)   # [slots, *shape] per state entry
     scratch: dict[str, Any] = field(default_factory=dict)
+    #: When set, parts plan launch shapes from this context length instead of the batch's own
+    #: (a captured graph must keep its launch shapes from step to step).
+    planning_context_len: int | None = None
 
     # the arrays every step has (names in the arena)
     TOKEN_IDS = "token_ids"

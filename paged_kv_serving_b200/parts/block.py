@@ -20,6 +20,11 @@ class PreNormBlock(Part):
     pending ``delta`` and returns its own feed-forward output as the next pending delta.
     """
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(child.graph_safe for child in self.sub_parts().values())
+
+
     def __init__(self, mixer_norm: Part, mixer: Part, ff_norm: Part, feed_forward: Part) -> None:
         self.mixer_norm = mixer_norm
         self.mixer = mixer

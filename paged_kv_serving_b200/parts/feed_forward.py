@@ -22,6 +22,9 @@ class SwiGLU(Part):
     fused ``silu * up`` kernel.
     """
 
+    graph_safe = True
+
+
     def __init__(self, width: int, inner: int, clip: float = 60.0) -> None:
         self.width = int(width)
         self.inner = int(inner)

@@ -17,6 +17,9 @@ class RMSNorm(Part):
     (reference: src/paged_kv_serving/engine/model.py:43-46), fused with the residual add in
     front of it: the stream ``hidden`` (float32) first takes the pending ``delta``."""
 
+    graph_safe = True
+
+
     def __init__(self, width: int, eps: float) -> None:
         self.width = int(width)
         self.eps = float(eps)

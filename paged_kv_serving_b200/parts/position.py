@@ -22,6 +22,8 @@ class PositionEncoding(Part):
     position only.
     """
 
+    graph_safe = True
+
     def fused_tables(self, device: torch.device) -> tuple[torch.Tensor, torch.Tensor] | None:
         return None
 

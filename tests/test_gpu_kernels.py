@@ -50,7 +50,7 @@ def test_embedding_gather(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [72, 1000, 4096, 11008])
+@pytest.mark.parametrize("width", [72, 1000, 1001, 4096, 11008, 16384, 20000])
 def test_add_rmsnorm(dtype, width):
     from paged_kv_serving_b200 import ops
 
@@ -78,11 +78,11 @@ def test_add_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_silu_mul(dtype):
+@pytest.mark.parametrize("ff", [300, 301, 304, 14336])
+def test_silu_mul(dtype, ff):
     from paged_kv_serving_b200 import ops
 
     rng = np.random.default_rng(1)
-    ff = 300
     x = (rng.standard_normal((13, 2 * ff)) * 4).astype(np.float32)
     x[0, :4] = [-100.0, 100.0, -60.0, 60.0]
     x_d = dev(x, DTYPES[dtype])
@@ -94,11 +94,12 @@ def test_silu_mul(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_rope_kv_store(dtype):
+@pytest.mark.parametrize("heads, kv, hd", [(5, 5, 48), (7, 1, 20), (32, 8, 128), (4, 2, 8)])
+def test_rope_kv_store(dtype, heads, kv, hd):
     from paged_kv_serving_b200 import ops
 
     rng = np.random.default_rng(2)
-    heads, kv, hd, page, pages, tokens = 5, 5, 48, 4, 9, 11
+    page, pages, tokens = 4, 9, 11
     cos, sin = plain_model.rope_tables(64, hd, 1234.5)
     qkv = rng.standard_normal((tokens, (heads + 2 * kv) * hd)).astype(np.float32)
     positions = rng.integers(0, 64, size=tokens).astype(np.int32)

@@ -144,3 +144,30 @@ def test_long_decoding(dtype):
     for i in range(20, len(tokens)):
         got.append(session.step([{"id": "r", "tokens": [tokens[i]], "want": [0]}]))
     helpers.assert_close(np.concatenate(got), want[19:], dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_captured_decode_steps_equal_eager_ones(dtype):
+    """Decode-only steps replay CUDA graphs; the same steps without graphs give the same logits,
+    also when the number of live requests changes from step to step."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    tensors = helpers.tensors_for("C", dtype)
+    model = helpers.build_model(helpers.TINY_C, tensors, dtype)
+    prompts = [helpers.random_tokens(helpers.TINY_C, n, seed=70 + n) for n in (40, 75, 23)]
+    outputs = []
+    for use_graphs in (True, False):
+        session = ReplaySession(model, max_tokens=512, block_size=16)
+        session.runner.use_graphs = use_graphs
+        got = []
+        for i, p in enumerate(prompts):
+            session.step([{"id": f"s{i}", "tokens": p[:20], "want": []}])
+        for k in range(20, 75):
+            entries = [{"id": f"s{i}", "tokens": [p[k]], "want": [0]} for i, p in enumerate(prompts) if k < len(p)]
+            got.append(session.step(entries))
+        if use_graphs:
+            assert len(session.runner._graphs) >= 3        # batches of 3, 2 and 1 requests
+        outputs.append(np.concatenate(got))
+    want = plain_model.forward(helpers.TINY_C, tensors, prompts[1])
+    helpers.assert_close(outputs[0][-1:], want[74:75], dtype, "graph decode against plain")
+    assert np.abs(outputs[0] - outputs[1]).max() <= (1e-5 if dtype == "float32" else helpers.bf16_atol(outputs[1]))
