@@ -63,6 +63,20 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const D* __restri
   }
 }
 
+// Where gate and up of output column i sit in an input row. interleave = 0: gate columns
+// [0, ff), up columns [ff, 2 ff). interleave = B: blocks of B gate columns followed by the B
+// matching up columns (the layout the fused tensor-core product works on).
+__device__ __forceinline__ void gate_up_at(int i, int ff, int interleave, int& g, int& u) {
+  if (interleave == 0) {
+    g = i;
+    u = ff + i;
+  } else {
+    const int b = i / interleave;
+    g = b * 2 * interleave + (i - b * interleave);
+    u = g + interleave;
+  }
+}
+
 // The same, for widths that are multiples of 4 and at most 4 * VEC_PER_THREAD * blockDim: every
 // thread keeps its part of the row in registers (one pass over memory, 16-byte accesses).
 constexpr int NORM_VEC_PER_THREAD = 4;
@@ -129,17 +143,20 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const D* __re
 // ---------------------------------------------------------------------------------------------
 // ff a multiple of 8 (bfloat16) or 4 (float32): 16-byte accesses, one flat grid over all chunks
 template <typename A, int V>
-__global__ void silu_mul_vec_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, long long n_chunks,
-                                    float clip) {
+__global__ void silu_mul_vec_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, int in_stride,
+                                    int interleave, long long n_chunks, float clip) {
   const int chunks_per_row = ff / V;
   for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
     const long long t = c / chunks_per_row;
     const int i = (int)(c - t * chunks_per_row) * V;
-    const A* g = gate_up + t * 2 * ff + i;
+    int gi, ui;
+    gate_up_at(i, ff, interleave, gi, ui);
+    const A* g = gate_up + t * in_stride + gi;
+    const A* u = gate_up + t * in_stride + ui;
     A* o = out + t * ff + i;
 #pragma unroll
     for (int q = 0; q < V; q += 4) {
-      const float4 gv = load4(g + q), uv = load4(g + ff + q);
+      const float4 gv = load4(g + q), uv = load4(u + q);
       float4 r;
       r.x = gv.x * (1.0f / (1.0f + expf(-fminf(fmaxf(gv.x, -clip), clip)))) * uv.x;
       r.y = gv.y * (1.0f / (1.0f + expf(-fminf(fmaxf(gv.y, -clip), clip)))) * uv.y;
@@ -151,16 +168,18 @@ __global__ void silu_mul_vec_kernel(const A* __restrict__ gate_up, A* __restrict
 }
 
 template <typename A>
-__global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, float clip) {
+__global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, int in_stride,
+                                int interleave, float clip) {
   const int t = blockIdx.y;
-  const A* g = gate_up + (size_t)t * 2 * ff;
-  const A* u = g + ff;
+  const A* row = gate_up + (size_t)t * in_stride;
   A* o = out + (size_t)t * ff;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ff; i += gridDim.x * blockDim.x) {
-    const float x = to_float(g[i]);
+    int gi, ui;
+    gate_up_at(i, ff, interleave, gi, ui);
+    const float x = to_float(row[gi]);
     const float c = fminf(fmaxf(x, -clip), clip);
     const float s = x * (1.0f / (1.0f + expf(-c)));
-    o[i] = from_float<A>(s * to_float(u[i]));
+    o[i] = from_float<A>(s * to_float(row[ui]));
   }
 }
 
@@ -325,19 +344,20 @@ PKV_EXPORT int pkv_add_rmsnorm(float* hidden, const void* delta, int delta_dtype
   return PKV_ERR_DTYPE;
 }
 
-PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, int ff, float clip, void* stream) {
+PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, int ff, int in_stride,
+                            int interleave, float clip, void* stream) {
   if (n_tokens <= 0) return 0;
-  if (ff <= 0) return PKV_ERR_SIZE;
+  if (ff <= 0 || interleave < 0 || in_stride < 2 * ff) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
-  if ((dtype == PKV_BF16 && ff % 8 == 0) || (dtype == PKV_F32 && ff % 4 == 0)) {
-    const int v = dtype == PKV_BF16 ? 8 : 4;
+  const int v = dtype == PKV_BF16 ? 8 : 4;
+  if ((dtype == PKV_BF16 || dtype == PKV_F32) && ff % v == 0 && in_stride % v == 0 && interleave % v == 0) {
     const long long n_chunks = (long long)n_tokens * (ff / v);
     long long blocks = (n_chunks + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == PKV_BF16)
-      silu_mul_vec_kernel<bf16, 8><<<(int)blocks, 256, 0, s>>>((const bf16*)gate_up, (bf16*)out, ff, n_chunks, clip);
+      silu_mul_vec_kernel<bf16, 8><<<(int)blocks, 256, 0, s>>>((const bf16*)gate_up, (bf16*)out, ff, in_stride, interleave, n_chunks, clip);
     else
-      silu_mul_vec_kernel<float, 4><<<(int)blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, ff, n_chunks, clip);
+      silu_mul_vec_kernel<float, 4><<<(int)blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, ff, in_stride, interleave, n_chunks, clip);
     return launch_status();
   }
   const int threads = 256;
@@ -348,9 +368,9 @@ PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tok
     const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
     dim3 grid(bx, nt);
     if (dtype == PKV_F32)
-      silu_mul_kernel<float><<<grid, threads, 0, s>>>((const float*)gate_up + (size_t)t0 * 2 * ff, (float*)out + (size_t)t0 * ff, ff, clip);
+      silu_mul_kernel<float><<<grid, threads, 0, s>>>((const float*)gate_up + (size_t)t0 * in_stride, (float*)out + (size_t)t0 * ff, ff, in_stride, interleave, clip);
     else if (dtype == PKV_BF16)
-      silu_mul_kernel<bf16><<<grid, threads, 0, s>>>((const bf16*)gate_up + (size_t)t0 * 2 * ff, (bf16*)out + (size_t)t0 * ff, ff, clip);
+      silu_mul_kernel<bf16><<<grid, threads, 0, s>>>((const bf16*)gate_up + (size_t)t0 * in_stride, (bf16*)out + (size_t)t0 * ff, ff, in_stride, interleave, clip);
     else
       return PKV_ERR_DTYPE;
   }

@@ -1,0 +1,408 @@
+// Matrix product on the fifth-generation tensor cores of sm_100a, written by hand:
+//   D[M, N] = A[M, K] . B[N, K]^T      A, B bfloat16 with K contiguous, accumulation in float32
+// Operand tiles are brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle),
+// multiplied by tcgen05.mma issued by one thread, accumulated in tensor memory (TMEM) and read
+// back with tcgen05.ld for the epilogue, which is fused with what follows the product in the
+// decoder:
+//   EPI_BF16      store D as bfloat16                         (QKV, output and down projections)
+//   EPI_F32       store D as float32                          (logits of the LM head)
+//   EPI_SILU_MUL  B holds gate and up rows interleaved in blocks of 128; the epilogue stores
+//                 silu(gate) * up as bfloat16, half as wide   (the SwiGLU feed-forward,
+//                 reference formula: src/paged_kv_serving/engine/model.py:49-51, 256-259)
+//
+// One block per SM walks over 128 x 256 tiles of D with six warps: warp 0 issues the TMA loads
+// into a ring of stages, warp 1 allocates TMEM and issues the MMAs (four of K = 16 per 64-wide K
+// block), warps 2-5 run the epilogue, each on the 32 TMEM lanes it may address. Two accumulators
+// alternate in TMEM, so the epilogue of a tile runs under the MMAs of the next one.
+// Ring slots are handed over with mbarriers: TMA completes "full" with its byte count, the MMA
+// thread releases "empty" and "accumulator ready" with tcgen05.commit, the epilogue warps hand an
+// accumulator back with plain arrivals. No load is multicast; every block fetches its own tiles.
+//
+// Every wait on an mbarrier is bounded: after about a second without progress a block records
+// an error code in the status word, lets its copies in flight land (again bounded), frees its
+// TMEM and returns, so a fault in the hand-over can never hang the GPU.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pkv {
+
+constexpr int GM_BM = 128;
+constexpr int GM_BK = 64;                    // 64 bf16 = 128 bytes = one swizzle row
+constexpr int GM_THREADS = 192;
+constexpr int GM_UMMA_K = 16;
+constexpr long long GM_WAIT_CYCLES = 2000000000LL;   // about one second at 2 GHz
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2 };
+enum { GEMM_ERR_TIMEOUT = 2 };
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait: false when the block gave up (its own limit ran out, or another role did).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const long long start = clock64();
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 0xff) == 0xff) {
+      if (*abort_flag) return false;
+      if (clock64() - start > GM_WAIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c_inner, int c_outer) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c_inner), "r"(c_outer)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(columns));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled by 128
+// bytes: groups of 8 rows are 1024 bytes apart (stride offset), the leading offset is unused.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffff) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused for this layout)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset: 8 rows x 128 bytes
+  d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                            // 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float silu_clipped(float x, float clip) {
+  const float c = fminf(fmaxf(x, -clip), clip);
+  return x * (1.0f / (1.0f + expf(-c)));
+}
+
+// Epilogue of one 32-column chunk pair: converts and stores what one thread holds of its row.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(void* out, int ldo, int row, int col0, int n_valid, const float (&v)[32]) {
+  if (EPI == EPI_F32) {
+    float* dst = reinterpret_cast<float*>(out) + (size_t)row * ldo + col0;
+    if (col0 + 32 <= n_valid) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_valid) dst[i] = v[i];
+    }
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + col0;
+    if (col0 + 32 <= n_valid) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 packed;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 pair = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+          w[j] = *reinterpret_cast<uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(dst + i) = packed;
+      }
+    } else {
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_valid) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// Persistent: each block walks over output tiles (row blocks fastest, so that the blocks in
+// flight share a few tiles of B, the weights, while all of A stays in L2). Two accumulators in
+// TMEM alternate, so the epilogue of one tile runs under the MMAs of the next.
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    void* __restrict__ out, int ldo, int M, int n_valid, int K, int m_tiles, int n_tiles, float clip,
+                    int* __restrict__ status) {
+  constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;
+  constexpr uint32_t B_BYTES = BN * GM_BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;           // two accumulators of BN columns (a power of two)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_blocks = (K + GM_BK - 1) / GM_BK;
+  const int total_tiles = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);                 // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* aborted = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * GM_BM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int stage = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty_bar[stage], ((it / STAGES) - 1) & 1, aborted)) { ok = false; break; }
+          uint8_t* a_dst = tiles + (size_t)stage * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full_bar[stage], kb * GM_BK, m0);
+          tma_load_2d(a_dst + A_BYTES, &map_b, &full_bar[stage], kb * GM_BK, n0);
+        }
+      }
+      if (*aborted) {
+        // let the copies already issued land before the block's shared memory is given up
+        for (int j = max(0, it - STAGES); j < it; ++j) {
+          const long long start = clock64();
+          while (!mbar_try_wait(&full_bar[j % STAGES], (j / STAGES) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = BN
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (local >= 2) ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, aborted);   // epilogue drained it
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int stage = it % STAGES;
+          ok = mbar_wait(&full_bar[stage], (it / STAGES) & 1, aborted);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_addr(tiles + (size_t)stage * STAGE_BYTES);
+          const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < GM_BK / GM_UMMA_K; ++k) {
+            // advancing 16 elements along K inside the swizzled row: 32 bytes = 2 units of 16 bytes
+            umma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);          // the slot is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);       // the accumulator is complete once all MMAs are done
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                  // the TMEM lanes this warp may address: 32 * (warp % 4)
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile % m_tiles) * GM_BM, n0 = (tile / m_tiles) * BN;
+      const int row = m0 + quarter * 32 + lane;
+      // every lane waits; the warp goes on only as a whole (tcgen05.ld needs all 32 lanes)
+      const bool ready = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (local >> 1) & 1, aborted) ? 1 : 0) != 0;
+      if (!ready) break;
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      if (EPI == EPI_SILU_MUL) {
+        // columns [0, BN/2) of the tile are gate values, [BN/2, BN) the matching up values
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          float g[32], u[32];
+          tmem_load32(lane_addr + c, g);
+          tmem_load32(lane_addr + BN / 2 + c, u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) g[i] = silu_clipped(g[i], clip) * u[i];
+          if (row < M) store_chunk<EPI_BF16>(out, ldo, row, (n0 >> 1) + c, n_valid, g);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          float v[32];
+          tmem_load32(lane_addr + c, v);
+          if (row < M) store_chunk<EPI>(out, ldo, row, n0 + c, n_valid, v);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);   // this warp has read its part of the accumulator
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0 && abort_flag) atomicExch(status, GEMM_ERR_TIMEOUT);
+}
+
+// -----------------------------------------------------------------------------------------------
+// host side
+// -----------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows, fetched in boxes of
+// [box_rows, 64] with the 128-byte swizzle. Outside the matrix a box is filled with zeros.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return PKV_ERR_LIMIT;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)GM_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : PKV_ERR_SIZE;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int n_tiles_cols,
+                       int n_valid, int K, float clip, int* status, cudaStream_t s) {
+  const size_t smem = (size_t)STAGES * (GM_BM + BN) * GM_BK * 2 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int m_tiles = (M + GM_BM - 1) / GM_BM;
+  const long long total = (long long)m_tiles * n_tiles_cols;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  }
+  const int blocks = (int)(total < sm_count ? total : sm_count);
+  gemm_tcgen05_kernel<BN, STAGES, EPI><<<blocks, GM_THREADS, smem, s>>>(map_a, map_b, out, ldo, M, n_valid, K, m_tiles,
+                                                                       n_tiles_cols, clip, status);
+  return launch_status();
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+// 1 when this kernel takes the operands (alignment and size rules of TMA), else 0.
+PKV_EXPORT int pkv_gemm_tcgen05_supports(long long a_ptr, long long b_ptr, int lda, int ldb, int K) {
+  return (a_ptr % 16 == 0 && b_ptr % 16 == 0 && lda % 8 == 0 && ldb % 8 == 0 && K >= 8 && K % 8 == 0) ? 1 : 0;
+}
+
+// D = A . B^T with A [M, K] (lda), B [N, K] (ldb), both bfloat16.
+//   epilogue 0: out bfloat16 [M, N]; 1: out float32 [M, N];
+//   2: B rows interleaved (128 gate rows, 128 up rows, ...), out bfloat16 [M, n_out] = silu(gate) * up.
+// `status` is a device int that receives an error code if a block had to give up a wait.
+PKV_EXPORT int pkv_gemm_tcgen05(const void* a, int lda, const void* b, int ldb, void* out, int ldo, int M, int N,
+                                int K, int epilogue, int n_out, float clip, int* status, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!pkv_gemm_tcgen05_supports((long long)(uintptr_t)a, (long long)(uintptr_t)b, lda, ldb, K)) return PKV_ERR_ALIGN;
+  if (lda < K || ldb < K) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  alignas(64) CUtensorMap map_a, map_b;
+  int r = make_map(&map_a, a, M, K, lda, GM_BM);
+  if (r) return r;
+  if (epilogue == EPI_SILU_MUL) {
+    if (N % 256 || n_out <= 0 || n_out > N / 2 || ldo % 8 || (uintptr_t)out % 16) return PKV_ERR_SIZE;
+    r = make_map(&map_b, b, N, K, ldb, 256);
+    if (r) return r;
+    return launch_gemm<256, 4, EPI_SILU_MUL>(map_a, map_b, out, ldo, M, N / 256, n_out, K, clip, status, s);
+  }
+  if (epilogue == EPI_BF16) {
+    if (ldo % 8 || (uintptr_t)out % 16) return PKV_ERR_ALIGN;
+    r = make_map(&map_b, b, N, K, ldb, 256);
+    if (r) return r;
+    return launch_gemm<256, 4, EPI_BF16>(map_a, map_b, out, ldo, M, (N + 255) / 256, N, K, clip, status, s);
+  }
+  if (epilogue == EPI_F32) {
+    if (ldo % 4 || (uintptr_t)out % 16) return PKV_ERR_ALIGN;
+    r = make_map(&map_b, b, N, K, ldb, 256);
+    if (r) return r;
+    return launch_gemm<256, 4, EPI_F32>(map_a, map_b, out, ldo, M, (N + 255) / 256, N, K, clip, status, s);
+  }
+  return PKV_ERR_DTYPE;
+}

@@ -136,7 +136,7 @@ class ModelRunner:
                 self.bindings.append(CacheBinding(call.cache, group=g, index=index, write=call.write))
             else:
                 self.bindings.append(CacheBinding(call.cache, state=self.storage.state_index[call.cache], write=call.write))
-        self._status = torch.zeros((1,), dtype=torch.int32, device=model.device)
+        self._status = ops.status_word(model.device)
         self.steps_run = 0
         self.use_graphs = use_graphs
         self._graph_safe = all(block.graph_safe for block in model.layout.blocks) and model.layout.final_norm.graph_safe
@@ -258,7 +258,7 @@ class ModelRunner:
         if not want_logits:
             return None
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
-        return gemm.matmul(normed, model.head.t(), out_dtype=torch.float32)
+        return gemm.linear(normed, model.head, out_dtype=torch.float32)
 
     def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None) -> StepResult:
         """Run one batch: writes the cache for every token given, returns logits where wanted.
@@ -322,10 +322,17 @@ class ModelRunner:
                              "launches": launches}
         return StepResult(logits[:count], rows, count, ctx.arena.bytes_uploaded)
 
+    def check_status(self) -> None:
+        """Raise if a kernel recorded a fault since the last check (this synchronises)."""
+        code = int(self._status.item())
+        if code:
+            self._status.zero_()
+            what = {1: "a token id outside the embedding table", 2: "a tensor-core product gave up a wait"}
+            raise RuntimeError(f"a kernel recorded a fault: {what.get(code, f'code {code}')}")
+
     def execute(self, batch: ExecutionBatch) -> dict[str, np.ndarray]:
         """The reference's executor interface (src/paged_kv_serving/engine/engine.py:64-73):
         host float32 rows keyed by sequence id."""
         result = self.step(batch).by_sequence()
-        if int(self._status.item()) != 0:
-            raise RuntimeError("a kernel saw a token id outside the embedding table")
+        self.check_status()
         return result

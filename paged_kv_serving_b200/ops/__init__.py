@@ -16,8 +16,8 @@ from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
     "add_rmsnorm", "attention_bf16_rows", "attention_bf16_supports", "attention_decode_bf16",
-    "attention_prefill_bf16", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather",
-    "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul",
+    "attention_prefill_bf16", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports",
+    "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
 ]
 
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
@@ -122,15 +122,33 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, clip: float) -> torch.Tensor:
-    """``silu(gate) * up`` for a fused ``[T, 2*ff]`` input whose first half of columns is the gate."""
+def silu_mul(gate_up: torch.Tensor, clip: float, ff: int | None = None, interleave: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` for a fused input ``[T, >= 2*ff]``; output ``[T, ff]``.
+
+    ``interleave = 0``: the first ``ff`` columns are the gate, the next ``ff`` the up values.
+    ``interleave = B``: blocks of ``B`` gate columns followed by the ``B`` matching up columns.
+    """
     _need(gate_up, None, "gate_up")
-    n, two_ff = gate_up.shape
-    ff = two_ff // 2
+    n, width = gate_up.shape
+    if ff is None:
+        ff = width // 2
     out = torch.empty((n, ff), dtype=gate_up.dtype, device=gate_up.device)
-    fn = _fn("elementwise", "pkv_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
-    _check(fn(_ptr(gate_up), _ptr(out), dtype_code(gate_up.dtype), n, ff, float(clip), _stream()), "silu_mul")
+    fn = _fn("elementwise", "pkv_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(gate_up), _ptr(out), dtype_code(gate_up.dtype), n, ff, width, int(interleave), float(clip),
+              _stream()), "silu_mul")
     return out
+
+
+_STATUS: dict[str, torch.Tensor] = {}
+
+
+def status_word(device: torch.device | str) -> torch.Tensor:
+    """The int32 status word of a device: kernels record a code there instead of trapping
+    (1: a token id outside the embedding table, 2: a tensor-core product gave up a wait)."""
+    key = str(torch.device(device))
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _STATUS[key]
 
 
 def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None,
@@ -245,6 +263,50 @@ def attention_decode_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Te
               _ptr(scratch), total_rows, _stream()), "attention_decode_bf16")
     if num_splits > 1:
         LAUNCHES["count"] += 1   # the merge kernel
+
+
+def gemm_tcgen05_supports(a: torch.Tensor, b_nk: torch.Tensor) -> bool:
+    """Whether the hand-written tcgen05 product takes these operands (bfloat16, K contiguous,
+    16-byte aligned rows)."""
+    if a.dtype != torch.bfloat16 or b_nk.dtype != torch.bfloat16 or a.stride(1) != 1 or b_nk.stride(1) != 1:
+        return False
+    lib = library("gemm_tcgen05")
+    lib.pkv_gemm_tcgen05_supports.restype = c_int
+    lib.pkv_gemm_tcgen05_supports.argtypes = [c_longlong, c_longlong, c_int, c_int, c_int]
+    return bool(lib.pkv_gemm_tcgen05_supports(a.data_ptr(), b_nk.data_ptr(), a.stride(0), b_nk.stride(0), a.shape[1]))
+
+
+GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "silu_mul": 2}
+
+
+def gemm_tcgen05(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epilogue: str = "bf16",
+                 n_out: int = 0, clip: float = 60.0) -> torch.Tensor:
+    """``a [M, K] @ b_nk [N, K]^T`` on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).
+
+    ``epilogue``: ``"bf16"`` / ``"f32"`` store the product; ``"silu_mul"`` expects the rows of
+    ``b_nk`` interleaved in blocks of 128 gate rows and 128 up rows and stores
+    ``silu(gate) * up`` as ``[M, n_out]``. ``status`` receives an error code if a block gave up.
+    """
+    if epilogue not in GEMM_EPILOGUES:
+        raise ValueError(f"unknown epilogue {epilogue!r}")
+    for name, t in (("a", a), ("b_nk", b_nk)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a bfloat16 CUDA matrix with contiguous rows")
+    _need(status, torch.int32, "status")
+    m, k = a.shape
+    n = b_nk.shape[0]
+    if b_nk.shape[1] != k:
+        raise ValueError("inner sizes differ")
+    if epilogue == "silu_mul":
+        out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
+    else:
+        out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
+    fn = _fn("gemm_tcgen05", "pkv_gemm_tcgen05",
+             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+              c_void_p, c_void_p])
+    _check(fn(_ptr(a), a.stride(0), _ptr(b_nk), b_nk.stride(0), _ptr(out), out.stride(0), m, n, k,
+              GEMM_EPILOGUES[epilogue], int(n_out), float(clip), _ptr(status), _stream()), "gemm_tcgen05")
+    return out
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,

@@ -1,27 +1,41 @@
 """Matrix products of the product path.
 
-The reference's engine hands every matrix product to a library (NumPy/OpenBLAS,
-src/paged_kv_serving/engine/model.py:249,258-259,264); here the library is cuBLAS through
-``torch.mm``. Reduced-precision modes are switched off: float32 products use true float32
-multiply-adds (no TF32), bfloat16 products accumulate in float32 without reduced-precision
-reductions.
+Weights are held as ``[out, in]`` with the inner size contiguous. In bfloat16, products with at
+least ``TCGEN05_MIN_ROWS`` rows of activations (prompt portions) run on the hand-written
+tcgen05/TMA kernel of ``csrc/gemm_tcgen05.cu``, with the SiLU-times-up step of the feed-forward
+fused into its epilogue; the few rows of a decode step, and the float32 path, go to cuBLAS
+through ``torch.mm``, as the reference's engine hands its products to a library
+(src/paged_kv_serving/engine/model.py:249,258-259,264). Reduced-precision modes are switched
+off: float32 products use true float32 multiply-adds (no TF32), bfloat16 products accumulate in
+float32 without reduced-precision reductions.
 """
 
 from __future__ import annotations
 
 import torch
 
-__all__ = ["matmul"]
+from paged_kv_serving_b200 import ops
+
+__all__ = ["TCGEN05_MIN_ROWS", "linear", "linear_silu_mul", "matmul"]
 
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
+#: Activations with at least this many rows use the tcgen05 kernel (its tiles are 128 rows tall).
+TCGEN05_MIN_ROWS = 128
+#: Set to False to send every product to cuBLAS (used by tests that compare the two).
+USE_TCGEN05 = True
+
+
+def _own_kernel(x: torch.Tensor, w_nk: torch.Tensor) -> bool:
+    return (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] >= TCGEN05_MIN_ROWS
+            and ops.gemm_tcgen05_supports(x, w_nk))
+
 
 def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``x [T, K] @ w [K, N]``; ``w`` may be a transposed view. ``out_dtype`` float32 keeps the
-    float32 accumulator of a bfloat16 product."""
+    """``x [T, K] @ w [K, N]`` through cuBLAS; ``w`` may be a transposed view."""
     if not x.is_cuda:
         raise ValueError("matmul runs on the GPU only (there is no CPU path)")
     if x.dtype != w.dtype:
@@ -29,3 +43,20 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w, out_dtype=out_dtype)
     return torch.mm(x, w)
+
+
+def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x [T, K] @ w_nk [N, K]^T``; ``out_dtype`` float32 keeps the float32 accumulator."""
+    wants_f32 = out_dtype == torch.float32
+    # rows of the output must start on 16-byte boundaries for the kernel's vector stores
+    if w_nk.shape[0] % (4 if wants_f32 else 8) == 0 and _own_kernel(x, w_nk):
+        return ops.gemm_tcgen05(x, w_nk, ops.status_word(x.device), "f32" if wants_f32 else "bf16")
+    return matmul(x, w_nk.t(), out_dtype)
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleave: int, clip: float) -> torch.Tensor:
+    """``silu(x @ gate^T) * (x @ up^T)`` for gate and up rows held in one matrix (``interleave``
+    as in ``ops.silu_mul``); ``[T, ff]``."""
+    if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and _own_kernel(x, w_gate_up):
+        return ops.gemm_tcgen05(x, w_gate_up, ops.status_word(x.device), "silu_mul", n_out=ff, clip=clip)
+    return ops.silu_mul(matmul(x, w_gate_up.t()), clip, ff=ff, interleave=interleave)

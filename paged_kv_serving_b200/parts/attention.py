@@ -74,6 +74,11 @@ class PagedAttention(Part):
             "out_proj": ParamSpec((self.n_heads * self.head_dim, self.width)),
         }
 
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        # held as [out, in]: the inner size contiguous, as the matrix-product kernels read it
+        self.qkv_proj = params["qkv_proj"].t().contiguous()
+        self.out_proj = params["out_proj"].t().contiguous()
+
     def cache_request(self) -> PagedKVRequest:
         return PagedKVRequest(self.n_kv_heads, self.head_dim, self.window)
 
@@ -148,7 +153,7 @@ class PagedAttention(Part):
         group = ctx.groups[binding.group]
         k_pool = group.k_pool[binding.index]
         v_pool = group.v_pool[binding.index]
-        qkv = gemm.matmul(x, self.qkv_proj)
+        qkv = gemm.linear(x, self.qkv_proj)
         positions = ctx.ints(ctx.POSITIONS)
         tables = self.position.fused_tables(ctx.device)
         if tables is None:
@@ -161,13 +166,13 @@ class PagedAttention(Part):
                           self.n_heads, self.n_kv_heads, self.head_dim, group.page_size)
         if self._fast(ctx):
             attended = self._attend_fast(qkv, ctx, group, k_pool, v_pool)
-            return gemm.matmul(attended, self.out_proj)
+            return gemm.linear(attended, self.out_proj)
         seq_name, row_name = self._work_names()
         attended = ops.paged_attention_generic(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.head_dim,
             group.page_size, self.window or 0, self.scale)
-        return gemm.matmul(attended, self.out_proj)
+        return gemm.linear(attended, self.out_proj)
 
     def _attend_fast(self, qkv, ctx: StepContext, group, k_pool, v_pool) -> torch.Tensor:
         plan = ctx.scratch[f"attention/fast/g{self.group_size}"]

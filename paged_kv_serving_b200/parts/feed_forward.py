@@ -18,9 +18,14 @@ class SwiGLU(Part):
     argument of the sigmoid's exponential clipped to ``[-clip, clip]``
     (reference: src/paged_kv_serving/engine/model.py:49-51, 256-259).
 
-    The gate and up matrices are concatenated at load so that one matrix product feeds the
-    fused ``silu * up`` kernel.
+    Weights are re-laid at load as ``[out, in]``. Gate and up become one matrix so that a single
+    product feeds the ``silu * up`` step: in bfloat16 their rows are interleaved in blocks of
+    128 (padded with zero rows to a multiple of 128), which lets the tensor-core kernel apply the
+    step in its epilogue; in float32 they are simply stacked.
     """
+
+    graph_safe = True
+    BLOCK = 128
 
     graph_safe = True
 
@@ -29,8 +34,9 @@ class SwiGLU(Part):
         self.width = int(width)
         self.inner = int(inner)
         self.clip = float(clip)
-        self.gate_up: torch.Tensor | None = None   # [width, 2 * inner]
-        self.down_proj: torch.Tensor | None = None  # [inner, width]
+        self.gate_up: torch.Tensor | None = None    # [2 * inner (padded), width]
+        self.down_proj: torch.Tensor | None = None  # [width, inner]
+        self.interleave = 0
 
     def param_specs(self) -> dict[str, ParamSpec]:
         return {
@@ -40,9 +46,24 @@ class SwiGLU(Part):
         }
 
     def load(self, params: dict[str, torch.Tensor]) -> None:
-        self.gate_up = torch.cat([params["gate_proj"], params["up_proj"]], dim=1).contiguous()
-        self.down_proj = params["down_proj"].contiguous()
+        gate, up = params["gate_proj"].t(), params["up_proj"].t()          # [inner, width]
+        if gate.dtype == torch.bfloat16:
+            block = self.BLOCK
+            blocks = -(-self.inner // block)
+            fused = torch.zeros((blocks, 2, block, self.width), dtype=gate.dtype, device=gate.device)
+            flat = fused.view(blocks, 2, block * self.width)
+            padded = torch.zeros((2, blocks * block, self.width), dtype=gate.dtype, device=gate.device)
+            padded[0, :self.inner] = gate
+            padded[1, :self.inner] = up
+            flat[:, 0] = padded[0].view(blocks, block * self.width)
+            flat[:, 1] = padded[1].view(blocks, block * self.width)
+            self.gate_up = fused.view(2 * blocks * block, self.width)
+            self.interleave = block
+        else:
+            self.gate_up = torch.cat([gate, up], dim=0).contiguous()
+            self.interleave = 0
+        self.down_proj = params["down_proj"].t().contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gate_up = gemm.matmul(x, self.gate_up)
-        return gemm.matmul(ops.silu_mul(gate_up, self.clip), self.down_proj)
+        gated = gemm.linear_silu_mul(x, self.gate_up, self.inner, self.interleave, self.clip)
+        return gemm.linear(gated, self.down_proj)

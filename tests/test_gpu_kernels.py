@@ -91,6 +91,15 @@ def test_silu_mul(dtype, ff):
     want = plain_model.silu(seen[:, :ff]) * seen[:, ff:]
     assert np.isfinite(as_np(out)).all()
     assert np.abs(as_np(out) - want).max() <= tol(dtype, np.abs(want).max())
+    # the interleaved layout: blocks of 8 (and of 128) gate columns, each followed by its up columns
+    for block in (8, 128):
+        padded = -(-ff // block) * block
+        wide = np.zeros((13, 2 * padded), dtype=np.float32)
+        cols = np.arange(ff)
+        wide[:, (cols // block) * 2 * block + cols % block] = seen[:, :ff]
+        wide[:, (cols // block) * 2 * block + block + cols % block] = seen[:, ff:]
+        again = ops.silu_mul(dev(wide, DTYPES[dtype]), 60.0, ff=ff, interleave=block)
+        assert np.array_equal(as_np(again), as_np(out))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -278,6 +287,71 @@ def test_attention_refuses_what_it_cannot_do():
     with pytest.raises(ValueError, match="limit"):
         ops.attention_prefill_bf16(b, b[:, :24].contiguous(), pool_b, pool_b, i, one, one[:1], one[:1], one[:1],
                                    1, 1, 24, 1, 0, 1.0)
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (1, 520, 136), (200, 1000, 72), (300, 96, 4096), (2048, 1024, 200),
+                                     (130, 1320, 120)])
+@pytest.mark.parametrize("epilogue", ["bf16", "f32"])
+def test_gemm_tcgen05(m, n, k, epilogue):
+    """The hand-written tcgen05/TMA product against a float32 product of the same bfloat16
+    operands: tails in every dimension (rows, columns, inner size), one row, many tiles."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(m + n + k)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert ops.gemm_tcgen05_supports(a, b)
+    out = ops.gemm_tcgen05(a, b, status, epilogue)
+    want = a.double() @ b.double().t()
+    assert int(status.item()) == 0
+    scale = float(want.abs().max())
+    bound = 1e-5 * scale if epilogue == "f32" else 2 ** -8 * scale
+    assert float((out.double() - want).abs().max()) <= bound
+    # a strided view of a wider matrix (rows 16-byte aligned) is taken as it is
+    wide = torch.zeros((m, k + 8), dtype=torch.bfloat16, device="cuda")
+    wide[:, :k] = a
+    again = ops.gemm_tcgen05(wide[:, :k], b, status, epilogue)
+    assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("m, ff, k", [(128, 128, 64), (257, 200, 120), (2048, 1000, 256), (3, 384, 72)])
+def test_gemm_tcgen05_silu_mul_epilogue(m, ff, k):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(ff)
+    blocks = -(-ff // 128)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    gate = torch.from_numpy(rng.standard_normal((ff, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    up = torch.from_numpy(rng.standard_normal((ff, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    fused = torch.zeros((blocks, 2, 128, k), dtype=torch.bfloat16, device="cuda")
+    for b in range(blocks):
+        rows = min(128, ff - 128 * b)
+        fused[b, 0, :rows] = gate[128 * b:128 * b + rows]
+        fused[b, 1, :rows] = up[128 * b:128 * b + rows]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.gemm_tcgen05(a, fused.view(-1, k), status, "silu_mul", n_out=ff)
+    g, u = (a.float() @ gate.float().t()).cpu().numpy(), (a.float() @ up.float().t()).cpu().numpy()
+    want = plain_model.silu(g) * u
+    assert int(status.item()) == 0 and out.shape == (m, ff)
+    assert np.abs(as_np(out) - want).max() <= 2 ** -8 * np.abs(want).max() + 1e-6
+
+
+def test_gemm_tcgen05_refuses_unaligned_operands():
+    from paged_kv_serving_b200 import ops
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = torch.zeros((4, 36), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((16, 36), dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_tcgen05_supports(a, b)                  # rows of 72 bytes do not start on 16-byte boundaries
+    with pytest.raises(ValueError, match="alignment"):
+        ops.gemm_tcgen05(a, b, status)
+    assert not ops.gemm_tcgen05_supports(a.float(), b.float())  # bfloat16 only
+    a = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((12, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="alignment"):          # 12 bfloat16 columns: output rows of 24 bytes
+        ops.gemm_tcgen05(a, b, status, "bf16")
+    assert ops.gemm_tcgen05(a, b, status, "f32").shape == (4, 12)
 
 
 def test_sampling_kernel_greedy_ties_and_distribution():
