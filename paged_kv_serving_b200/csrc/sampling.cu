@@ -222,3 +222,41 @@ PKV_EXPORT int pkv_sample(const float* logits, long long row_stride, const float
                                                                     probs, out, vocab, greedy_below);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same sampling for callers that cannot allocate: the work area is part of the library image.
+// See sampling_noalloc.h for who needs this and for the rules of use.
+// ---------------------------------------------------------------------------------------------
+#include "sampling_noalloc.h"
+
+// In device code this name is the array itself. In host code it is only a stand-in for it: the
+// device address has to be asked for with cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float pkv_sample_static_area[PKV_SAMPLE_STATIC_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* static_area_of_device[kMaxDevices] = {};
+}  // namespace
+
+PKV_EXPORT int pkv_sample_static_scratch(const float* logits, long long row_stride, const float* temperature,
+                                         const float* top_p, const double* uniform, int32_t* out, int n_rows,
+                                         int vocab, float greedy_below, void* stream) {
+  if (n_rows <= 0) return 0;
+  if (vocab <= 0 || row_stride < vocab) return PKV_ERR_SIZE;
+  if ((long long)n_rows * vocab > (long long)PKV_SAMPLE_STATIC_FLOATS) return PKV_SAMPLE_STATIC_TOO_LARGE;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= kMaxDevices) return PKV_ERR_LIMIT;
+  if (!static_area_of_device[device]) {
+    // set-up, once per device, with that device current
+    float* address = nullptr;
+    e = cudaGetSymbolAddress((void**)&address, pkv_sample_static_area);
+    if (e != cudaSuccess) return (int)e;
+    static_area_of_device[device] = address;
+  }
+  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, temperature, top_p, uniform,
+                                                                    static_area_of_device[device], out, vocab,
+                                                                    greedy_below);
+  return launch_status();
+}

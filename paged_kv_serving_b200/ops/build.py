@@ -49,7 +49,7 @@ def _nvcc() -> str:
 def _source_hash(name: str) -> str:
     digest = hashlib.sha256()
     digest.update(" ".join(NVCC_FLAGS).encode())
-    for path in [CSRC / f"{name}.cu", *sorted(CSRC.glob("*.cuh"))]:
+    for path in [CSRC / f"{name}.cu", *sorted(CSRC.glob("*.cuh")), *sorted(CSRC.glob("*.h"))]:
         digest.update(path.name.encode())
         digest.update(path.read_bytes())
     return digest.hexdigest()[:16]
