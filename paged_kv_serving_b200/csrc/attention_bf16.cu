@@ -20,7 +20,11 @@
 // all 4 warps share, each warp taking 16 keys of every 64-key tile; warps and then splits are
 // merged with the usual (max, sum, accumulator) rule. With more than one split the partial
 // results go through scratch memory and a small merge kernel.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace pkv {
 
@@ -46,6 +50,7 @@ struct AttnParams {
   int n_heads, n_kv, page_size, page_shift, window;   // page_shift: log2(page_size), or -1
   float scale_log2;             // scale * log2(e)
   int num_splits;               // decode only
+  int use_cluster;              // decode only: the splits of one (entry, kv head) are one thread-block cluster
   float* part_o;                // decode scratch [T*H, splits, HD]
   float* part_ml;               // decode scratch [T*H, splits, 2]
 };
@@ -309,6 +314,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
   bf16* k_s = q_s + DEC_ROWS * LD;                    // [2][AT_BN][LD]
   bf16* v_s = k_s + 2 * AT_BN * LD;                   // [2][AT_BN][LD]
   __shared__ float warp_m[4][DEC_ROWS], warp_l[4][DEC_ROWS];
+  __shared__ float part_m[DEC_ROWS], part_l[DEC_ROWS];     // this block's merged state, read by its cluster
 
   const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_a[blockIdx.z];
   const int group = p.n_heads / p.n_kv;
@@ -461,6 +467,12 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     const size_t out_row = (size_t)(tok0 + q_local) * p.n_heads + head;
     if (p.num_splits == 1) {
       p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(l > 0.0f ? acc / l : 0.0f);
+    } else if (p.use_cluster) {
+      reinterpret_cast<float*>(v_s)[row * HD + d] = acc;     // the value tiles are no longer needed
+      if (d == 0) {
+        part_m[row] = m;
+        part_l[row] = l;
+      }
     } else {
       p.part_o[(out_row * p.num_splits + split) * HD + d] = acc;
       if (d == 0) {
@@ -468,6 +480,34 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
         p.part_ml[(out_row * p.num_splits + split) * 2 + 1] = l;
       }
     }
+  }
+  if (p.use_cluster && p.num_splits > 1) {
+    // The splits of this (entry, kv head) are the blocks of one cluster: block 0 folds the others'
+    // states out of their shared memory (distributed shared memory), no scratch, no second kernel.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (split == 0) {
+      float* own_o = reinterpret_cast<float*>(v_s);
+      for (int idx = threadIdx.x; idx < rows_valid * HD; idx += AT_THREADS) {
+        const int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+        for (int r = 0; r < p.num_splits; ++r) m = fmaxf(m, *cluster.map_shared_rank(&part_m[row], r));
+        float l = 0.0f, acc = 0.0f;
+        if (m > -INFINITY) {
+          for (int r = 0; r < p.num_splits; ++r) {
+            const float mr = *cluster.map_shared_rank(&part_m[row], r);
+            if (mr > -INFINITY) {
+              const float f = exp2f(mr - m);
+              l += *cluster.map_shared_rank(&part_l[row], r) * f;
+              acc += *cluster.map_shared_rank(&own_o[row * HD + d], r) * f;
+            }
+          }
+        }
+        const int q_local = row / group, head = kvh * group + row % group;
+        p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(l > 0.0f ? acc / l : 0.0f);
+      }
+    }
+    cluster.sync();     // the others keep their shared memory until block 0 has read it
   }
 }
 
@@ -516,6 +556,22 @@ static int launch_decode(const AttnParams& p, int n_work, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
+  if (p.use_cluster && p.num_splits > 1) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(p.num_splits, p.n_kv, n_work);
+    config.blockDim = dim3(AT_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = s;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = p.num_splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, attention_decode_kernel<HD>, p);
+    return e == cudaSuccess ? launch_status() : (int)e;
+  }
   attention_decode_kernel<HD><<<dim3(p.num_splits, p.n_kv, n_work), AT_THREADS, smem, s>>>(p);
   return launch_status();
 }
@@ -558,6 +614,23 @@ PKV_EXPORT int pkv_attention_bf16_supports(int hd, int q_row_stride) {
 
 PKV_EXPORT int pkv_attention_bf16_rows(int which) { return which == 0 ? AT_BM : DEC_ROWS; }
 
+// How many decode blocks fit on one SM for this head size (0 when the head size is not taken):
+// the host sizes the number of splits so that one wave of blocks covers the work.
+template <int HD> static int decode_blocks_per_sm() {
+  const size_t smem = (size_t)(DEC_ROWS + 4 * AT_BN) * (HD + AT_PAD) * sizeof(bf16);
+  cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int blocks = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<HD>, AT_THREADS, smem) != cudaSuccess) return 0;
+  return blocks;
+}
+
+PKV_EXPORT int pkv_attention_decode_blocks_per_sm(int hd) {
+#define CALL(HD) return decode_blocks_per_sm<HD>()
+  PKV_HD_SWITCH(hd, CALL)
+#undef CALL
+  return 0;
+}
+
 PKV_EXPORT int pkv_attention_prefill_bf16(const void* qkv, int q_row_stride, void* out, const void* k_pool,
                                           const void* v_pool, const int32_t* block_table, int table_stride,
                                           const int32_t* seq_starts, const int32_t* first_pos,
@@ -568,7 +641,7 @@ PKV_EXPORT int pkv_attention_prefill_bf16(const void* qkv, int q_row_stride, voi
   if (bad) return bad;
   AttnParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
                table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size, log2_or_minus1(page_size), window,
-               scale * 1.4426950408889634f, 1, nullptr, nullptr};
+               scale * 1.4426950408889634f, 1, 0, nullptr, nullptr};
   cudaStream_t s = (cudaStream_t)stream;
 #define CALL(HD) return launch_prefill<HD>(p, n_work, s)
   PKV_HD_SWITCH(hd, CALL)
@@ -592,18 +665,20 @@ PKV_EXPORT int pkv_attention_decode_bf16(const void* qkv, int q_row_stride, void
   if (bad) return bad;
   if (num_splits < 1 || num_splits > 65535 || n_work > 65535) return PKV_ERR_LIMIT;
   if (max_entry_tokens * (n_heads / n_kv) > DEC_ROWS) return PKV_ERR_LIMIT;
-  if (num_splits > 1 && !scratch) return PKV_ERR_SIZE;
+  // up to 8 splits (the portable cluster size) merge inside a cluster; more go through scratch
+  const int use_cluster = (num_splits > 1 && num_splits <= 8) ? 1 : 0;
+  if (num_splits > 1 && !use_cluster && !scratch) return PKV_ERR_SIZE;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)total_rows * num_splits * hd : nullptr;
   AttnParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
                table_stride, seq_starts, first_pos, work_seq, nullptr, n_heads, n_kv, page_size, log2_or_minus1(page_size), window,
-               scale * 1.4426950408889634f, num_splits, part_o, part_ml};
+               scale * 1.4426950408889634f, num_splits, use_cluster, part_o, part_ml};
   cudaStream_t s = (cudaStream_t)stream;
   int status = 0;
 #define CALL(HD) status = launch_decode<HD>(p, n_work, s)
   PKV_HD_SWITCH(hd, CALL)
 #undef CALL
-  if (status || num_splits == 1) return status;
+  if (status || num_splits == 1 || use_cluster) return status;
   const int warps = 4;
   const int rows_max = max_entry_tokens * n_heads;
   attention_merge_kernel<<<dim3((rows_max + warps - 1) / warps, n_work), warps * 32, 0, s>>>(

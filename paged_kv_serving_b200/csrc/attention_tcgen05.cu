@@ -1,0 +1,399 @@
+// Paged causal attention for runs of queries (prefill) on the fifth-generation tensor cores.
+//
+// What it computes restates the reference (rouviere-german/paged-kv-serving):
+//   src/paged_kv_serving/engine/attention.py:83-121  scores = q.k * scale, keys after the query's
+//   absolute position masked, online softmax folded tile by tile, output acc / sum;
+//   src/paged_kv_serving/engine/runner.py:198-212    every entry attends over its own block table.
+// Grouped-query heads and an optional window generalise it. attention_bf16.cu (mma.sync) and
+// attention_generic.cu (float32) take the sizes this kernel refuses: it wants bfloat16, a head
+// size of 64 or 128 and a page size that is a multiple of 8.
+//
+// One block handles 128 queries of one sequence for one head and walks the keys in tiles of 128
+// absolute positions (aligned to multiples of 128 from position 0), with six warps:
+//   warp 0     TMA: the query tile from the fused qkv buffer, then for every key tile the pages
+//              the block table names, page by page, into 128-byte-swizzled shared memory (a page
+//              that was given back, or that lies past the last key, is fetched from outside the
+//              pool and arrives as zeros)
+//   warp 1     tcgen05.mma: S = Q.K^T into one of two score buffers in tensor memory, and
+//              O += P.V into the output accumulator (V is read in place, as an N-major operand)
+//   warps 2-5  softmax, one query row per thread: scores from TMEM, mask by position, running
+//              maximum and sum in float32 (log2 domain), probabilities to shared memory as the
+//              bfloat16 A operand of the second product; the accumulator in TMEM is rescaled only
+//              when a row's maximum grew by more than 2^8 since its last rescale; finally O / sum
+// Scores of tile j+1 are computed while the softmax of tile j runs. All hand-overs go through
+// mbarriers whose waits are bounded (status code 2 on a give-up, TMEM freed, no hang).
+#include "tcgen05.cuh"
+
+namespace pkv {
+
+constexpr int FA_BM = 128;        // queries per block
+constexpr int FA_BN = 128;        // keys per tile
+constexpr int FA_THREADS = 192;
+constexpr int FA_TABLE_CACHE = 1024;
+constexpr float FA_RESCALE_STEP = 8.0f;   // log2: rescale the accumulator when the maximum grew by 2^8
+
+struct FaParams {
+  bf16* out;                     // [T, H * HD]
+  const int32_t* block_table;    // [S, table_stride]
+  int table_stride;
+  const int32_t* seq_starts;
+  const int32_t* first_pos;
+  const int32_t* work_seq;       // entry of each work item
+  const int32_t* work_q0;        // first query (inside the entry) of each work item
+  int n_heads, n_kv, page_size, page_shift, window;
+  float scale_log2;
+  int pool_rows;                 // rows of the key/value maps; a row coordinate >= this reads zeros
+  int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+  constexpr int PANELS = HD / 64;                        // 64-column panels of a row of Q, K or V
+  constexpr uint32_t PANEL_BYTES = 128 * 128;            // 128 rows of 128 bytes
+  constexpr uint32_t TILE_BYTES = PANELS * PANEL_BYTES;  // a Q, K or V tile
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t S_COL = 0, O_COL = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = base;
+  uint8_t* k_s = q_s + TILE_BYTES;           // [2][TILE_BYTES]
+  uint8_t* v_s = k_s + 2 * TILE_BYTES;       // [2][TILE_BYTES]
+  uint8_t* p_s = v_s + 2 * TILE_BYTES;       // probabilities: 128 rows x 128 keys, two panels
+  __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ int32_t table_cache[FA_TABLE_CACHE];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x / p.n_heads, head = blockIdx.x - item * p.n_heads;
+  const int kvh = head / (p.n_heads / p.n_kv);
+  const int s = p.work_seq[item], q0 = p.work_q0[item];
+  const int tok0 = p.seq_starts[s];
+  const int n_q = p.seq_starts[s + 1] - tok0;
+  const int pos0 = p.first_pos[s];
+  const int rows_valid = min(FA_BM, n_q - q0);
+  const int qpos_first = pos0 + q0;
+  const int key_hi = qpos_first + rows_valid;                                     // exclusive
+  const int key_lo = p.window > 0 ? max(0, qpos_first - p.window + 1) : 0;
+  const int tile_begin = key_lo / FA_BN, tile_end = (key_hi - 1) / FA_BN;         // inclusive
+  const int n_tiles = tile_end - tile_begin + 1;
+  const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(&p_full, 4);
+    mbar_init(&pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // the block-table entries of this block's key range, read once
+  const int entry_first = p.page_shift >= 0 ? (tile_begin * FA_BN) >> p.page_shift : (tile_begin * FA_BN) / p.page_size;
+  const int entry_last = p.page_shift >= 0 ? (key_hi - 1) >> p.page_shift : (key_hi - 1) / p.page_size;
+  const bool table_cached = entry_last - entry_first + 1 <= FA_TABLE_CACHE;
+  if (table_cached)
+    for (int i = threadIdx.x; i <= entry_last - entry_first; i += FA_THREADS) table_cache[i] = table[entry_first + i];
+  if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* aborted = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, TILE_BYTES);
+      for (int pn = 0; pn < PANELS; ++pn)
+        tma_load_2d(q_s + pn * PANEL_BYTES, &map_q, &q_full, head * HD + 64 * pn, tok0 + q0);
+      const int pages_per_tile = FA_BN / p.page_size;
+      bool ok = true;
+      int loaded_k = 0, loaded_v = 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int stage = j & 1;
+        const int tile_base = (tile_begin + j) * FA_BN;
+        for (int which = 0; which < 2 && ok; ++which) {      // 0: keys, 1: values
+          uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
+          uint64_t* full = which ? &v_full[stage] : &k_full[stage];
+          if (j >= 2 && !mbar_wait(empty, ((j >> 1) - 1) & 1, aborted)) { ok = false; break; }
+          uint8_t* dst = (which ? v_s : k_s) + stage * TILE_BYTES;
+          mbar_expect_tx(full, TILE_BYTES);
+          for (int i = 0; i < pages_per_tile; ++i) {
+            const int pos = tile_base + i * p.page_size;
+            int row = p.pool_rows;                               // outside the pool: zeros
+            if (pos < key_hi && pos + p.page_size > key_lo) {
+              const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+              const int page = table_cached ? table_cache[e - entry_first] : table[e];
+              if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+            }
+            for (int pn = 0; pn < PANELS; ++pn)
+              tma_load_2d(dst + pn * PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
+          }
+          if (which) loaded_v = j + 1; else loaded_k = j + 1;
+        }
+      }
+      if (*aborted) {   // let the copies in flight land before the shared memory is given up
+        const long long start = clock64();
+        while (!mbar_try_wait(&q_full, 0) && clock64() - start < GM_WAIT_CYCLES) {}
+        for (int j = max(0, loaded_k - 2); j < loaded_k; ++j)
+          while (!mbar_try_wait(&k_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
+        for (int j = max(0, loaded_v - 2); j < loaded_v; ++j)
+          while (!mbar_try_wait(&v_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // float32 accumulate, bfloat16 operands, M = 128; scores: N = 128, both operands K-major;
+      // output: N = HD, A (probabilities) K-major, B (values, [key][dim]) N-major
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_BN >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
+      auto issue_scores = [&](int j) {
+        const int stage = j & 1;
+        const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s + stage * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * PANEL_BYTES;
+          umma_bf16(tmem_base + S_COL + stage * FA_BN, umma_desc(q_addr + off) + 2 * (ks & 3),
+                    umma_desc(k_addr + off) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[stage]);
+        umma_commit(&s_full[stage]);
+      };
+      bool ok = mbar_wait(&q_full, 0, aborted) && mbar_wait(&k_full[0], 0, aborted);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          const int next = (j + 1) & 1;
+          ok = mbar_wait(&k_full[next], ((j + 1) >> 1) & 1, aborted);
+          if (ok && j + 1 >= 2) ok = mbar_wait(&s_empty[next], (((j + 1) >> 1) - 1) & 1, aborted);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(j + 1);
+        }
+        ok = mbar_wait(&p_full, j & 1, aborted) && mbar_wait(&v_full[j & 1], (j >> 1) & 1, aborted);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t p_addr = smem_addr(p_s), v_addr = smem_addr(v_s + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ++ks) {
+          umma_bf16(tmem_base + O_COL, umma_desc(p_addr + (ks >> 2) * PANEL_BYTES) + 2 * (ks & 3),
+                    umma_desc_mn(v_addr + ks * 16 * 128, PANEL_BYTES, 1024), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[j & 1]);
+        umma_commit(&pv_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------ softmax and epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qpos = qpos_first + row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float m_ref = -INFINITY, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int buf = j & 1;
+      const int tile_base = (tile_begin + j) * FA_BN;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[buf], (j >> 1) & 1, aborted) ? 1 : 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      float sc[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c) tmem_load32(lane_base + S_COL + buf * FA_BN + c * 32, *reinterpret_cast<float(*)[32]>(&sc[c * 32]));
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);     // the score buffer may be overwritten
+
+      const bool need_mask = tile_base + FA_BN - 1 > qpos_first || tile_base + FA_BN > key_hi ||
+                             (p.window > 0 && tile_base < key_hi - p.window);
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < FA_BN; ++c) {
+        float v = sc[c] * p.scale_log2;
+        if (need_mask) {
+          const int kpos = tile_base + c;
+          const bool visible = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+          v = visible ? v : -INFINITY;
+        }
+        sc[c] = v;
+        tmax = fmaxf(tmax, v);
+      }
+      // the reference maximum moves only when the row's maximum outgrew it by 2^8
+      const bool grow = tmax > m_ref + FA_RESCALE_STEP;
+      const float m_new = grow ? tmax : m_ref;
+      const float alpha = grow ? exp2f(m_ref - m_new) : 1.0f;        // m_ref = -inf gives 0
+      const float shift = m_new == -INFINITY ? 0.0f : m_new;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < FA_BN; ++c) {
+        sc[c] = exp2f(sc[c] - shift);
+        sum += sc[c];
+      }
+      l = l * alpha + sum;
+      m_ref = m_new;
+
+      if (j > 0) {
+        // the previous P.V must be complete: it read the probability buffer and wrote the accumulator
+        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (j - 1) & 1, aborted) ? 1 : 0) != 0;
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow ? 1 : 0)) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            float o[32];
+            tmem_load32(lane_base + O_COL + c * 32, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_store32(lane_base + O_COL + c * 32, o);
+          }
+        }
+      }
+      // probabilities of this row as the bfloat16 A operand: two panels of 64 keys, rows of 128
+      // bytes whose 16-byte chunks are swizzled by the row number
+#pragma unroll
+      for (int c = 0; c < FA_BN / 8; ++c) {
+        uint4 packed;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 pair = __floats2bfloat162_rn(sc[c * 8 + 2 * i], sc[c * 8 + 2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&pair);
+        }
+        const int panel = c >> 3, chunk = c & 7;
+        *reinterpret_cast<uint4*>(p_s + panel * PANEL_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = packed;
+      }
+      if (tile_base + FA_BN > key_hi) {
+        // slots of the last page past the last key may hold anything (0 x NaN = NaN): clear them
+        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[buf], (j >> 1) & 1, aborted) ? 1 : 0) != 0;
+        if (!ok) break;
+        const int r = key_hi - tile_base + (int)threadIdx.x - 64;     // threads 64..191 take one row each
+        if (r < FA_BN)
+          for (int pn = 0; pn < PANELS; ++pn) {
+            uint4* dst = reinterpret_cast<uint4*>(v_s + buf * TILE_BYTES + pn * PANEL_BYTES + r * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+      }
+      fence_async_shared();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (n_tiles - 1) & 1, aborted) ? 1 : 0) != 0;
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      bf16* dst = p.out + (size_t)(tok0 + q0 + row) * ((size_t)p.n_heads * HD) + (size_t)head * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        float o[32];
+        tmem_load32(lane_base + O_COL + c * 32, o);
+        if (row < rows_valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 packed;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 pair = __floats2bfloat162_rn(o[i + 2 * k] * inv, o[i + 2 * k + 1] * inv);
+              w[k] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = packed;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct PoolMapKey {
+  const void* base;
+  long long rows;
+  int hd, box;
+  CUtensorMap map;
+};
+
+static const CUtensorMap* pool_map(const void* base, long long rows, int hd, int box_rows) {
+  static PoolMapKey cache[512];
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) return &cache[i].map;
+  PoolMapKey& slot = cache[used < 512 ? used : 511];
+  if (make_tile_map(&slot.map, base, rows, hd, hd, box_rows)) return nullptr;
+  slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows;
+  if (used < 512) ++used;
+  return &slot.map;
+}
+
+template <int HD>
+static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
+                     cudaStream_t s) {
+  const size_t smem = (size_t)(HD / 64) * 128 * 128 * 5 + 2 * 128 * 128 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attention_tcgen05_kernel<HD><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
+  return launch_status();
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+// 1 when this kernel takes the sizes, 0 when another attention kernel must be used.
+PKV_EXPORT int pkv_attention_tcgen05_supports(int hd, int page_size, int q_row_stride) {
+  return ((hd == 64 || hd == 128) && page_size >= 8 && page_size % 8 == 0 && FA_BN % page_size == 0 &&
+          q_row_stride % 8 == 0) ? 1 : 0;
+}
+
+PKV_EXPORT int pkv_attention_tcgen05_rows() { return FA_BM; }
+
+PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, int n_tokens, void* out,
+                                             const void* k_pool, const void* v_pool, long long n_pages,
+                                             const int32_t* block_table, int table_stride, const int32_t* seq_starts,
+                                             const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
+                                             int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
+                                             float scale, int* status, void* stream) {
+  if (n_work <= 0) return 0;
+  if (!pkv_attention_tcgen05_supports(hd, page_size, q_row_stride)) return PKV_ERR_LIMIT;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0) return PKV_ERR_SIZE;
+  const long long pool_rows = n_pages * n_kv * page_size;
+  if (pool_rows >= (1LL << 31) - page_size || (long long)n_work * n_heads >= (1LL << 31)) return PKV_ERR_LIMIT;
+  if ((uintptr_t)qkv % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16) return PKV_ERR_ALIGN;
+  alignas(64) CUtensorMap map_q;
+  int r = make_tile_map(&map_q, qkv, n_tokens, q_row_stride, q_row_stride, FA_BM);
+  if (r) return r;
+  const CUtensorMap* map_k = pool_map(k_pool, pool_rows, hd, page_size);
+  const CUtensorMap* map_v = pool_map(v_pool, pool_rows, hd, page_size);
+  if (!map_k || !map_v) return PKV_ERR_SIZE;
+  int shift = -1;
+  for (int i = 0; i < 31; ++i)
+    if ((1 << i) == page_size) shift = i;
+  FaParams p{(bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size,
+             shift, window, scale * 1.4426950408889634f, (int)pool_rows, status};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 128) return launch_fa<128>(map_q, *map_k, *map_v, p, n_work, s);
+  return launch_fa<64>(map_q, *map_k, *map_v, p, n_work, s);
+}

@@ -21,9 +21,7 @@
 // Every wait on an mbarrier is bounded: after about a second without progress a block records
 // an error code in the status word, lets its copies in flight land (again bounded), frees its
 // TMEM and returns, so a fault in the hand-over can never hang the GPU.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace pkv {
 
@@ -31,99 +29,9 @@ constexpr int GM_BM = 128;
 constexpr int GM_BK = 64;                    // 64 bf16 = 128 bytes = one swizzle row
 constexpr int GM_THREADS = 192;
 constexpr int GM_UMMA_K = 16;
-constexpr long long GM_WAIT_CYCLES = 2000000000LL;   // about one second at 2 GHz
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2 };
 enum { GEMM_ERR_TIMEOUT = 2 };
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
-  return done != 0;
-}
-// Bounded wait: false when the block gave up (its own limit ran out, or another role did).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  const long long start = clock64();
-  for (uint32_t spin = 0;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0xff) == 0xff) {
-      if (*abort_flag) return false;
-      if (clock64() - start > GM_WAIT_CYCLES) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c_inner, int c_outer) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c_inner), "r"(c_outer)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(columns));
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns));
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled by 128
-// bytes: groups of 8 rows are 1024 bytes apart (stride offset), the leading offset is unused.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3ffff) >> 4);          // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                            // leading byte offset (unused for this layout)
-  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset: 8 rows x 128 bytes
-  d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                            // 128-byte swizzle
-  return d;
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 __device__ __forceinline__ float silu_clipped(float x, float clip) {
   const float c = fminf(fmaxf(x, -clip), clip);
@@ -163,9 +71,6 @@ __device__ __forceinline__ void store_chunk(void* out, int ldo, int row, int col
   }
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
 
 // Persistent: each block walks over output tiles (row blocks fastest, so that the blocks in
 // flight share a few tiles of B, the weights, while all of A stays in L2). Two accumulators in
@@ -309,37 +214,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // -----------------------------------------------------------------------------------------------
 // host side
 // -----------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// A [rows, cols] bfloat16 matrix with `ld` elements between rows, fetched in boxes of
-// [box_rows, 64] with the 128-byte swizzle. Outside the matrix a box is filled with zeros.
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_tiled();
-  if (!fn) return PKV_ERR_LIMIT;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)GM_BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : PKV_ERR_SIZE;
-}
-
 template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int n_tiles_cols,
                        int n_valid, int K, float clip, int* status, cudaStream_t s) {
@@ -384,23 +258,23 @@ PKV_EXPORT int pkv_gemm_tcgen05(const void* a, int lda, const void* b, int ldb, 
   if (lda < K || ldb < K) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   alignas(64) CUtensorMap map_a, map_b;
-  int r = make_map(&map_a, a, M, K, lda, GM_BM);
+  int r = make_tile_map(&map_a, a, M, K, lda, GM_BM);
   if (r) return r;
   if (epilogue == EPI_SILU_MUL) {
     if (N % 256 || n_out <= 0 || n_out > N / 2 || ldo % 8 || (uintptr_t)out % 16) return PKV_ERR_SIZE;
-    r = make_map(&map_b, b, N, K, ldb, 256);
+    r = make_tile_map(&map_b, b, N, K, ldb, 256);
     if (r) return r;
     return launch_gemm<256, 4, EPI_SILU_MUL>(map_a, map_b, out, ldo, M, N / 256, n_out, K, clip, status, s);
   }
   if (epilogue == EPI_BF16) {
     if (ldo % 8 || (uintptr_t)out % 16) return PKV_ERR_ALIGN;
-    r = make_map(&map_b, b, N, K, ldb, 256);
+    r = make_tile_map(&map_b, b, N, K, ldb, 256);
     if (r) return r;
     return launch_gemm<256, 4, EPI_BF16>(map_a, map_b, out, ldo, M, (N + 255) / 256, N, K, clip, status, s);
   }
   if (epilogue == EPI_F32) {
     if (ldo % 4 || (uintptr_t)out % 16) return PKV_ERR_ALIGN;
-    r = make_map(&map_b, b, N, K, ldb, 256);
+    r = make_tile_map(&map_b, b, N, K, ldb, 256);
     if (r) return r;
     return launch_gemm<256, 4, EPI_F32>(map_a, map_b, out, ldo, M, (N + 255) / 256, N, K, clip, status, s);
   }

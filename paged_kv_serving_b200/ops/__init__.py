@@ -16,7 +16,9 @@ from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
     "add_rmsnorm", "attention_bf16_rows", "attention_bf16_supports", "attention_decode_bf16",
-    "attention_prefill_bf16", "attention_rows_per_block", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports",
+    "attention_decode_blocks_per_sm",
+    "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
+    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports",
     "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
 ]
 
@@ -218,6 +220,53 @@ def attention_bf16_rows() -> tuple[int, int]:
     return int(lib.pkv_attention_bf16_rows(0)), int(lib.pkv_attention_bf16_rows(1))
 
 
+def attention_tcgen05_supports(head_dim: int, page_size: int, q_row_stride: int) -> bool:
+    """Whether the tcgen05 prefill attention takes these sizes (head 64 or 128, pages of 8k keys)."""
+    lib = library("attention_tcgen05")
+    lib.pkv_attention_tcgen05_supports.restype = c_int
+    lib.pkv_attention_tcgen05_supports.argtypes = [c_int, c_int, c_int]
+    return bool(lib.pkv_attention_tcgen05_supports(int(head_dim), int(page_size), int(q_row_stride)))
+
+
+def attention_tcgen05_rows() -> int:
+    lib = library("attention_tcgen05")
+    lib.pkv_attention_tcgen05_rows.restype = c_int
+    return int(lib.pkv_attention_tcgen05_rows())
+
+
+def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                              block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
+                              work_seq: torch.Tensor, work_q0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                              page_size: int, window: int, scale: float, status: torch.Tensor) -> None:
+    """Prefill attention on tcgen05 tensor cores with TMA page loads; writes the rows of its work
+    items (blocks of 128 queries) into ``out``."""
+    for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("work_q0", work_q0), ("status", status)):
+        _need(t, torch.int32, name)
+    fn = _fn("attention_tcgen05", "pkv_attention_prefill_tcgen05",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], qkv.shape[0], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0],
+              _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq),
+              _ptr(work_q0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), float(scale),
+              _ptr(status), _stream()), "attention_prefill_tcgen05")
+
+
+_DECODE_BLOCKS: dict[int, int] = {}
+
+
+def attention_decode_blocks_per_sm(head_dim: int) -> int:
+    """Decode-attention blocks that fit on one SM at this head size (for sizing the key splits)."""
+    if head_dim not in _DECODE_BLOCKS:
+        lib = library("attention_bf16")
+        lib.pkv_attention_decode_blocks_per_sm.restype = c_int
+        lib.pkv_attention_decode_blocks_per_sm.argtypes = [c_int]
+        _DECODE_BLOCKS[head_dim] = max(1, int(lib.pkv_attention_decode_blocks_per_sm(int(head_dim))))
+    return _DECODE_BLOCKS[head_dim]
+
+
 def attention_prefill_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                            block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
                            work_seq: torch.Tensor, work_q0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
@@ -250,7 +299,7 @@ def attention_decode_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Te
                     ("work_seq", work_seq)):
         _need(t, torch.int32, name)
     total_rows = qkv.shape[0] * n_heads
-    if num_splits > 1:
+    if num_splits > 8:     # up to 8 splits merge inside a thread-block cluster and need no scratch
         _need(scratch, torch.float32, "scratch")
         if scratch.numel() < total_rows * num_splits * (head_dim + 2):
             raise ValueError("attention scratch is too small for this many splits")
@@ -261,7 +310,7 @@ def attention_decode_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Te
               block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), work_seq.numel(),
               int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(num_splits),
               _ptr(scratch), total_rows, _stream()), "attention_decode_bf16")
-    if num_splits > 1:
+    if num_splits > 8:
         LAUNCHES["count"] += 1   # the merge kernel
 
 

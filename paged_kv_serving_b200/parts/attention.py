@@ -62,6 +62,7 @@ class PagedAttention(Part):
         self.qkv_proj: torch.Tensor | None = None
         self.out_proj: torch.Tensor | None = None
         self._fast_ok: bool | None = None
+        self._tcgen05_ok: dict[int, bool] = {}
 
     @property
     def group_size(self) -> int:
@@ -96,14 +97,32 @@ class PagedAttention(Part):
             self._fast_ok = ops.attention_bf16_supports(self.head_dim, qkv_width)
         return self._fast_ok
 
-    def _plan_fast(self, ctx: StepContext) -> None:
+    #: Set to False to keep runs of queries on the mma.sync kernel (tests compare the two).
+    USE_TCGEN05 = True
+
+    def _tcgen05(self, page_size: int) -> bool:
+        """Whether runs of queries go to the tcgen05 kernel (head 64 or 128, pages of 8k keys)."""
+        if not self.USE_TCGEN05:
+            return False
+        key = page_size
+        if key not in self._tcgen05_ok:
+            qkv_width = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+            self._tcgen05_ok[key] = ops.attention_tcgen05_supports(self.head_dim, page_size, qkv_width)
+        return self._tcgen05_ok[key]
+
+    def _fast_key(self, page_size: int) -> str:
+        return f"attention/fast/g{self.group_size}/{'t' if self._tcgen05(page_size) else 'm'}"
+
+    def _plan_fast(self, ctx: StepContext, page_size: int) -> None:
         """Work lists of the bfloat16 kernels: entries of at most 16 rows per key/value head go
-        to the split-KV decode kernel, longer ones are cut into blocks of 64 queries for the
-        prefill kernel (heaviest blocks first)."""
-        key = f"attention/fast/g{self.group_size}"
+        to the split-KV decode kernel, longer ones are cut into blocks of queries (128 for the
+        tcgen05 kernel, 64 for the mma.sync one) for the prefill kernel, heaviest blocks first."""
+        key = self._fast_key(page_size)
         if key in ctx.scratch:
             return
         block_rows, decode_rows = ops.attention_bf16_rows()
+        if self._tcgen05(page_size):
+            block_rows = ops.attention_tcgen05_rows()
         lens = np.asarray(ctx.seq_lens, dtype=np.int64)
         first = np.asarray(ctx.first_positions, dtype=np.int64)
         small = lens * self.group_size <= decode_rows
@@ -120,9 +139,12 @@ class PagedAttention(Part):
             longest = int((first[decode_entries] + lens[decode_entries]).max())
             if ctx.planning_context_len is not None:
                 longest = ctx.planning_context_len
+            # as many splits of the key range as still run in one wave of blocks, at most 8 (the
+            # splits of an entry form one thread-block cluster) and at most one per 64-key tile
             tiles = max(1, -(-longest // 64))
             blocks_per_split = len(decode_entries) * self.n_kv_heads
-            num_splits = int(min(tiles, 32, max(1, -(-2 * _sm_count(ctx.device) // blocks_per_split))))
+            resident = ops.attention_decode_blocks_per_sm(self.head_dim) * _sm_count(ctx.device)
+            num_splits = int(max(1, min(tiles, 8, resident // blocks_per_split)))
         names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq")}
         ctx.arena.add(names["prefill_seq"], work_seq[order] if len(order) else [0])
         ctx.arena.add(names["prefill_q0"], work_q0[order] if len(order) else [0])
@@ -135,7 +157,7 @@ class PagedAttention(Part):
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
         if self._fast(ctx):
-            self._plan_fast(ctx)
+            self._plan_fast(ctx, ctx.groups[binding.group].page_size)
             return
         seq_name, row_name = self._work_names()
         if seq_name in ctx.arena:
@@ -175,18 +197,23 @@ class PagedAttention(Part):
         return gemm.linear(attended, self.out_proj)
 
     def _attend_fast(self, qkv, ctx: StepContext, group, k_pool, v_pool) -> torch.Tensor:
-        plan = ctx.scratch[f"attention/fast/g{self.group_size}"]
+        plan = ctx.scratch[self._fast_key(group.page_size)]
         names = plan["names"]
         out = torch.empty((qkv.shape[0], self.n_heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
         table, starts, first = ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS)
-        if plan["n_prefill"]:
+        if plan["n_prefill"] and self._tcgen05(group.page_size):
+            ops.attention_prefill_tcgen05(qkv, out, k_pool, v_pool, table, starts, first,
+                                          ctx.ints(names["prefill_seq"]), ctx.ints(names["prefill_q0"]), self.n_heads,
+                                          self.n_kv_heads, self.head_dim, group.page_size, self.window or 0,
+                                          self.scale, ops.status_word(qkv.device))
+        elif plan["n_prefill"]:
             ops.attention_prefill_bf16(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["prefill_seq"]),
                                        ctx.ints(names["prefill_q0"]), self.n_heads, self.n_kv_heads, self.head_dim,
                                        group.page_size, self.window or 0, self.scale)
         if plan["n_decode"]:
             splits = plan["num_splits"]
             scratch = None
-            if splits > 1:
+            if splits > 8:
                 size = qkv.shape[0] * self.n_heads * splits * (self.head_dim + 2)
                 scratch = ctx.scratch.get("attention/split_scratch")
                 if scratch is None or scratch.numel() < size:

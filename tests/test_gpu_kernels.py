@@ -146,7 +146,8 @@ def test_rope_kv_store(dtype, heads, kv, hd):
     assert np.array_equal(as_np(k_pool)[p, :, o], k[0])
 
 
-def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True, fast=False, splits=1):
+def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True, fast=False, splits=1,
+                    tcgen05=False):
     """Random sequences already in the cache (``contexts`` tokens each), of which the last
     ``queries`` tokens are this step's queries. Returns device inputs and the plain answer."""
     from paged_kv_serving_b200 import ops
@@ -190,13 +191,22 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
     group = heads // kv
     if fast:
         block_rows, decode_rows = ops.attention_bf16_rows()
+        if tcgen05:
+            block_rows = ops.attention_tcgen05_rows()
         out = torch.full((q_all.shape[0], heads * hd), float("nan"), dtype=torch_dtype, device="cuda")
         small = [s for s, n_q in enumerate(queries) if n_q * group <= decode_rows]
         large = [(s, q0) for s, n_q in enumerate(queries) if n_q * group > decode_rows for q0 in range(0, n_q, block_rows)]
         common = (dev(np.stack(tables).astype(np.int32)), dev(np.asarray(starts, dtype=np.int32)),
                   dev(np.asarray(firsts, dtype=np.int32)))
         qkv_d = dev(qkv, torch_dtype)
-        if large:
+        if large and tcgen05:
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            ops.attention_prefill_tcgen05(qkv_d, out, k_pool, v_pool, *common,
+                                          dev(np.asarray([s for s, _ in large], dtype=np.int32)),
+                                          dev(np.asarray([q for _, q in large], dtype=np.int32)),
+                                          heads, kv, hd, page, window or 0, 1.0 / math.sqrt(hd), status)
+            assert int(status.item()) == 0
+        elif large:
             ops.attention_prefill_bf16(qkv_d, out, k_pool, v_pool, *common,
                                        dev(np.asarray([s for s, _ in large], dtype=np.int32)),
                                        dev(np.asarray([q for _, q in large], dtype=np.int32)),
@@ -205,7 +215,7 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
             scratch = torch.full((q_all.shape[0] * heads * splits * (hd + 2),), float("nan"), device="cuda")
             ops.attention_decode_bf16(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
                                       max(queries[s] for s in small), heads, kv, hd, page, window or 0,
-                                      1.0 / math.sqrt(hd), splits, scratch if splits > 1 else None)
+                                      1.0 / math.sqrt(hd), splits, scratch if splits > 8 else None)
         return as_np(out), np.concatenate(wants)
     rows_per_block = ops.attention_rows_per_block()
     work_seq, work_row0 = [], []
@@ -241,7 +251,7 @@ def test_paged_attention_window_edges(dtype, window):
     assert np.abs(got - want).max() <= tol(dtype, 2)
 
 
-@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("splits", [1, 3, 8, 11])
 @pytest.mark.parametrize("heads, kv, hd, page", [(8, 1, 16, 1), (6, 2, 48, 4), (3, 3, 128, 16), (32, 8, 128, 16),
                                                    (16, 2, 64, 8), (9, 3, 80, 5), (4, 4, 112, 3), (8, 4, 32, 16),
                                                    (10, 2, 96, 7)])
@@ -253,6 +263,34 @@ def test_attention_bf16_tensor_core_kernels(heads, kv, hd, page, splits):
     got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
                                 contexts=[300, 1, 65, 33, 128, 200, 64, 513], queries=[1, 1, 65, 2, 17, 150, 64, 1],
                                 dtype="bfloat16", fast=True, splits=splits)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("heads, kv, hd, page", [(32, 8, 128, 16), (3, 3, 128, 8), (16, 2, 64, 8), (4, 4, 64, 32),
+                                                   (6, 1, 128, 128)])
+def test_attention_tcgen05_prefill(heads, kv, hd, page):
+    """The tcgen05/TMA prefill kernel: runs of 17 to 513 queries, block edges at 128 and 129
+    queries, a run deep inside its context, partial last pages filled with NaN, one far key that
+    dominates the last query; short entries go to the decode kernel in the same batch."""
+    from paged_kv_serving_b200 import ops
+
+    assert ops.attention_tcgen05_supports(hd, page, (heads + 2 * kv) * hd)
+    assert not ops.attention_tcgen05_supports(48, 16, 144) and not ops.attention_tcgen05_supports(128, 4, 384)
+    rng = np.random.default_rng(hd + page)
+    got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
+                                contexts=[300, 1, 129, 33, 128, 700, 513, 1000], queries=[100, 1, 129, 17, 128, 150, 513, 2],
+                                dtype="bfloat16", fast=True, splits=2, tcgen05=True)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("window", [1, 63, 128, 129, 300])
+def test_attention_tcgen05_prefill_window_edges(window):
+    rng = np.random.default_rng(window)
+    got, want = _attention_case(rng, heads=4, kv=2, hd=64, page=8, window=window,
+                                contexts=[400, 128, 31, 640], queries=[200, 128, 31, 300],
+                                dtype="bfloat16", fast=True, splits=2, tcgen05=True)
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 
