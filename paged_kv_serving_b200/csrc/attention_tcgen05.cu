@@ -46,6 +46,12 @@ struct FaParams {
   int* status;
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -109,44 +115,52 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (warp == 0) {
     // ------------------------------------------------------------------------ TMA producer
+    // Lane 0 waits for a free slot and announces the bytes; then every lane issues one box
+    // (one page of one 64-column panel), so the many small copies of a tile start together.
     if (lane == 0) {
       mbar_expect_tx(&q_full, TILE_BYTES);
       for (int pn = 0; pn < PANELS; ++pn)
         tma_load_2d(q_s + pn * PANEL_BYTES, &map_q, &q_full, head * HD + 64 * pn, tok0 + q0);
-      const int pages_per_tile = FA_BN / p.page_size;
-      bool ok = true;
-      int loaded_k = 0, loaded_v = 0;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int stage = j & 1;
-        const int tile_base = (tile_begin + j) * FA_BN;
-        for (int which = 0; which < 2 && ok; ++which) {      // 0: keys, 1: values
-          uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
-          uint64_t* full = which ? &v_full[stage] : &k_full[stage];
-          if (j >= 2 && !mbar_wait(empty, ((j >> 1) - 1) & 1, aborted)) { ok = false; break; }
-          uint8_t* dst = (which ? v_s : k_s) + stage * TILE_BYTES;
-          mbar_expect_tx(full, TILE_BYTES);
-          for (int i = 0; i < pages_per_tile; ++i) {
-            const int pos = tile_base + i * p.page_size;
-            int row = p.pool_rows;                               // outside the pool: zeros
-            if (pos < key_hi && pos + p.page_size > key_lo) {
-              const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-              const int page = table_cached ? table_cache[e - entry_first] : table[e];
-              if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
-            }
-            for (int pn = 0; pn < PANELS; ++pn)
-              tma_load_2d(dst + pn * PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
-          }
-          if (which) loaded_v = j + 1; else loaded_k = j + 1;
+    }
+    const int pages_per_tile = FA_BN / p.page_size;
+    const int boxes = pages_per_tile * PANELS;
+    bool ok = true;
+    int loaded_k = 0, loaded_v = 0;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int stage = j & 1;
+      const int tile_base = (tile_begin + j) * FA_BN;
+      for (int which = 0; which < 2 && ok; ++which) {      // 0: keys, 1: values
+        uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
+        uint64_t* full = which ? &v_full[stage] : &k_full[stage];
+        if (lane == 0) {
+          if (j >= 2 && !mbar_wait(empty, ((j >> 1) - 1) & 1, aborted)) ok = false;
+          if (ok) mbar_expect_tx(full, TILE_BYTES);
         }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        uint8_t* dst = (which ? v_s : k_s) + stage * TILE_BYTES;
+        for (int b = lane; b < boxes; b += 32) {
+          const int i = b / PANELS, pn = b - i * PANELS;
+          const int pos = tile_base + i * p.page_size;
+          int row = p.pool_rows;                               // outside the pool: zeros
+          if (pos < key_hi && pos + p.page_size > key_lo) {
+            const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+            const int page = table_cached ? table_cache[e - entry_first] : table[e];
+            if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+          }
+          tma_load_2d(dst + pn * PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
+        }
+        __syncwarp();
+        if (which) loaded_v = j + 1; else loaded_k = j + 1;
       }
-      if (*aborted) {   // let the copies in flight land before the shared memory is given up
-        const long long start = clock64();
-        while (!mbar_try_wait(&q_full, 0) && clock64() - start < GM_WAIT_CYCLES) {}
-        for (int j = max(0, loaded_k - 2); j < loaded_k; ++j)
-          while (!mbar_try_wait(&k_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
-        for (int j = max(0, loaded_v - 2); j < loaded_v; ++j)
-          while (!mbar_try_wait(&v_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
-      }
+    }
+    if (lane == 0 && *aborted) {   // let the copies in flight land before the shared memory is given up
+      const long long start = clock64();
+      while (!mbar_try_wait(&q_full, 0) && clock64() - start < GM_WAIT_CYCLES) {}
+      for (int j = max(0, loaded_k - 2); j < loaded_k; ++j)
+        while (!mbar_try_wait(&k_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
+      for (int j = max(0, loaded_v - 2); j < loaded_v; ++j)
+        while (!mbar_try_wait(&v_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------ MMA issuer
@@ -210,36 +224,51 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       tc_fence_after();
       float sc[FA_BN];
 #pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c) tmem_load32(lane_base + S_COL + buf * FA_BN + c * 32, *reinterpret_cast<float(*)[32]>(&sc[c * 32]));
+      for (int c = 0; c < FA_BN / 32; ++c)
+        tmem_load32_nowait(lane_base + S_COL + buf * FA_BN + c * 32, *reinterpret_cast<float(*)[32]>(&sc[c * 32]));
+      tmem_load_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[buf]);     // the score buffer may be overwritten
 
       const bool need_mask = tile_base + FA_BN - 1 > qpos_first || tile_base + FA_BN > key_hi ||
                              (p.window > 0 && tile_base < key_hi - p.window);
+      // maximum of the raw scores (the scale is positive, so it can be applied to the maximum)
       float tmax = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < FA_BN; ++c) {
-        float v = sc[c] * p.scale_log2;
-        if (need_mask) {
+        for (int c = 0; c < FA_BN; ++c) {
           const int kpos = tile_base + c;
           const bool visible = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
-          v = visible ? v : -INFINITY;
+          sc[c] = visible ? sc[c] : -INFINITY;
+          tmax = fmaxf(tmax, sc[c]);
         }
-        sc[c] = v;
-        tmax = fmaxf(tmax, v);
+      } else {
+        float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < FA_BN; c += 4) {
+          t0 = fmaxf(t0, sc[c]); t1 = fmaxf(t1, sc[c + 1]); t2 = fmaxf(t2, sc[c + 2]); t3 = fmaxf(t3, sc[c + 3]);
+        }
+        tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
       }
+      tmax *= p.scale_log2;
       // the reference maximum moves only when the row's maximum outgrew it by 2^8
       const bool grow = tmax > m_ref + FA_RESCALE_STEP;
       const float m_new = grow ? tmax : m_ref;
       const float alpha = grow ? exp2f(m_ref - m_new) : 1.0f;        // m_ref = -inf gives 0
-      const float shift = m_new == -INFINITY ? 0.0f : m_new;
-      float sum = 0.0f;
+      const float neg_shift = m_new == -INFINITY ? 0.0f : -m_new;
+      float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-      for (int c = 0; c < FA_BN; ++c) {
-        sc[c] = exp2f(sc[c] - shift);
-        sum += sc[c];
+      for (int c = 0; c < FA_BN; c += 4) {
+        // p = 2^(score * scale - max): one multiply-add and one ex2 per element; a masked score
+        // (-inf) gives exactly 0
+        sc[c] = ex2_approx(fmaf(sc[c], p.scale_log2, neg_shift));
+        sc[c + 1] = ex2_approx(fmaf(sc[c + 1], p.scale_log2, neg_shift));
+        sc[c + 2] = ex2_approx(fmaf(sc[c + 2], p.scale_log2, neg_shift));
+        sc[c + 3] = ex2_approx(fmaf(sc[c + 3], p.scale_log2, neg_shift));
+        s0 += sc[c]; s1 += sc[c + 1]; s2 += sc[c + 2]; s3 += sc[c + 3];
       }
+      const float sum = (s0 + s1) + (s2 + s3);
       l = l * alpha + sum;
       m_ref = m_new;
 
