@@ -488,23 +488,40 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     cluster.sync();
     if (split == 0) {
       float* own_o = reinterpret_cast<float*>(v_s);
+      // per row: the weight of every split's accumulator, exp2(m_r - M) / L, computed once
+      __shared__ float weight[8][DEC_ROWS];
+      if (threadIdx.x < rows_valid) {
+        const int row = threadIdx.x;
+        float mr[8], lr[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          mr[r] = r < p.num_splits ? *cluster.map_shared_rank(&part_m[row], r) : -INFINITY;
+          lr[r] = r < p.num_splits ? *cluster.map_shared_rank(&part_l[row], r) : 0.0f;
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) m = fmaxf(m, mr[r]);
+        float l = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          mr[r] = mr[r] > -INFINITY ? exp2f(mr[r] - m) : 0.0f;
+          l += lr[r] * mr[r];
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) weight[r][row] = mr[r] * inv;
+      }
+      __syncthreads();
       for (int idx = threadIdx.x; idx < rows_valid * HD; idx += AT_THREADS) {
         const int row = idx / HD, d = idx - row * HD;
-        float m = -INFINITY;
-        for (int r = 0; r < p.num_splits; ++r) m = fmaxf(m, *cluster.map_shared_rank(&part_m[row], r));
-        float l = 0.0f, acc = 0.0f;
-        if (m > -INFINITY) {
-          for (int r = 0; r < p.num_splits; ++r) {
-            const float mr = *cluster.map_shared_rank(&part_m[row], r);
-            if (mr > -INFINITY) {
-              const float f = exp2f(mr - m);
-              l += *cluster.map_shared_rank(&part_l[row], r) * f;
-              acc += *cluster.map_shared_rank(&own_o[row * HD + d], r) * f;
-            }
-          }
-        }
+        float part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) part[r] = r < p.num_splits ? *cluster.map_shared_rank(&own_o[row * HD + d], r) : 0.0f;
+        float acc = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) acc += part[r] * weight[r][row];
         const int q_local = row / group, head = kvh * group + row % group;
-        p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(l > 0.0f ? acc / l : 0.0f);
+        p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(acc);
       }
     }
     cluster.sync();     // the others keep their shared memory until block 0 has read it

@@ -1,0 +1,455 @@
+// Split-KV decode attention fed by TMA: the memory-bound twin of the decode kernel in
+// attention_bf16.cu for the common sizes (bfloat16, head size 64 or 128, pages of 8k keys).
+//
+// What it computes restates the reference (rouviere-german/paged-kv-serving,
+// src/paged_kv_serving/engine/attention.py:83-121): scores = q.k * scale, keys after the query's
+// absolute position masked, online softmax folded tile by tile, output acc / sum; every entry
+// over its own block table (src/paged_kv_serving/engine/runner.py:198-212).
+//
+// A decode step reads each cached key and value once and does little arithmetic on it, so the
+// kernel is built around keeping many bytes in flight per SM. One block per (split of the key
+// range, key/value head, entry): a producer warp walks the block table and issues one TMA box per
+// page and 64-column panel into a ring of up to six 64-key stages (128-byte swizzle, completion on
+// mbarriers); four consumer warps each take 16 keys of every stage with mma.sync (the at most 16
+// (query token, head in group) rows of the entry form one MMA row tile), keep their own running
+// (maximum, sum, accumulator) and hand the stage back. Warps are merged through shared memory,
+// the splits of one entry through the shared memory of their thread-block cluster.
+// Every mbarrier wait is bounded; a give-up sets status code 2 and the block leaves in order.
+#include <cooperative_groups.h>
+
+#include "tcgen05.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace pkv {
+
+constexpr int DT_BN = 64;          // keys per stage
+constexpr int DT_ROWS = 16;        // rows of an entry per key/value head
+constexpr int DT_THREADS = 160;    // four consumer warps and one producer warp
+constexpr int DT_TABLE_CACHE = 512;
+
+struct DecTmaParams {
+  const bf16* qkv;
+  int q_row_stride;
+  bf16* out;
+  const int32_t* block_table;
+  int table_stride;
+  const int32_t* seq_starts;
+  const int32_t* first_pos;
+  const int32_t* work_seq;
+  int n_heads, n_kv, page_size, page_shift, window;
+  float scale_log2;
+  int num_splits;
+  int pool_rows;
+  int* status;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(DT_THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const DecTmaParams p) {
+  constexpr int PANELS = HD / 64;
+  constexpr uint32_t PANEL_BYTES = DT_BN * 128;                 // 64 keys x 128 bytes
+  constexpr uint32_t HALF_BYTES = PANELS * PANEL_BYTES;         // the keys (or the values) of a stage
+  constexpr uint32_t STAGE_BYTES = 2 * HALF_BYTES;
+  constexpr int KSTEPS = HD / 16;
+  constexpr int DTILES = HD / 8;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
+  __shared__ float warp_m[4][DT_ROWS], warp_l[4][DT_ROWS];
+  __shared__ float part_m[DT_ROWS], part_l[DT_ROWS];
+  __shared__ int32_t table_cache[DT_TABLE_CACHE];
+  __shared__ int abort_flag;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_seq[blockIdx.z];
+  const int group = p.n_heads / p.n_kv;
+  const int tok0 = p.seq_starts[s];
+  const int n_q = p.seq_starts[s + 1] - tok0;
+  const int pos0 = p.first_pos[s];
+  const int rows_valid = n_q * group;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int key_hi = pos0 + n_q;
+  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int tile_first = key_lo / DT_BN, tile_last = (key_hi - 1) / DT_BN;
+  const int tiles_per_split = (tile_last - tile_first + p.num_splits) / p.num_splits;
+  const int tile_begin = tile_first + split * tiles_per_split;
+  const int tile_end = min(tile_last, tile_begin + tiles_per_split - 1);
+  const int n_tiles = max(0, tile_end - tile_begin + 1);
+  const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 4);          // one arrival per consumer warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const int entry_first = n_tiles ? (p.page_shift >= 0 ? (tile_begin * DT_BN) >> p.page_shift : (tile_begin * DT_BN) / p.page_size) : 0;
+  const int entry_last = n_tiles ? (p.page_shift >= 0 ? (min(key_hi, (tile_end + 1) * DT_BN) - 1) >> p.page_shift
+                                                      : (min(key_hi, (tile_end + 1) * DT_BN) - 1) / p.page_size) : -1;
+  const bool table_cached = entry_last - entry_first + 1 <= DT_TABLE_CACHE;
+  if (table_cached)
+    for (int i = threadIdx.x; i <= entry_last - entry_first; i += DT_THREADS) table_cache[i] = table[entry_first + i];
+  __syncthreads();
+  volatile int* aborted = &abort_flag;
+
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------------ producer
+    const int pages_per_tile = DT_BN / p.page_size;
+    const int boxes = pages_per_tile * PANELS * 2;      // keys and values
+    bool ok = true;
+    int issued = 0;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int stage = j % STAGES;
+      if (lane == 0) {
+        if (j >= STAGES && !mbar_wait(&empty_bar[stage], ((j / STAGES) - 1) & 1, aborted)) ok = false;
+        if (ok) mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const int tile_base = (tile_begin + j) * DT_BN;
+      uint8_t* dst = ring + (size_t)stage * STAGE_BYTES;
+      for (int b = lane; b < boxes; b += 32) {
+        const int which = b / (pages_per_tile * PANELS);          // 0: keys, 1: values
+        const int rest = b - which * pages_per_tile * PANELS;
+        const int i = rest / PANELS, pn = rest - i * PANELS;
+        const int pos = tile_base + i * p.page_size;
+        int row = p.pool_rows;                                     // outside the pool: zeros
+        if (pos < key_hi && pos + p.page_size > key_lo) {
+          const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+          const int page = table_cached ? table_cache[e - entry_first] : table[e];
+          if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+        }
+        tma_load_2d(dst + which * HALF_BYTES + pn * PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k,
+                    &full_bar[stage], 64 * pn, row);
+      }
+      __syncwarp();
+      issued = j + 1;
+    }
+    if (lane == 0 && *aborted) {
+      const long long start = clock64();
+      for (int j = max(0, issued - STAGES); j < issued; ++j)
+        while (!mbar_try_wait(&full_bar[j % STAGES], (j / STAGES) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
+    }
+  } else {
+    // ------------------------------------------------------------------------ consumers
+    // queries of this warp's MMA row tile, straight from global memory into A fragments
+    uint32_t qa[KSTEPS][4];
+    {
+      const int ra = g, rb = g + 8;
+      const bf16* pa = nullptr;
+      const bf16* pb = nullptr;
+      if (ra < rows_valid) pa = p.qkv + (size_t)(tok0 + ra / group) * p.q_row_stride + (size_t)(kvh * group + ra % group) * HD;
+      if (rb < rows_valid) pb = p.qkv + (size_t)(tok0 + rb / group) * p.q_row_stride + (size_t)(kvh * group + rb % group) * HD;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        qa[kk][0] = pa ? *reinterpret_cast<const uint32_t*>(pa + kk * 16 + 2 * t4) : 0u;
+        qa[kk][1] = pb ? *reinterpret_cast<const uint32_t*>(pb + kk * 16 + 2 * t4) : 0u;
+        qa[kk][2] = pa ? *reinterpret_cast<const uint32_t*>(pa + kk * 16 + 8 + 2 * t4) : 0u;
+        qa[kk][3] = pb ? *reinterpret_cast<const uint32_t*>(pb + kk * 16 + 8 + 2 * t4) : 0u;
+      }
+    }
+    const int row_a = g, row_b = g + 8;
+    const int qpos_a = pos0 + row_a / group, qpos_b = pos0 + row_b / group;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int stage = j % STAGES;
+      ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (j / STAGES) & 1, aborted) ? 1 : 0) != 0;
+      if (!ok) break;
+      const uint32_t k_base = smem_addr(ring + (size_t)stage * STAGE_BYTES);
+      const uint32_t v_base = k_base + HALF_BYTES;
+      const int wbase = (tile_begin + j) * DT_BN + warp * 16;
+      if (wbase < key_hi && wbase + 15 >= key_lo) {
+        if (wbase + 16 > key_hi) {
+          // slots of the last page past the last key may hold anything (0 x NaN = NaN): clear the
+          // value rows this warp will read
+          for (int idx = lane; idx < 16 * PANELS * 8; idx += 32) {
+            const int r = idx / (PANELS * 8), c = idx - r * (PANELS * 8);
+            if (wbase + r >= key_hi)
+              *reinterpret_cast<uint4*>(ring + (size_t)stage * STAGE_BYTES + HALF_BYTES + (c >> 3) * PANEL_BYTES +
+                                        (warp * 16 + r) * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          __syncwarp();
+        }
+        float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          // keys as the B operand: rows are keys, 16-byte chunks swizzled by the row number
+          const int krow = warp * 16 + (lane & 7) + 8 * (lane >> 4);
+          const int chunk = kk * 2 + ((lane >> 3) & 1);
+          uint32_t b[4];
+          ldsm_x4(b, k_base + (chunk >> 3) * PANEL_BYTES + krow * 128 + (((chunk & 7) ^ (krow & 7)) << 4));
+          mma16816(sc[0], qa[kk], b[0], b[1]);
+          mma16816(sc[1], qa[kk], b[2], b[3]);
+        }
+        float tmax_a = -INFINITY, tmax_b = -INFINITY;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int kpos = wbase + jj * 8 + 2 * t4 + (e & 1);
+            const int qpos = (e < 2) ? qpos_a : qpos_b;
+            const bool visible = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+            const float v = visible ? sc[jj][e] * p.scale_log2 : -INFINITY;
+            sc[jj][e] = v;
+            if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+          }
+        }
+        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
+        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
+        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
+        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
+        const float new_a = fmaxf(m_a, tmax_a), new_b = fmaxf(m_b, tmax_b);
+        const float shift_a = new_a == -INFINITY ? 0.0f : new_a, shift_b = new_b == -INFINITY ? 0.0f : new_b;
+        const float resc_a = exp2f(m_a - shift_a), resc_b = exp2f(m_b - shift_b);
+        m_a = new_a; m_b = new_b;
+        float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          sc[jj][0] = exp2f(sc[jj][0] - shift_a); sc[jj][1] = exp2f(sc[jj][1] - shift_a);
+          sc[jj][2] = exp2f(sc[jj][2] - shift_b); sc[jj][3] = exp2f(sc[jj][3] - shift_b);
+          sum_a += sc[jj][0] + sc[jj][1];
+          sum_b += sc[jj][2] + sc[jj][3];
+        }
+        l_a = l_a * resc_a + sum_a;
+        l_b = l_b * resc_b + sum_b;
+        uint32_t a[4];
+        a[0] = pack2(sc[0][0], sc[0][1]); a[1] = pack2(sc[0][2], sc[0][3]);
+        a[2] = pack2(sc[1][0], sc[1][1]); a[3] = pack2(sc[1][2], sc[1][3]);
+#pragma unroll
+        for (int dd = 0; dd < DTILES / 2; ++dd) {
+          // values as the B operand (transposed load): rows are keys, columns dims
+          const int vrow = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int chunk = dd * 2 + (lane >> 4);
+          uint32_t b[4];
+          ldsm_x4_trans(b, v_base + (chunk >> 3) * PANEL_BYTES + vrow * 128 + (((chunk & 7) ^ (vrow & 7)) << 4));
+          o[2 * dd][0] *= resc_a; o[2 * dd][1] *= resc_a; o[2 * dd][2] *= resc_b; o[2 * dd][3] *= resc_b;
+          o[2 * dd + 1][0] *= resc_a; o[2 * dd + 1][1] *= resc_a; o[2 * dd + 1][2] *= resc_b; o[2 * dd + 1][3] *= resc_b;
+          mma16816(o[2 * dd], a, b[0], b[1]);
+          mma16816(o[2 * dd + 1], a, b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
+    }
+  }
+
+  // ---- merge the four consumer warps (each saw a quarter of the keys) ----
+  __syncthreads();           // every copy that was waited for has landed; the ring is free
+  float* o_s = reinterpret_cast<float*>(ring);                       // [4][DT_ROWS][HD]
+  float* part_o = o_s + 4 * DT_ROWS * HD;                            // [DT_ROWS][HD]
+  if (warp < 4) {
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (t4 == 0) {
+      warp_m[warp][g] = m_a; warp_m[warp][g + 8] = m_b;
+      warp_l[warp][g] = l_a; warp_l[warp][g + 8] = l_b;
+    }
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+      float* da = o_s + ((size_t)warp * DT_ROWS + g) * HD + i * 8 + 2 * t4;
+      float* db = o_s + ((size_t)warp * DT_ROWS + g + 8) * HD + i * 8 + 2 * t4;
+      da[0] = o[i][0]; da[1] = o[i][1];
+      db[0] = o[i][2]; db[1] = o[i][3];
+    }
+  }
+  __syncthreads();
+  const size_t out_stride = (size_t)p.n_heads * HD;
+  for (int idx = threadIdx.x; idx < rows_valid * HD; idx += DT_THREADS) {
+    const int row = idx / HD, d = idx - row * HD;
+    const float m = fmaxf(fmaxf(warp_m[0][row], warp_m[1][row]), fmaxf(warp_m[2][row], warp_m[3][row]));
+    float l = 0.0f, acc = 0.0f;
+    if (m > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(warp_m[w][row] - m);
+        l += warp_l[w][row] * f;
+        acc += o_s[((size_t)w * DT_ROWS + row) * HD + d] * f;
+      }
+    }
+    if (p.num_splits == 1) {
+      const int q_local = row / group, head = kvh * group + row % group;
+      p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(l > 0.0f ? acc / l : 0.0f);
+    } else {
+      part_o[row * HD + d] = acc;
+      if (d == 0) {
+        part_m[row] = m;
+        part_l[row] = l;
+      }
+    }
+  }
+  if (p.num_splits > 1) {
+    // the splits of this (entry, kv head) are the blocks of one cluster: block 0 folds the others'
+    // states out of their shared memory
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (split == 0) {
+      // per row: the weight of every split's accumulator, exp2(m_r - M) / L, computed once
+      __shared__ float weight[8][DT_ROWS];
+      if (threadIdx.x < rows_valid) {
+        const int row = threadIdx.x;
+        float mr[8], lr[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          mr[r] = r < p.num_splits ? *cluster.map_shared_rank(&part_m[row], r) : -INFINITY;
+          lr[r] = r < p.num_splits ? *cluster.map_shared_rank(&part_l[row], r) : 0.0f;
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) m = fmaxf(m, mr[r]);
+        float l = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          mr[r] = mr[r] > -INFINITY ? exp2f(mr[r] - m) : 0.0f;
+          l += lr[r] * mr[r];
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) weight[r][row] = mr[r] * inv;
+      }
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < rows_valid * HD; idx += DT_THREADS) {
+        const int row = idx / HD, d = idx - row * HD;
+        float part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) part[r] = r < p.num_splits ? *cluster.map_shared_rank(&part_o[row * HD + d], r) : 0.0f;
+        float acc = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) acc += part[r] * weight[r][row];
+        const int q_local = row / group, head = kvh * group + row % group;
+        p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(acc);
+      }
+    }
+    cluster.sync();
+  }
+  if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 2);
+}
+
+struct DecMapKey {
+  const void* base;
+  long long rows;
+  int hd, box;
+  CUtensorMap map;
+};
+
+static const CUtensorMap* dec_pool_map(const void* base, long long rows, int hd, int box_rows) {
+  static DecMapKey cache[512];
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) return &cache[i].map;
+  DecMapKey& slot = cache[used < 512 ? used : 511];
+  if (make_tile_map(&slot.map, base, rows, hd, hd, box_rows)) return nullptr;
+  slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows;
+  if (used < 512) ++used;
+  return &slot.map;
+}
+
+template <int HD, int STAGES>
+static size_t dec_smem() { return (size_t)STAGES * 2 * (HD / 64) * DT_BN * 128 + 1024; }
+
+template <int HD, int STAGES>
+static int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecTmaParams& p, int n_work, cudaStream_t s) {
+  const size_t smem = dec_smem<HD, STAGES>();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(p.num_splits, p.n_kv, n_work);
+  config.blockDim = dim3(DT_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = s;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = p.num_splits;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, attention_decode_tma_kernel<HD, STAGES>, mk, mv, p);
+  return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+// 1 when this kernel takes the sizes (else the decode kernel of attention_bf16.cu serves them)
+PKV_EXPORT int pkv_attention_decode_tma_supports(int hd, int page_size, int q_row_stride) {
+  return ((hd == 64 || hd == 128) && page_size >= 8 && page_size % 8 == 0 && DT_BN % page_size == 0 &&
+          q_row_stride % 2 == 0) ? 1 : 0;
+}
+
+// Blocks of this kernel that fit on one SM (the host sizes the number of splits with it).
+template <int HD, int STAGES> static int dec_blocks_per_sm() {
+  int blocks = 0;
+  const size_t smem = dec_smem<HD, STAGES>();
+  cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_tma_kernel<HD, STAGES>, DT_THREADS, smem);
+  return blocks;
+}
+
+PKV_EXPORT int pkv_attention_decode_tma_blocks_per_sm(int hd, int deep_ring) {
+  if (hd == 128) return deep_ring ? dec_blocks_per_sm<128, 6>() : dec_blocks_per_sm<128, 3>();
+  if (hd == 64) return deep_ring ? dec_blocks_per_sm<64, 6>() : dec_blocks_per_sm<64, 3>();
+  return 0;
+}
+
+PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void* out, const void* k_pool,
+                                        const void* v_pool, long long n_pages, const int32_t* block_table,
+                                        int table_stride, const int32_t* seq_starts, const int32_t* first_pos,
+                                        const int32_t* work_seq, int n_work, int max_entry_tokens, int n_heads, int n_kv,
+                                        int hd, int page_size, int window, float scale, int num_splits, int deep_ring,
+                                        int* status, void* stream) {
+  if (n_work <= 0) return 0;
+  if (!pkv_attention_decode_tma_supports(hd, page_size, q_row_stride)) return PKV_ERR_LIMIT;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0) return PKV_ERR_SIZE;
+  if (num_splits < 1 || num_splits > 8 || n_work > 65535 || n_kv > 65535) return PKV_ERR_LIMIT;
+  if (max_entry_tokens * (n_heads / n_kv) > DT_ROWS) return PKV_ERR_LIMIT;
+  const long long pool_rows = n_pages * n_kv * page_size;
+  if (pool_rows >= (1LL << 31) - page_size) return PKV_ERR_LIMIT;
+  if ((uintptr_t)qkv % 4 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16) return PKV_ERR_ALIGN;
+  const CUtensorMap* map_k = dec_pool_map(k_pool, pool_rows, hd, page_size);
+  const CUtensorMap* map_v = dec_pool_map(v_pool, pool_rows, hd, page_size);
+  if (!map_k || !map_v) return PKV_ERR_SIZE;
+  int shift = -1;
+  for (int i = 0; i < 31; ++i)
+    if ((1 << i) == page_size) shift = i;
+  DecTmaParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq,
+                 n_heads, n_kv, page_size, shift, window, scale * 1.4426950408889634f, num_splits, (int)pool_rows, status};
+  cudaStream_t s = (cudaStream_t)stream;
+  // deep ring: one block per SM with six stages in flight (few blocks, long key ranges);
+  // shallow ring: three stages, two blocks per SM, so that one block's start and merge hide
+  // behind the other's streaming (many blocks)
+  if (hd == 128) return deep_ring ? launch_dec<128, 6>(*map_k, *map_v, p, n_work, s) : launch_dec<128, 3>(*map_k, *map_v, p, n_work, s);
+  return deep_ring ? launch_dec<64, 6>(*map_k, *map_v, p, n_work, s) : launch_dec<64, 3>(*map_k, *map_v, p, n_work, s);
+}

@@ -16,7 +16,8 @@ from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
     "add_rmsnorm", "attention_bf16_rows", "attention_bf16_supports", "attention_decode_bf16",
-    "attention_decode_blocks_per_sm",
+    "attention_decode_blocks_per_sm", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
+    "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
     "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports",
     "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
@@ -252,6 +253,50 @@ def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pool: torc
               _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq),
               _ptr(work_q0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), float(scale),
               _ptr(status), _stream()), "attention_prefill_tcgen05")
+
+
+_DECODE_TMA_BLOCKS: dict[tuple[int, bool], int] = {}
+
+
+def attention_decode_tma_supports(head_dim: int, page_size: int, q_row_stride: int) -> bool:
+    """Whether the TMA-fed decode attention takes these sizes (head 64 or 128, pages of 8k keys)."""
+    lib = library("attention_decode_tma")
+    lib.pkv_attention_decode_tma_supports.restype = c_int
+    lib.pkv_attention_decode_tma_supports.argtypes = [c_int, c_int, c_int]
+    return bool(lib.pkv_attention_decode_tma_supports(int(head_dim), int(page_size), int(q_row_stride)))
+
+
+def attention_decode_tma_blocks_per_sm(head_dim: int, deep_ring: bool) -> int:
+    """Blocks of the TMA decode kernel per SM with the deep (six-stage) or shallow (three-stage) ring."""
+    key = (head_dim, bool(deep_ring))
+    if key not in _DECODE_TMA_BLOCKS:
+        lib = library("attention_decode_tma")
+        lib.pkv_attention_decode_tma_blocks_per_sm.restype = c_int
+        lib.pkv_attention_decode_tma_blocks_per_sm.argtypes = [c_int, c_int]
+        _DECODE_TMA_BLOCKS[key] = max(1, int(lib.pkv_attention_decode_tma_blocks_per_sm(int(head_dim), int(deep_ring))))
+    return _DECODE_TMA_BLOCKS[key]
+
+
+def attention_decode_tma(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                         block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
+                         work_seq: torch.Tensor, max_entry_tokens: int, n_heads: int, n_kv: int, head_dim: int,
+                         page_size: int, window: int, scale: float, num_splits: int, status: torch.Tensor,
+                         deep_ring: bool = True) -> None:
+    """Split-KV decode attention with TMA page loads into a ring of stages (at most 8 splits,
+    merged inside a thread-block cluster); writes the rows of its entries into ``out``.
+    ``deep_ring``: six stages and one block per SM (few blocks), else three stages and two."""
+    for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("status", status)):
+        _need(t, torch.int32, name)
+    fn = _fn("attention_decode_tma", "pkv_attention_decode_tma",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
+              block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), work_seq.numel(),
+              int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(num_splits),
+              int(bool(deep_ring)), _ptr(status), _stream()), "attention_decode_tma")
 
 
 _DECODE_BLOCKS: dict[int, int] = {}

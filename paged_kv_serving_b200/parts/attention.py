@@ -62,7 +62,7 @@ class PagedAttention(Part):
         self.qkv_proj: torch.Tensor | None = None
         self.out_proj: torch.Tensor | None = None
         self._fast_ok: bool | None = None
-        self._tcgen05_ok: dict[int, bool] = {}
+        self._tcgen05_ok: dict = {}
 
     @property
     def group_size(self) -> int:
@@ -110,6 +110,14 @@ class PagedAttention(Part):
             self._tcgen05_ok[key] = ops.attention_tcgen05_supports(self.head_dim, page_size, qkv_width)
         return self._tcgen05_ok[key]
 
+    def _decode_tma(self, page_size: int) -> bool:
+        """Whether short entries go to the TMA-fed decode kernel."""
+        key = ("decode", page_size)
+        if key not in self._tcgen05_ok:
+            qkv_width = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+            self._tcgen05_ok[key] = self.USE_TCGEN05 and ops.attention_decode_tma_supports(self.head_dim, page_size, qkv_width)
+        return self._tcgen05_ok[key]
+
     def _fast_key(self, page_size: int) -> str:
         return f"attention/fast/g{self.group_size}/{'t' if self._tcgen05(page_size) else 'm'}"
 
@@ -134,7 +142,7 @@ class PagedAttention(Part):
         work_q0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * block_rows
         cost = first[work_seq] + work_q0
         order = np.argsort(-cost, kind="stable")
-        num_splits = 1
+        num_splits, deep_ring = 1, True
         if len(decode_entries):
             longest = int((first[decode_entries] + lens[decode_entries]).max())
             if ctx.planning_context_len is not None:
@@ -143,7 +151,15 @@ class PagedAttention(Part):
             # splits of an entry form one thread-block cluster) and at most one per 64-key tile
             tiles = max(1, -(-longest // 64))
             blocks_per_split = len(decode_entries) * self.n_kv_heads
-            resident = ops.attention_decode_blocks_per_sm(self.head_dim) * _sm_count(ctx.device)
+            deep_ring = True
+            if self._decode_tma(page_size):
+                # the three-stage ring (two blocks per SM) measured at least as fast as the six-stage
+                # one (one block per SM) at every batch size and context length tried
+                deep_ring = False
+                per_sm = ops.attention_decode_tma_blocks_per_sm(self.head_dim, deep_ring)
+            else:
+                per_sm = ops.attention_decode_blocks_per_sm(self.head_dim)
+            resident = per_sm * _sm_count(ctx.device)
             num_splits = int(max(1, min(tiles, 8, resident // blocks_per_split)))
         names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq")}
         ctx.arena.add(names["prefill_seq"], work_seq[order] if len(order) else [0])
@@ -152,7 +168,7 @@ class PagedAttention(Part):
         ctx.scratch[key] = {
             "names": names, "n_prefill": int(len(order)), "n_decode": int(len(decode_entries)),
             "max_small_tokens": int(lens[decode_entries].max()) if len(decode_entries) else 0,
-            "num_splits": num_splits,
+            "num_splits": num_splits, "deep_ring": deep_ring,
         }
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
@@ -210,7 +226,12 @@ class PagedAttention(Part):
             ops.attention_prefill_bf16(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["prefill_seq"]),
                                        ctx.ints(names["prefill_q0"]), self.n_heads, self.n_kv_heads, self.head_dim,
                                        group.page_size, self.window or 0, self.scale)
-        if plan["n_decode"]:
+        if plan["n_decode"] and self._decode_tma(group.page_size):
+            ops.attention_decode_tma(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["decode_seq"]),
+                                     plan["max_small_tokens"], self.n_heads, self.n_kv_heads, self.head_dim,
+                                     group.page_size, self.window or 0, self.scale, plan["num_splits"],
+                                     ops.status_word(qkv.device), plan["deep_ring"])
+        elif plan["n_decode"]:
             splits = plan["num_splits"]
             scratch = None
             if splits > 8:

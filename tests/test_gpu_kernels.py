@@ -147,7 +147,7 @@ def test_rope_kv_store(dtype, heads, kv, hd):
 
 
 def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True, fast=False, splits=1,
-                    tcgen05=False):
+                    tcgen05=False, deep_ring=True):
     """Random sequences already in the cache (``contexts`` tokens each), of which the last
     ``queries`` tokens are this step's queries. Returns device inputs and the plain answer."""
     from paged_kv_serving_b200 import ops
@@ -211,7 +211,13 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
                                        dev(np.asarray([s for s, _ in large], dtype=np.int32)),
                                        dev(np.asarray([q for _, q in large], dtype=np.int32)),
                                        heads, kv, hd, page, window or 0, 1.0 / math.sqrt(hd))
-        if small:
+        if small and tcgen05 and ops.attention_decode_tma_supports(hd, page, qkv.shape[1]):
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            ops.attention_decode_tma(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
+                                     max(queries[s] for s in small), heads, kv, hd, page, window or 0,
+                                     1.0 / math.sqrt(hd), splits, status, deep_ring=deep_ring)
+            assert int(status.item()) == 0
+        elif small:
             scratch = torch.full((q_all.shape[0] * heads * splits * (hd + 2),), float("nan"), device="cuda")
             ops.attention_decode_bf16(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
                                       max(queries[s] for s in small), heads, kv, hd, page, window or 0,
@@ -280,6 +286,37 @@ def test_attention_tcgen05_prefill(heads, kv, hd, page):
     rng = np.random.default_rng(hd + page)
     got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
                                 contexts=[300, 1, 129, 33, 128, 700, 513, 1000], queries=[100, 1, 129, 17, 128, 150, 513, 2],
+                                dtype="bfloat16", fast=True, splits=2, tcgen05=True)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("deep_ring", [True, False])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("heads, kv, hd, page", [(32, 8, 128, 16), (3, 3, 128, 8), (16, 2, 64, 8), (4, 4, 64, 32),
+                                                   (8, 1, 128, 64)])
+def test_attention_decode_tma(heads, kv, hd, page, splits, deep_ring):
+    """The TMA-fed decode kernel alone: one to a few queries per entry over contexts from 1 to
+    1500 keys (more tiles than ring stages), partial last pages filled with NaN, a far key that
+    dominates, splits merged inside a cluster."""
+    from paged_kv_serving_b200 import ops
+
+    assert ops.attention_decode_tma_supports(hd, page, (heads + 2 * kv) * hd)
+    group = heads // kv
+    few = max(1, 16 // group)
+    rng = np.random.default_rng(hd + page + splits)
+    got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
+                                contexts=[300, 1, 65, 1500, 128, 64, 513, 1000], queries=[1, 1, few, 1, min(few, 2), 1, 1, few],
+                                dtype="bfloat16", fast=True, splits=splits, tcgen05=True, deep_ring=deep_ring)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("window", [1, 63, 64, 65, 300])
+def test_attention_decode_tma_window_edges(window):
+    rng = np.random.default_rng(window)
+    got, want = _attention_case(rng, heads=4, kv=2, hd=64, page=8, window=window,
+                                contexts=[400, 128, 31, 640, 65], queries=[1, 2, 1, 8, 1],
                                 dtype="bfloat16", fast=True, splits=2, tcgen05=True)
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
