@@ -19,7 +19,7 @@ __all__ = [
     "attention_decode_blocks_per_sm", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
     "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
-    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports",
+    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
     "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
 ]
 
@@ -371,15 +371,31 @@ def gemm_tcgen05_supports(a: torch.Tensor, b_nk: torch.Tensor) -> bool:
 
 
 GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "silu_mul": 2}
+_GEMM_WORKSPACE: dict[str, torch.Tensor] = {}
+
+
+def gemm_workspace(device: torch.device | str) -> torch.Tensor:
+    """The workspace of the two-SM tcgen05 product on a device (partial accumulators and flags of
+    its stream-K hand-over), allocated and zeroed once. Launches on one stream share it."""
+    key = str(torch.device(device))
+    if key not in _GEMM_WORKSPACE:
+        lib = library("gemm_tcgen05")
+        lib.pkv_gemm_tcgen05_workspace_bytes.restype = c_longlong
+        with torch.cuda.device(device):
+            size = int(lib.pkv_gemm_tcgen05_workspace_bytes())
+        _GEMM_WORKSPACE[key] = torch.zeros((size,), dtype=torch.uint8, device=device)
+    return _GEMM_WORKSPACE[key]
 
 
 def gemm_tcgen05(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epilogue: str = "bf16",
-                 n_out: int = 0, clip: float = 60.0) -> torch.Tensor:
+                 n_out: int = 0, clip: float = 60.0, pairs: bool = True) -> torch.Tensor:
     """``a [M, K] @ b_nk [N, K]^T`` on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
     ``epilogue``: ``"bf16"`` / ``"f32"`` store the product; ``"silu_mul"`` expects the rows of
     ``b_nk`` interleaved in blocks of 128 gate rows and 128 up rows and stores
     ``silu(gate) * up`` as ``[M, n_out]``. ``status`` receives an error code if a block gave up.
+    ``pairs``: with more than 128 rows, let pairs of SMs share each tile (tcgen05 cta_group::2) and
+    deal the work out stream-K fashion; partial tiles pass through ``gemm_workspace``.
     """
     if epilogue not in GEMM_EPILOGUES:
         raise ValueError(f"unknown epilogue {epilogue!r}")
@@ -397,9 +413,11 @@ def gemm_tcgen05(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epil
         out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
     fn = _fn("gemm_tcgen05", "pkv_gemm_tcgen05",
              [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-              c_void_p, c_void_p])
+              c_void_p, c_longlong, c_void_p, c_void_p])
+    workspace = gemm_workspace(a.device) if pairs and m > 128 else None
     _check(fn(_ptr(a), a.stride(0), _ptr(b_nk), b_nk.stride(0), _ptr(out), out.stride(0), m, n, k,
-              GEMM_EPILOGUES[epilogue], int(n_out), float(clip), _ptr(status), _stream()), "gemm_tcgen05")
+              GEMM_EPILOGUES[epilogue], int(n_out), float(clip), _ptr(workspace),
+              workspace.numel() if workspace is not None else 0, _ptr(status), _stream()), "gemm_tcgen05")
     return out
 
 

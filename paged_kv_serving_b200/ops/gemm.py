@@ -1,9 +1,10 @@
 """Matrix products of the product path.
 
 Weights are held as ``[out, in]`` with the inner size contiguous. In bfloat16, products with at
-least ``TCGEN05_MIN_ROWS`` rows of activations (prompt portions) run on the hand-written
-tcgen05/TMA kernel of ``csrc/gemm_tcgen05.cu``, with the SiLU-times-up step of the feed-forward
-fused into its epilogue; the few rows of a decode step, and the float32 path, go to cuBLAS
+least ``TCGEN05_MIN_ROWS`` rows of activations (prompt portions) can run on the hand-written
+tcgen05/TMA kernels of ``csrc/gemm_tcgen05.cu``: the gate/up product of the feed-forward always
+does, with its SiLU-times-up step fused into the epilogue, the plain products when
+``PLAIN_PRODUCT_KERNEL`` says so; the few rows of a decode step, and the float32 path, go to cuBLAS
 through ``torch.mm``, as the reference's engine hands its products to a library
 (src/paged_kv_serving/engine/model.py:249,258-259,264). Reduced-precision modes are switched
 off: float32 products use true float32 multiply-adds (no TF32), bfloat16 products accumulate in
@@ -27,6 +28,12 @@ torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 TCGEN05_MIN_ROWS = 128
 #: Set to False to send every product to cuBLAS (used by tests that compare the two).
 USE_TCGEN05 = True
+#: Which kernel takes the plain products (no fused epilogue) of prompt portions: "library" for
+#: cuBLAS, "tcgen05" for the two-SM kernel of this package. Timed at 2,048 rows with the layer
+#: sizes of an 8-billion-parameter model, cuBLAS is ahead on these by a tenth (fewer idle SMs in
+#: the last wave of tiles), while the fused gate/up product is faster here than cuBLAS followed by
+#: an activation kernel, so the library keeps the plain ones.
+PLAIN_PRODUCT_KERNEL = "library"
 
 
 def _own_kernel(x: torch.Tensor, w_nk: torch.Tensor) -> bool:
@@ -49,7 +56,8 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
     """``x [T, K] @ w_nk [N, K]^T``; ``out_dtype`` float32 keeps the float32 accumulator."""
     wants_f32 = out_dtype == torch.float32
     # rows of the output must start on 16-byte boundaries for the kernel's vector stores
-    if w_nk.shape[0] % (4 if wants_f32 else 8) == 0 and _own_kernel(x, w_nk):
+    if (PLAIN_PRODUCT_KERNEL == "tcgen05" and w_nk.shape[0] % (4 if wants_f32 else 8) == 0
+            and _own_kernel(x, w_nk)):
         return ops.gemm_tcgen05(x, w_nk, ops.status_word(x.device), "f32" if wants_f32 else "bf16")
     return matmul(x, w_nk.t(), out_dtype)
 
@@ -58,5 +66,8 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleav
     """``silu(x @ gate^T) * (x @ up^T)`` for gate and up rows held in one matrix (``interleave``
     as in ``ops.silu_mul``); ``[T, ff]``."""
     if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and _own_kernel(x, w_gate_up):
-        return ops.gemm_tcgen05(x, w_gate_up, ops.status_word(x.device), "silu_mul", n_out=ff, clip=clip)
+        # one SM per tile: with this many tiles the two-SM kernel's split of the last wave costs
+        # more than it saves
+        return ops.gemm_tcgen05(x, w_gate_up, ops.status_word(x.device), "silu_mul", n_out=ff, clip=clip,
+                                pairs=False)
     return ops.silu_mul(matmul(x, w_gate_up.t()), clip, ff=ff, interleave=interleave)

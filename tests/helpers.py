@@ -27,9 +27,17 @@ TINY_C = {
     "n_kv_heads": 2, "head_dim": 48, "d_ff": 200, "max_seq_len": 1024, "rope_theta": 50000.0,
     "norm_eps": 3e-6, "tie_embeddings": True,
 }
-PAGE_SIZE = {"A": 4, "B": 8, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-WEIGHT_SEED = {"A": 0, "B": 2, "C": 5}
+# A fourth shape at the sizes the Blackwell-specific kernels take (head size 64, pages of 16,
+# widths that are multiples of 8): in bfloat16 its prompts run through the tcgen05 matrix product,
+# the tcgen05 prefill attention and the TMA-fed decode attention.
+TINY_D = {
+    "architecture": "LlamaToyDecoder", "vocab_size": 512, "d_model": 256, "n_layers": 2, "n_heads": 8,
+    "n_kv_heads": 2, "head_dim": 64, "d_ff": 392, "max_seq_len": 1024, "rope_theta": 500000.0,
+    "norm_eps": 1e-5, "tie_embeddings": False,
+}
+PAGE_SIZE = {"A": 4, "B": 8, "C": 16, "D": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+WEIGHT_SEED = {"A": 0, "B": 2, "C": 5, "D": 7}
 
 # Tolerances, fixed before any GPU run. float32: the reference's own bound for paged against
 # dense logits (tests/property/test_equivalence.py:33-34 of the reference). bfloat16: activations
@@ -42,9 +50,11 @@ def bf16_atol(reference: np.ndarray) -> float:
     return 0.03 * float(np.abs(reference).max()) + 2e-3
 
 
-def tensors_for(name: str, dtype: str, std: float = 0.08, norm_jitter: float = 0.1) -> dict[str, np.ndarray]:
+def tensors_for(name: str, dtype: str, std: float | None = None, norm_jitter: float = 0.1) -> dict[str, np.ndarray]:
     """Random float32 tensors of a tiny configuration; for bfloat16 the matrices are rounded so
     that the plain implementation and the engine hold exactly the same values."""
+    if std is None:
+        std = 0.04 if name == "D" else 0.08     # wider layers: keep activations at the same scale
     tensors = plain_model.random_tensors(CONFIGS[name], WEIGHT_SEED[name], std=std, norm_jitter=norm_jitter)
     if dtype == "bfloat16":
         tensors = {k: (plain_model.round_to_bfloat16(v) if v.ndim == 2 else v) for k, v in tensors.items()}

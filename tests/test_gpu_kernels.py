@@ -364,10 +364,11 @@ def test_attention_refuses_what_it_cannot_do():
                                    1, 1, 24, 1, 0, 1.0)
 
 
-@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (1, 520, 136), (200, 1000, 72), (300, 96, 4096), (2048, 1024, 200),
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (1, 520, 136), (200, 1000, 72), (300, 96, 4096), (2048, 1024, 200), (1000, 4000, 1032), (2100, 2304, 72), (520, 6400, 136),
                                      (130, 1320, 120)])
+@pytest.mark.parametrize("pairs", [True, False])
 @pytest.mark.parametrize("epilogue", ["bf16", "f32"])
-def test_gemm_tcgen05(m, n, k, epilogue):
+def test_gemm_tcgen05(m, n, k, epilogue, pairs):
     """The hand-written tcgen05/TMA product against a float32 product of the same bfloat16
     operands: tails in every dimension (rows, columns, inner size), one row, many tiles."""
     from paged_kv_serving_b200 import ops
@@ -377,7 +378,7 @@ def test_gemm_tcgen05(m, n, k, epilogue):
     b = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).cuda().to(torch.bfloat16)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     assert ops.gemm_tcgen05_supports(a, b)
-    out = ops.gemm_tcgen05(a, b, status, epilogue)
+    out = ops.gemm_tcgen05(a, b, status, epilogue, pairs=pairs)
     want = a.double() @ b.double().t()
     assert int(status.item()) == 0
     scale = float(want.abs().max())
@@ -386,12 +387,13 @@ def test_gemm_tcgen05(m, n, k, epilogue):
     # a strided view of a wider matrix (rows 16-byte aligned) is taken as it is
     wide = torch.zeros((m, k + 8), dtype=torch.bfloat16, device="cuda")
     wide[:, :k] = a
-    again = ops.gemm_tcgen05(wide[:, :k], b, status, epilogue)
+    again = ops.gemm_tcgen05(wide[:, :k], b, status, epilogue, pairs=pairs)
     assert torch.equal(again, out)
 
 
-@pytest.mark.parametrize("m, ff, k", [(128, 128, 64), (257, 200, 120), (2048, 1000, 256), (3, 384, 72)])
-def test_gemm_tcgen05_silu_mul_epilogue(m, ff, k):
+@pytest.mark.parametrize("pairs", [True, False])
+@pytest.mark.parametrize("m, ff, k", [(128, 128, 64), (257, 200, 120), (2048, 1000, 256), (3, 384, 72), (600, 3000, 520)])
+def test_gemm_tcgen05_silu_mul_epilogue(m, ff, k, pairs):
     from paged_kv_serving_b200 import ops
 
     rng = np.random.default_rng(ff)
@@ -405,7 +407,7 @@ def test_gemm_tcgen05_silu_mul_epilogue(m, ff, k):
         fused[b, 0, :rows] = gate[128 * b:128 * b + rows]
         fused[b, 1, :rows] = up[128 * b:128 * b + rows]
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = ops.gemm_tcgen05(a, fused.view(-1, k), status, "silu_mul", n_out=ff)
+    out = ops.gemm_tcgen05(a, fused.view(-1, k), status, "silu_mul", n_out=ff, pairs=pairs)
     g, u = (a.float() @ gate.float().t()).cpu().numpy(), (a.float() @ up.float().t()).cpu().numpy()
     want = plain_model.silu(g) * u
     assert int(status.item()) == 0 and out.shape == (m, ff)

@@ -16,7 +16,7 @@ import plain_model
 pytestmark = pytest.mark.gpu
 
 DTYPES = ("float32", "bfloat16")
-LENGTHS = {"A": 100, "B": 150, "C": 300}
+LENGTHS = {"A": 100, "B": 150, "C": 300, "D": 450}
 
 
 def _session(name, dtype, max_tokens):
@@ -34,7 +34,7 @@ def _reference(name, tensors, tokens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ("A", "B", "C"))
+@pytest.mark.parametrize("name", ("A", "B", "C", "D"))
 def test_whole_prompt_every_position(name, dtype):
     session, tensors = _session(name, dtype, 512)
     tokens = helpers.random_tokens(helpers.CONFIGS[name], LENGTHS[name], seed=11)
@@ -44,7 +44,7 @@ def test_whole_prompt_every_position(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ("A", "B", "C"))
+@pytest.mark.parametrize("name", ("A", "B", "C", "D"))
 def test_bulk_then_last_32_one_by_one(name, dtype):
     session, tensors = _session(name, dtype, 512)
     tokens = helpers.random_tokens(helpers.CONFIGS[name], LENGTHS[name], seed=12)
@@ -57,12 +57,13 @@ def test_bulk_then_last_32_one_by_one(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ("A", "B", "C"))
+@pytest.mark.parametrize("name", ("A", "B", "C", "D"))
 def test_portions_of_changing_size(name, dtype):
     session, tensors = _session(name, dtype, 512)
     tokens = helpers.random_tokens(helpers.CONFIGS[name], LENGTHS[name], seed=13)
     want = _reference(name, tensors, tokens)
-    sizes, cycle, at = [], [7, 3, 11, 2, 5, 2, 13, 1, 4], 0
+    # config D also takes portions of 130 and 150 tokens: enough rows for the tensor-core product
+    sizes, cycle, at = [], [7, 3, 11, 2, 5, 2, 13, 1, 4] if name != "D" else [7, 150, 2, 130, 3, 1, 60, 2], 0
     while sum(sizes) < len(tokens):
         sizes.append(min(cycle[at % len(cycle)], len(tokens) - sum(sizes)))
         at += 1
@@ -76,7 +77,7 @@ def test_portions_of_changing_size(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ("A", "B"))
+@pytest.mark.parametrize("name", ("A", "B", "D"))
 def test_mixed_requests_with_page_reuse(name, dtype):
     """Up to four live requests; portions of some beside decoded tokens of others; the pool
     (256 tokens) is smaller than what all requests need together, so pages are used again."""
