@@ -306,6 +306,8 @@ __global__ void __launch_bounds__(AT_THREADS) attention_prefill_kernel(const Att
 // ---------------------------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const AttnParams p) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   constexpr int LD = HD + AT_PAD;
   constexpr int KSTEPS = HD / 16;
   constexpr int DTILES = HD / 8;
@@ -532,6 +534,8 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        bf16* __restrict__ out, const int32_t* __restrict__ seq_starts,
                                        const int32_t* __restrict__ work_entry, int n_heads, int hd, int num_splits) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int s = work_entry[blockIdx.y];
   const int tok0 = seq_starts[s], n_q = seq_starts[s + 1] - tok0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -573,24 +577,9 @@ static int launch_decode(const AttnParams& p, int n_work, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  if (p.use_cluster && p.num_splits > 1) {
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(p.num_splits, p.n_kv, n_work);
-    config.blockDim = dim3(AT_THREADS);
-    config.dynamicSmemBytes = smem;
-    config.stream = s;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = p.num_splits;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, attention_decode_kernel<HD>, p);
-    return e == cudaSuccess ? launch_status() : (int)e;
-  }
-  attention_decode_kernel<HD><<<dim3(p.num_splits, p.n_kv, n_work), AT_THREADS, smem, s>>>(p);
-  return launch_status();
+  const int cluster_x = (p.use_cluster && p.num_splits > 1) ? p.num_splits : 0;
+  return launch_kernel(attention_decode_kernel<HD>, dim3(p.num_splits, p.n_kv, n_work), dim3(AT_THREADS), smem, s, true,
+                       cluster_x, p);
 }
 
 }  // namespace pkv
@@ -698,7 +687,6 @@ PKV_EXPORT int pkv_attention_decode_bf16(const void* qkv, int q_row_stride, void
   if (status || num_splits == 1 || use_cluster) return status;
   const int warps = 4;
   const int rows_max = max_entry_tokens * n_heads;
-  attention_merge_kernel<<<dim3((rows_max + warps - 1) / warps, n_work), warps * 32, 0, s>>>(
-      part_o, part_ml, (bf16*)out, seq_starts, work_seq, n_heads, hd, num_splits);
-  return launch_status();
+  return launch_kernel(attention_merge_kernel, dim3((rows_max + warps - 1) / warps, n_work), dim3(warps * 32), 0, s, true, 0,
+                       (const float*)part_o, (const float*)part_ml, (bf16*)out, seq_starts, work_seq, n_heads, hd, num_splits);
 }

@@ -80,6 +80,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ int32_t table_cache[DT_TABLE_CACHE];
   __shared__ int abort_flag;
 
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_seq[blockIdx.z];
   const int group = p.n_heads / p.n_kv;
   const int tok0 = p.seq_starts[s];
@@ -383,20 +385,8 @@ static int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecTma
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(p.num_splits, p.n_kv, n_work);
-  config.blockDim = dim3(DT_THREADS);
-  config.dynamicSmemBytes = smem;
-  config.stream = s;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeClusterDimension;
-  attribute[0].val.clusterDim.x = p.num_splits;
-  attribute[0].val.clusterDim.y = 1;
-  attribute[0].val.clusterDim.z = 1;
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, attention_decode_tma_kernel<HD, STAGES>, mk, mv, p);
-  return e == cudaSuccess ? launch_status() : (int)e;
+  return launch_kernel(attention_decode_tma_kernel<HD, STAGES>, dim3(p.num_splits, p.n_kv, n_work), dim3(DT_THREADS), smem, s,
+                       true, p.num_splits, mk, mv, p);
 }
 
 }  // namespace pkv

@@ -64,4 +64,49 @@ inline int launch_status() {
   return e == cudaSuccess ? 0 : (int)e;
 }
 
+// Programmatic dependent launch. A kernel launched with `chained` may start while the kernel
+// before it on the stream is still running, once every block of that kernel has called
+// `dependents_may_launch()` (or has ended). It must call `wait_for_prior_kernels()` before it
+// reads anything an earlier kernel writes and before it writes anything at all; the call returns
+// when the kernel before it has finished and its writes are visible. Because every chained
+// kernel waits in this way, a kernel that has passed its wait knows that all earlier work on
+// the stream has finished, not only its direct predecessor. Kernels call both at their top
+// (the calls do nothing in a kernel launched the ordinary way); only what is constant during a
+// step (weights) may be touched before the wait.
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launches `kernel`; `chained` as above, `cluster_x` > 0 groups that many blocks along x into a
+// thread-block cluster. Returns 0 or the CUDA error.
+template <typename... P, typename... A>
+inline int launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool chained,
+                         int cluster_x, A&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int n = 0;
+  if (cluster_x > 0) {
+    attributes[n].id = cudaLaunchAttributeClusterDimension;
+    attributes[n].val.clusterDim.x = cluster_x;
+    attributes[n].val.clusterDim.y = 1;
+    attributes[n].val.clusterDim.z = 1;
+    ++n;
+  }
+#ifdef PKV_NO_CHAIN  // build switch for comparisons: every launch an ordinary one
+  chained = false;
+#endif
+  if (chained) {
+    attributes[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  config.attrs = attributes;
+  config.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, P(args)...);
+  return e == cudaSuccess ? launch_status() : (int)e;
+}
+
 }  // namespace pkv

@@ -17,6 +17,8 @@ namespace pkv {
 template <typename W>
 __global__ void embedding_gather_kernel(const W* __restrict__ table, const int32_t* __restrict__ ids,
                                         float* __restrict__ out, int d, int vocab, int* __restrict__ status) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) {  // never read outside the table: record and use row 0
@@ -40,6 +42,8 @@ template <typename D, typename O>
 __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const D* __restrict__ delta,
                                    const float* __restrict__ weight, float eps, O* __restrict__ out,
                                    const int32_t* __restrict__ rows, int d) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   extern __shared__ float row_buf[];  // d floats + 32 scratch
   float* scratch = row_buf + d;
   const int r = blockIdx.x;
@@ -102,6 +106,8 @@ template <typename D, typename O>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const D* __restrict__ delta,
                                        const float* __restrict__ weight, float eps, O* __restrict__ out,
                                        const int32_t* __restrict__ rows, int d) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -145,6 +151,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const D* __re
 template <typename A, int V>
 __global__ void silu_mul_vec_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, int in_stride,
                                     int interleave, long long n_chunks, float clip) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int chunks_per_row = ff / V;
   for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
     const long long t = c / chunks_per_row;
@@ -170,6 +178,8 @@ __global__ void silu_mul_vec_kernel(const A* __restrict__ gate_up, A* __restrict
 template <typename A>
 __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int ff, int in_stride,
                                 int interleave, float clip) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int t = blockIdx.y;
   const A* row = gate_up + (size_t)t * in_stride;
   A* o = out + (size_t)t * ff;
@@ -198,6 +208,8 @@ __global__ void rope_kv_store_kernel(A* __restrict__ qkv, const int32_t* __restr
                                      C* __restrict__ k_pool, C* __restrict__ v_pool,
                                      const int32_t* __restrict__ slots, int n_heads, int n_kv, int hd,
                                      int page_size, int store) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // [0,H) q heads, [H,H+KV) k heads, [H+KV,H+2KV) v heads
   const int half = hd >> 1;
@@ -246,6 +258,8 @@ __global__ void rope_kv_store_vec_kernel(A* __restrict__ qkv, const int32_t* __r
                                          C* __restrict__ k_pool, C* __restrict__ v_pool,
                                          const int32_t* __restrict__ slots, int n_heads, int n_kv, int hd,
                                          int page_size, int store) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int t = blockIdx.x;
   const int half = hd >> 1;
   const int quads = half >> 2;                       // groups of 4 pairs per head
@@ -296,13 +310,14 @@ PKV_EXPORT int pkv_embedding_gather(const void* table, int table_dtype, const in
   if (d <= 0 || vocab <= 0) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = d >= 1024 ? 256 : 128;
+  // the first kernel of a step follows a copy from the host, not a kernel: an ordinary launch
   if (table_dtype == PKV_F32)
-    embedding_gather_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)table, ids, out, d, vocab, status);
-  else if (table_dtype == PKV_BF16)
-    embedding_gather_kernel<bf16><<<n_tokens, threads, 0, s>>>((const bf16*)table, ids, out, d, vocab, status);
-  else
-    return PKV_ERR_DTYPE;
-  return launch_status();
+    return launch_kernel(embedding_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, false, 0,
+                         (const float*)table, ids, out, d, vocab, status);
+  if (table_dtype == PKV_BF16)
+    return launch_kernel(embedding_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, false, 0,
+                         (const bf16*)table, ids, out, d, vocab, status);
+  return PKV_ERR_DTYPE;
 }
 
 template <typename D, typename O>
@@ -313,8 +328,8 @@ static int launch_add_rmsnorm(float* hidden, const void* delta, const float* wei
     int threads = ((chunks + 1) / 2 + 31) / 32 * 32;           // two chunks a thread where that fits
     if (threads < 64) threads = 64;
     if (threads > 1024) threads = 1024;
-    add_rmsnorm_vec_kernel<D, O><<<n_rows, threads, 0, s>>>(hidden, (const D*)delta, weight, eps, (O*)out, rows, d);
-    return launch_status();
+    return launch_kernel(add_rmsnorm_vec_kernel<D, O>, dim3(n_rows), dim3(threads), 0, s, true, 0,
+                         hidden, (const D*)delta, weight, eps, (O*)out, rows, d);
   }
   const size_t smem = (size_t)(d + 32) * sizeof(float);
   if (smem > 200 * 1024) return PKV_ERR_LIMIT;
@@ -323,8 +338,8 @@ static int launch_add_rmsnorm(float* hidden, const void* delta, const float* wei
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<D, O><<<n_rows, threads, smem, s>>>(hidden, (const D*)delta, weight, eps, (O*)out, rows, d);
-  return launch_status();
+  return launch_kernel(add_rmsnorm_kernel<D, O>, dim3(n_rows), dim3(threads), smem, s, true, 0,
+                       hidden, (const D*)delta, weight, eps, (O*)out, rows, d);
 }
 
 PKV_EXPORT int pkv_add_rmsnorm(float* hidden, const void* delta, int delta_dtype, const float* weight, float eps,
@@ -355,10 +370,10 @@ PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tok
     long long blocks = (n_chunks + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == PKV_BF16)
-      silu_mul_vec_kernel<bf16, 8><<<(int)blocks, 256, 0, s>>>((const bf16*)gate_up, (bf16*)out, ff, in_stride, interleave, n_chunks, clip);
-    else
-      silu_mul_vec_kernel<float, 4><<<(int)blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, ff, in_stride, interleave, n_chunks, clip);
-    return launch_status();
+      return launch_kernel(silu_mul_vec_kernel<bf16, 8>, dim3((int)blocks), dim3(256), 0, s, true, 0,
+                           (const bf16*)gate_up, (bf16*)out, ff, in_stride, interleave, n_chunks, clip);
+    return launch_kernel(silu_mul_vec_kernel<float, 4>, dim3((int)blocks), dim3(256), 0, s, true, 0,
+                         (const float*)gate_up, (float*)out, ff, in_stride, interleave, n_chunks, clip);
   }
   const int threads = 256;
   int bx = (ff + threads - 1) / threads;
@@ -367,14 +382,18 @@ PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tok
   for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
     const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
     dim3 grid(bx, nt);
+    int rc;
     if (dtype == PKV_F32)
-      silu_mul_kernel<float><<<grid, threads, 0, s>>>((const float*)gate_up + (size_t)t0 * in_stride, (float*)out + (size_t)t0 * ff, ff, in_stride, interleave, clip);
+      rc = launch_kernel(silu_mul_kernel<float>, grid, dim3(threads), 0, s, true, 0,
+                         (const float*)gate_up + (size_t)t0 * in_stride, (float*)out + (size_t)t0 * ff, ff, in_stride, interleave, clip);
     else if (dtype == PKV_BF16)
-      silu_mul_kernel<bf16><<<grid, threads, 0, s>>>((const bf16*)gate_up + (size_t)t0 * in_stride, (bf16*)out + (size_t)t0 * ff, ff, in_stride, interleave, clip);
+      rc = launch_kernel(silu_mul_kernel<bf16>, grid, dim3(threads), 0, s, true, 0,
+                         (const bf16*)gate_up + (size_t)t0 * in_stride, (bf16*)out + (size_t)t0 * ff, ff, in_stride, interleave, clip);
     else
       return PKV_ERR_DTYPE;
+    if (rc != 0) return rc;
   }
-  return launch_status();
+  return 0;
 }
 
 PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positions, const float* cos_t,
@@ -389,26 +408,26 @@ PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positi
     const int tasks = (n_heads + n_kv) * (hd / 8) + n_kv * (hd / 4);
     int vthreads = (tasks + 31) / 32 * 32;
     if (vthreads > 512) vthreads = 512;
-#define PKV_ROPE_VEC(A, C) \
-  rope_kv_store_vec_kernel<A, C><<<n_tokens, vthreads, 0, s>>>((A*)qkv, positions, cos_t, sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
+#define PKV_ROPE_VEC(A, C)                                                                                   \
+  return launch_kernel(rope_kv_store_vec_kernel<A, C>, dim3(n_tokens), dim3(vthreads), 0, s, true, 0, (A*)qkv, \
+                       positions, cos_t, sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
     if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_ROPE_VEC(float, float);
-    else if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(bf16, bf16);
-    else if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(float, bf16);
-    else if (act_dtype == PKV_BF16 && cache_dtype == PKV_F32) PKV_ROPE_VEC(bf16, float);
-    else return PKV_ERR_DTYPE;
+    if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(bf16, bf16);
+    if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(float, bf16);
+    if (act_dtype == PKV_BF16 && cache_dtype == PKV_F32) PKV_ROPE_VEC(bf16, float);
 #undef PKV_ROPE_VEC
-    return launch_status();
+    return PKV_ERR_DTYPE;
   }
   int threads = ((hd / 2 + 31) / 32) * 32;
   if (threads > 256) threads = 256;
   dim3 grid(n_tokens, n_heads + 2 * n_kv);
-#define PKV_ROPE(A, C) \
-  rope_kv_store_kernel<A, C><<<grid, threads, 0, s>>>((A*)qkv, positions, cos_t, sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
+#define PKV_ROPE(A, C)                                                                                           \
+  return launch_kernel(rope_kv_store_kernel<A, C>, grid, dim3(threads), 0, s, true, 0, (A*)qkv, positions, cos_t, \
+                       sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
   if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_ROPE(float, float);
-  else if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE(bf16, bf16);
-  else if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE(float, bf16);
-  else if (act_dtype == PKV_BF16 && cache_dtype == PKV_F32) PKV_ROPE(bf16, float);
-  else return PKV_ERR_DTYPE;
+  if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE(bf16, bf16);
+  if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE(float, bf16);
+  if (act_dtype == PKV_BF16 && cache_dtype == PKV_F32) PKV_ROPE(bf16, float);
 #undef PKV_ROPE
-  return launch_status();
+  return PKV_ERR_DTYPE;
 }

@@ -1,0 +1,354 @@
+// Matrix products of decode steps: a few rows of activations against a whole weight matrix,
+// out[M, N] = x[M, K] . w[N, K]^T in bfloat16 with float32 accumulation, for M up to 32.
+//
+// Such a product reads every weight once and does almost no arithmetic per byte, so the kernel is
+// built around the weight stream.
+//
+//  * The weight rows are the 16-row side of mma.sync.m16n8k16 and the activations its 8-wide
+//    side. A lane loads 16 contiguous bytes of a weight row straight from global memory into
+//    registers and uses them as the A fragments of two k-steps; the activations are loaded with
+//    the same pattern, so the order of k inside a 32-wide chunk is permuted in the same way on
+//    both sides and the dot products are unchanged. There is no shared-memory staging and no
+//    barrier in the main loop; two batches of weight loads are in flight per warp, and the
+//    activations, which every block reads again, come from L1 after an SM's first blocks.
+//  * The work (16-row tiles x 32-wide chunks of K) is dealt out evenly to two blocks per SM as
+//    contiguous ranges, whatever N and K are, so no SM idles in a last wave. Inside a block the
+//    eight warps split each tile's share of K and add their sums through shared memory in warp
+//    order. A block's range may begin and end inside a tile; such partial sums go through a
+//    workspace, and the block that delivers the last part of a tile adds the parts in block
+//    order. The result therefore depends on the sizes and the weights only, never on timing or
+//    on how many rows the batch has.
+//  * The first weights are requested before `griddepcontrol.wait`: launched as a programmatic
+//    dependent, the kernel streams weights while the kernel that produces its activations ends.
+//
+// Epilogues: bfloat16, float32, or silu(gate) * up for gate and up rows interleaved in blocks of
+// 128 (the layout of the fused feed-forward weight); the reference's feed-forward is
+// src/paged_kv_serving/engine/model.py:258-264.
+#include "common.cuh"
+
+namespace {
+
+using pkv::bf16;
+
+constexpr int SMALL_WARPS = 8;
+constexpr int SMALL_CHUNK = 32;           // k per chunk: 4 lanes x 8 elements
+constexpr int SMALL_MAX_TILES = 65536;    // counters in the workspace
+constexpr int SMALL_MAX_BLOCKS = 320;
+constexpr int SMALL_SLOT_FLOATS = 8 * 4 * 32;  // largest set of sums of a block
+constexpr int EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2;
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// weights are read once: past L1, and first to leave L2
+__device__ __forceinline__ uint64_t stream_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint4 load_stream(const void* p, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy));
+  return v;
+}
+
+struct SmallParams {
+  const bf16* x;
+  const bf16* w;
+  void* out;
+  float* partials;   // [blocks][2][SMALL_SLOT_FLOATS]
+  int* counters;     // [tiles], zero between launches
+  int M, N, K, ldx, ld_out, n_out;
+  int tiles, chunks;  // 16-row tiles (pairs of them with the fused activation), chunks of K per tile
+  float clip;
+};
+
+template <int RT, int EPI>
+__device__ __forceinline__ int tile_first_row(int tile, int r) {
+  if (EPI == EPI_SILU_MUL) return (tile >> 3) * 256 + (tile & 7) * 16 + r * 128;  // gate rows, then the up rows
+  return (tile * RT + r) * 16;
+}
+
+// Stores one value of a finished tile. Sum number `slot` = (r MT + j) 4 + i of lane l is weight
+// row first_row(r) + l/4 + 8 (i/2) against activation row 8 j + 2 (l%4) + i%2; with the fused
+// activation `s` is the gate sum and `up` the sum of the matching up row.
+template <int MT, int RT, int EPI>
+__device__ __forceinline__ void store_value(const SmallParams& p, int tile, int slot, int l, float s, float up) {
+  const int i = slot & 3, j = (slot >> 2) % MT, r = slot / (4 * MT);
+  const int m = j * 8 + 2 * (l & 3) + (i & 1);
+  const int row_in_tile = (l >> 2) + 8 * (i >> 1);
+  if (m >= p.M) return;
+  if (EPI == EPI_SILU_MUL) {
+    const int col = (tile >> 3) * 128 + (tile & 7) * 16 + row_in_tile;
+    if (col >= p.n_out) return;
+    const float clipped = fminf(fmaxf(s, -p.clip), p.clip);
+    const float act = s * (1.0f / (1.0f + expf(-clipped)));
+    reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ld_out + col] = __float2bfloat16_rn(act * up);
+  } else {
+    const int col = tile_first_row<RT, EPI>(tile, r) + row_in_tile;
+    if (col >= p.N) return;
+    if (EPI == EPI_F32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ld_out + col] = s;
+    else reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ld_out + col] = __float2bfloat16_rn(s);
+  }
+}
+
+// MT: 8-row groups of activations (M <= 8 MT). RT: 16-row weight tiles per unit of work.
+template <int MT, int RT, int EPI>
+__global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const SmallParams p) {
+  constexpr int DEPTH = 4 / RT;              // chunks per batch of loads
+  constexpr int SLOTS = RT * MT * 4;         // sums per lane
+  static_assert(SLOTS * 32 <= SMALL_SLOT_FLOATS, "a block's sums fit a workspace slot");
+  __shared__ float red[SMALL_WARPS][SLOTS][32];
+  __shared__ int is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const long long units = (long long)p.tiles * p.chunks;
+  const long long n_blocks = gridDim.x, me = blockIdx.x;
+  const long long range_begin = units * me / n_blocks, range_end = units * (me + 1) / n_blocks;
+  const uint64_t policy = stream_policy();
+
+  const bf16* xp[MT];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) xp[j] = p.x + (size_t)min(j * 8 + g, p.M - 1) * p.ldx + t * 8;
+  const bf16* wp[RT][2];
+  auto point_at_tile = [&](int tile) {
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+      const int row = tile_first_row<RT, EPI>(tile, r) + g;
+      wp[r][0] = p.w + (size_t)min(row, p.N - 1) * p.K + t * 8;
+      wp[r][1] = p.w + (size_t)min(row + 8, p.N - 1) * p.K + t * 8;
+    }
+  };
+  // the share of one warp in the chunks [cb, ce) of a tile
+  auto warp_share = [&](int cb, int ce, int& wb, int& we) {
+    const int per = (ce - cb + SMALL_WARPS - 1) / SMALL_WARPS;
+    wb = min(ce, cb + warp * per);
+    we = min(ce, wb + per);
+  };
+
+  float acc[RT][MT][4];
+  uint4 wa[2][DEPTH][RT][2];
+  auto load_batch = [&](int buf, int c) {
+#pragma unroll
+    for (int u = 0; u < DEPTH; ++u) {
+      const int cc = min(c + u, p.chunks - 1);  // past the share: a valid address, the value is unused
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        wa[buf][u][r][0] = load_stream(wp[r][0] + (size_t)cc * SMALL_CHUNK, policy);
+        wa[buf][u][r][1] = load_stream(wp[r][1] + (size_t)cc * SMALL_CHUNK, policy);
+      }
+    }
+  };
+  auto use_batch = [&](int buf, int c, int we) {
+#pragma unroll
+    for (int u = 0; u < DEPTH; ++u) {
+      if (c + u < we) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          // every block reads all activations; after the first blocks of an SM they come from L1
+          const uint4 xv = *reinterpret_cast<const uint4*>(xp[j] + (size_t)(c + u) * SMALL_CHUNK);
+#pragma unroll
+          for (int r = 0; r < RT; ++r) {
+            mma_16816(acc[r][j], wa[buf][u][r][0].x, wa[buf][u][r][1].x, wa[buf][u][r][0].y, wa[buf][u][r][1].y, xv.x, xv.y);
+            mma_16816(acc[r][j], wa[buf][u][r][0].z, wa[buf][u][r][1].z, wa[buf][u][r][0].w, wa[buf][u][r][1].w, xv.z, xv.w);
+          }
+        }
+      }
+    }
+  };
+
+  // first segment of this block's range
+  long long u0 = range_begin;
+  int tile = (int)(u0 / p.chunks);
+  int cb = (int)(u0 - (long long)tile * p.chunks);
+  int ce = (int)min((long long)p.chunks, cb + (range_end - u0));
+  int wb = 0, we = 0;
+  if (u0 < range_end) {
+    point_at_tile(tile);
+    warp_share(cb, ce, wb, we);
+    if (wb < we) load_batch(0, wb);
+  }
+  // the activations come from the kernel before this one; the weights above do not
+  pkv::wait_for_prior_kernels();
+
+  while (u0 < range_end) {
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+      for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.0f;
+    for (int c = wb; c < we; c += 2 * DEPTH) {
+      if (c + DEPTH < we) load_batch(1, c + DEPTH);
+      use_batch(0, c, we);
+      if (c + 2 * DEPTH < we) load_batch(0, c + 2 * DEPTH);
+      if (c + DEPTH < we) use_batch(1, c + DEPTH, we);
+    }
+    // request the first weights of the next segment before this one is added up
+    const int this_tile = tile, this_cb = cb, this_ce = ce;
+    u0 += ce - cb;
+    if (u0 < range_end) {
+      ++tile;
+      cb = 0;
+      ce = (int)min((long long)p.chunks, range_end - u0);
+      point_at_tile(tile);
+      warp_share(cb, ce, wb, we);
+      if (wb < we) load_batch(0, wb);
+    } else {
+      // This block has read its weights. Once every block has, the next kernel may take the
+      // places that free up and request its own first weights. (Earlier would be no gain: its
+      // blocks would sit beside blocks of this kernel that still wait for a place.)
+      pkv::dependents_may_launch();
+    }
+
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+      for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][(r * MT + j) * 4 + i][lane] = acc[r][j][i];
+    __syncthreads();
+
+    constexpr int OUT_SLOTS = (EPI == EPI_SILU_MUL) ? MT * 4 : SLOTS;  // with the activation a thread takes gate and up
+    const bool whole = this_cb == 0 && this_ce == p.chunks;
+    if (whole) {
+      for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
+        const int l = idx & 31, slot = idx >> 5;
+        float s = 0.0f, up = 0.0f;
+#pragma unroll
+        for (int wi = 0; wi < SMALL_WARPS; ++wi) s += red[wi][slot][l];
+        if (EPI == EPI_SILU_MUL) {
+#pragma unroll
+          for (int wi = 0; wi < SMALL_WARPS; ++wi) up += red[wi][slot + MT * 4][l];
+        }
+        store_value<MT, RT, EPI>(p, this_tile, slot, l, s, up);
+      }
+    } else {
+      // part of a tile: leave it in the workspace; the block that brings the last part adds them.
+      // The block that holds unit u is the last one whose range begins at or before u.
+      const long long tile_u0 = (long long)this_tile * p.chunks, tile_u1 = tile_u0 + p.chunks;
+      const long long b_lo = ((tile_u0 + 1) * n_blocks + units - 1) / units - 1;
+      const long long b_hi = (tile_u1 * n_blocks + units - 1) / units - 1;
+      float* mine = p.partials + ((size_t)me * 2 + (range_begin >= tile_u0 ? 0 : 1)) * SMALL_SLOT_FLOATS;
+      for (int idx = threadIdx.x; idx < SLOTS * 32; idx += SMALL_WARPS * 32) {
+        const int l = idx & 31, slot = idx >> 5;
+        float s = 0.0f;
+#pragma unroll
+        for (int wi = 0; wi < SMALL_WARPS; ++wi) s += red[wi][slot][l];
+        __stcg(mine + idx, s);
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) is_last = atomicAdd(p.counters + this_tile, 1) == (int)(b_hi - b_lo);
+      __syncthreads();
+      if (is_last) {
+        __threadfence();
+        for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
+          const int l = idx & 31, slot = idx >> 5;
+          float s = 0.0f, up = 0.0f;
+          for (long long q = b_lo; q <= b_hi; ++q) {
+            const long long q_begin = units * q / n_blocks;
+            const float* theirs = p.partials + ((size_t)q * 2 + (q_begin >= tile_u0 ? 0 : 1)) * SMALL_SLOT_FLOATS;
+            s += __ldcg(theirs + idx);
+            if (EPI == EPI_SILU_MUL) up += __ldcg(theirs + idx + MT * 4 * 32);
+          }
+          store_value<MT, RT, EPI>(p, this_tile, slot, l, s, up);
+        }
+        if (threadIdx.x == 0) p.counters[this_tile] = 0;  // ready for the next launch
+      }
+    }
+    __syncthreads();  // `red` and `is_last` are written again in the next round
+  }
+}
+
+int sm_count() {
+  static int count[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+  if (count[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 1;
+    count[device] = n;
+  }
+  return count[device];
+}
+
+template <int MT, int RT, int EPI>
+int launch_small(const SmallParams& p, int chained, cudaStream_t stream) {
+  // One block per tile is the cheapest arrangement (no tile is shared between blocks), but with a
+  // few waves of blocks, two to an SM, the last wave can be nearly empty. Then, and only then,
+  // the work is cut into one even range per place instead, at the price of some shared tiles.
+  const long long places = 2 * sm_count() < SMALL_MAX_BLOCKS ? 2 * sm_count() : SMALL_MAX_BLOCKS;
+  long long blocks = p.tiles;
+  if (p.tiles > 2 * places) {
+    const long long waves = (p.tiles + places - 1) / places;
+    if (waves * places * 10 > p.tiles * 11) blocks = places;   // more than a tenth of the places would idle
+  }
+  return pkv::launch_kernel(gemm_small_m_kernel<MT, RT, EPI>, dim3((unsigned)blocks), dim3(SMALL_WARPS * 32), 0, stream,
+                            chained != 0, 0, p);
+}
+
+template <int EPI>
+int dispatch_small(const SmallParams& p, int chained, cudaStream_t stream) {
+  constexpr int RT = (EPI == EPI_SILU_MUL) ? 2 : 1;
+  if (p.M <= 8) return launch_small<1, RT, EPI>(p, chained, stream);
+  if (p.M <= 16) return launch_small<2, RT, EPI>(p, chained, stream);
+  if (p.M <= 32) return launch_small<4, RT, EPI>(p, chained, stream);
+  return PKV_ERR_LIMIT;
+}
+
+}  // namespace
+
+// Largest number of activation rows that `pkv_gemm_small_m` takes with the given epilogue.
+PKV_EXPORT int pkv_gemm_small_m_max_rows(int epilogue) { (void)epilogue; return 32; }
+
+// Bytes of the workspace (partial sums and tile counters); it must be zero before its first use
+// and is left zero by every launch, so launches on one stream can share it.
+PKV_EXPORT long long pkv_gemm_small_m_workspace_bytes() {
+  return (long long)SMALL_MAX_BLOCKS * 2 * SMALL_SLOT_FLOATS * sizeof(float) + (long long)SMALL_MAX_TILES * sizeof(int);
+}
+
+// out = x . w^T. `x` is [M, K] with row stride `ldx` (elements), `w` [N, K] contiguous, both
+// bfloat16. Epilogue 0: bfloat16 out [M, N]; 1: float32 out [M, N]; 2: silu(gate) * up with the
+// gate and up rows of `w` interleaved in blocks of 128 (N a multiple of 256), bfloat16 out
+// [M, n_out], |gate| clipped to `clip` inside the exponential. K must be a multiple of 32.
+// `chained` non-zero launches as a programmatic dependent of the kernel before it on the stream:
+// the first weights are requested before that kernel has finished, the activations after.
+PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int epilogue,
+                                int n_out, float clip, int chained, void* workspace, long long workspace_bytes,
+                                void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return PKV_ERR_SIZE;
+  if (K % SMALL_CHUNK != 0 || ldx % 8 != 0) return PKV_ERR_SIZE;
+  if (M > pkv_gemm_small_m_max_rows(epilogue)) return PKV_ERR_LIMIT;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)workspace) & 15) return PKV_ERR_ALIGN;
+  if (!workspace || workspace_bytes < pkv_gemm_small_m_workspace_bytes()) return PKV_ERR_SIZE;
+  SmallParams p;
+  p.x = static_cast<const bf16*>(x);
+  p.w = static_cast<const bf16*>(w);
+  p.out = out;
+  p.partials = static_cast<float*>(workspace);
+  p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + (size_t)SMALL_MAX_BLOCKS * 2 * SMALL_SLOT_FLOATS * sizeof(float));
+  p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.clip = clip;
+  p.chunks = K / SMALL_CHUNK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (epilogue) {
+    case EPI_BF16:
+    case EPI_F32:
+      p.tiles = (N + 15) / 16; p.ld_out = N; p.n_out = N;
+      if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
+      return epilogue == EPI_BF16 ? dispatch_small<EPI_BF16>(p, chained, s) : dispatch_small<EPI_F32>(p, chained, s);
+    case EPI_SILU_MUL:
+      if (N % 256 != 0 || n_out <= 0 || n_out > N / 2) return PKV_ERR_SIZE;
+      p.tiles = (N / 256) * 8; p.ld_out = n_out; p.n_out = n_out;
+      if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
+      return dispatch_small<EPI_SILU_MUL>(p, chained, s);
+    default: return PKV_ERR_SIZE;
+  }
+}

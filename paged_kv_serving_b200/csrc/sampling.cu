@@ -85,6 +85,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, const floa
   __shared__ ArgMax scratch_a[32];
   __shared__ float shared_f;
   __shared__ int shared_i;
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int r = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * row_stride;
@@ -218,9 +220,8 @@ PKV_EXPORT int pkv_sample(const float* logits, long long row_stride, const float
                           float greedy_below, void* stream) {
   if (n_rows <= 0) return 0;
   if (vocab <= 0 || row_stride < vocab) return PKV_ERR_SIZE;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, temperature, top_p, uniform,
-                                                                    probs, out, vocab, greedy_below);
-  return launch_status();
+  return launch_kernel(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, true, 0, logits, row_stride,
+                       temperature, top_p, uniform, probs, out, vocab, greedy_below);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -5,7 +5,7 @@ rotates over 32 layers' worth of buffers (so that weights, keys and values come 
 a real step) and reports microseconds per launch with the achieved bandwidth or arithmetic rate.
 The sizes come from a preset of ``config/presets.py``; nothing here is used by the engine.
 
-    python -m paged_kv_serving_b200.kernel_bench [gemm] [prefill-attention] [decode-attention] [elementwise]
+    python -m paged_kv_serving_b200.kernel_bench [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise]
 """
 
 from __future__ import annotations
@@ -58,6 +58,42 @@ def bench_gemm(config, rows: int) -> None:
               f" | single {single:7.1f} us {flops / single / 1e6:6.0f} TFLOP/s"
               f" | cuBLAS (no epilogue) {lib:7.1f} us {flops / lib / 1e6:6.0f} TFLOP/s")
     assert int(status.item()) == 0
+
+
+def bench_decode_gemm(config) -> None:
+    """The four products of a layer at decode sizes, launched back to back as in a step, against cuBLAS."""
+    d, ff = config.d_model, config.d_ff
+    qkv = (config.n_heads + 2 * config.n_kv_heads) * config.head_dim
+    ff_rows = 2 * (-(-ff // 128) * 128)
+    copies = 3
+    weights = [[torch.randn(n, k, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+               for n, k in ((qkv, d), (d, config.n_heads * config.head_dim), (ff_rows, d), (d, ff))]
+    layer_bytes = 2.0 * sum(w[0].numel() for w in weights)
+    for rows in (1, 8, 16, 32):
+        x_d = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+        x_ff = torch.randn(rows, ff, device="cuda").to(torch.bfloat16)
+
+        def ours(i, chained=True):
+            ops.gemm_small_m(x_d, weights[0][i % copies], chained=chained)
+            ops.gemm_small_m(x_d, weights[1][i % copies], chained=chained)
+            if rows <= 32:
+                ops.gemm_small_m(x_d, weights[2][i % copies], "silu_mul", n_out=ff, chained=chained)
+            else:
+                ops.silu_mul(torch.mm(x_d, weights[2][i % copies].t()), 60.0, ff=ff, interleave=128)
+            ops.gemm_small_m(x_ff, weights[3][i % copies], chained=chained)
+
+        def lib(i):
+            torch.mm(x_d, weights[0][i % copies].t())
+            torch.mm(x_d, weights[1][i % copies].t())
+            ops.silu_mul(torch.mm(x_d, weights[2][i % copies].t()), 60.0, ff=ff, interleave=128)
+            torch.mm(x_ff, weights[3][i % copies].t())
+
+        t_chain = timed(ours, launches=12)
+        t_plain = timed(lambda i: ours(i, False), launches=12)
+        t_lib = timed(lib, launches=12)
+        print(f"decode products of one layer, {rows:2d} rows ({layer_bytes / 1e6:.0f} MB of weights): "
+              f"streaming kernel {t_chain:6.1f} us {layer_bytes / t_chain / 1e6:5.2f} TB/s"
+              f" | not chained {t_plain:6.1f} us | cuBLAS + activation kernel {t_lib:6.1f} us {layer_bytes / t_lib / 1e6:5.2f} TB/s")
 
 
 def _cache(config, batch: int, context: int, page: int):
@@ -149,7 +185,7 @@ def bench_elementwise(config, page: int) -> None:
 
 
 def main() -> int:
-    cases = {"gemm": None, "prefill-attention": bench_prefill_attention, "decode-attention": bench_decode_attention,
+    cases = {"gemm": None, "decode-gemm": None, "prefill-attention": bench_prefill_attention, "decode-attention": bench_decode_attention,
              "elementwise": bench_elementwise}
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("cases", nargs="*", choices=[*cases, []], help="which kernels to time (default: all)")
@@ -161,6 +197,8 @@ def main() -> int:
     for name in args.cases or list(cases):
         if name == "gemm":
             bench_gemm(config, args.rows)
+        elif name == "decode-gemm":
+            bench_decode_gemm(config)
         else:
             cases[name](config, args.page_size)
     return 0

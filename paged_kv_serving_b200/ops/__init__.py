@@ -19,7 +19,8 @@ __all__ = [
     "attention_decode_blocks_per_sm", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
     "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
-    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
+    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_small_m", "gemm_small_m_supports",
+    "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
     "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
 ]
 
@@ -418,6 +419,64 @@ def gemm_tcgen05(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epil
     _check(fn(_ptr(a), a.stride(0), _ptr(b_nk), b_nk.stride(0), _ptr(out), out.stride(0), m, n, k,
               GEMM_EPILOGUES[epilogue], int(n_out), float(clip), _ptr(workspace),
               workspace.numel() if workspace is not None else 0, _ptr(status), _stream()), "gemm_tcgen05")
+    return out
+
+
+SMALL_M_MAX_ROWS = {"bf16": 32, "f32": 32, "silu_mul": 32}
+
+
+def gemm_small_m_supports(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16") -> bool:
+    """Whether the weight-streaming product for few rows takes these operands: bfloat16, at most
+    ``SMALL_M_MAX_ROWS[epilogue]`` rows, an inner size that is a multiple of 32, contiguous
+    weights and 16-byte aligned rows."""
+    return (a.dtype == torch.bfloat16 and b_nk.dtype == torch.bfloat16 and a.dim() == 2 and b_nk.dim() == 2
+            and 0 < a.shape[0] <= SMALL_M_MAX_ROWS[epilogue] and a.shape[1] % 32 == 0 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and b_nk.is_contiguous() and a.data_ptr() % 16 == 0 and b_nk.data_ptr() % 16 == 0
+            and (epilogue != "silu_mul" or b_nk.shape[0] % 256 == 0))
+
+
+_SMALL_M_WORKSPACE: dict[str, torch.Tensor] = {}
+
+
+def _small_m_workspace(device: torch.device) -> torch.Tensor:
+    """Partial sums and tile counters of ``gemm_small_m`` on a device: allocated and zeroed once,
+    left zero by every launch, shared by the launches of a stream."""
+    key = str(torch.device(device))
+    if key not in _SMALL_M_WORKSPACE:
+        lib = library("gemm_small_m")
+        lib.pkv_gemm_small_m_workspace_bytes.restype = c_longlong
+        _SMALL_M_WORKSPACE[key] = torch.zeros((int(lib.pkv_gemm_small_m_workspace_bytes()),), dtype=torch.uint8, device=device)
+    return _SMALL_M_WORKSPACE[key]
+
+
+def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_out: int = 0, clip: float = 60.0,
+                 chained: bool = True) -> torch.Tensor:
+    """``a [M, K] @ b_nk [N, K]^T`` for the few rows of a decode step: the weights stream from
+    memory through registers into ``mma.sync`` (bfloat16 in, float32 accumulate), every weight
+    read once. Epilogues as in ``gemm_tcgen05``. ``chained`` launches the kernel as a programmatic
+    dependent of the one before it on the stream, so that it requests its first weights while
+    that kernel is still running; it reads ``a`` only after that kernel has finished."""
+    if epilogue not in GEMM_EPILOGUES:
+        raise ValueError(f"unknown epilogue {epilogue!r}")
+    for name, t in (("a", a), ("b_nk", b_nk)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a bfloat16 CUDA matrix with contiguous rows")
+    if not b_nk.is_contiguous():
+        raise ValueError("b_nk must be contiguous")
+    m, k = a.shape
+    n = b_nk.shape[0]
+    if b_nk.shape[1] != k:
+        raise ValueError("inner sizes differ")
+    if epilogue == "silu_mul":
+        out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
+    else:
+        out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
+    fn = _fn("gemm_small_m", "pkv_gemm_small_m",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+              c_longlong, c_void_p])
+    workspace = _small_m_workspace(a.device)
+    _check(fn(_ptr(a), _ptr(b_nk), _ptr(out), m, n, k, a.stride(0), GEMM_EPILOGUES[epilogue], int(n_out), float(clip),
+              1 if chained else 0, _ptr(workspace), workspace.numel(), _stream()), "gemm_small_m")
     return out
 
 

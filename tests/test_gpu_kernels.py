@@ -431,6 +431,73 @@ def test_gemm_tcgen05_refuses_unaligned_operands():
     assert ops.gemm_tcgen05(a, b, status, "f32").shape == (4, 12)
 
 
+@pytest.mark.parametrize("chained", [True, False])
+@pytest.mark.parametrize("m, n, k", [(1, 16, 32), (3, 331, 96), (8, 520, 4096), (9, 100, 160), (16, 1000, 2048), (17, 72, 1792),
+                                     (32, 4096, 320), (25, 250, 64), (31, 6144, 512)])
+@pytest.mark.parametrize("epilogue", ["bf16", "f32"])
+def test_gemm_small_m(m, n, k, epilogue, chained):
+    """The weight-streaming product of decode steps against a float64 product of the same
+    operands: every row-count bucket and its edge, weight rows that are no multiple of 16, inner
+    sizes that leave warps without work or with uneven shares; a row's result does not change
+    with the rows beside it."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(m * 7 + n + k)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    assert ops.gemm_small_m_supports(a, b, epilogue)
+    out = ops.gemm_small_m(a, b, epilogue, chained=chained)
+    want = a.double() @ b.double().t()
+    scale = float(want.abs().max())
+    bound = 1e-5 * scale if epilogue == "f32" else 2 ** -8 * scale
+    assert out.shape == (m, n) and float((out.double() - want).abs().max()) <= bound
+    alone = ops.gemm_small_m(a[m - 1:], b, epilogue, chained=chained)
+    assert torch.equal(alone[0], out[m - 1])
+    wide = torch.zeros((m, k + 8), dtype=torch.bfloat16, device="cuda")
+    wide[:, :k] = a
+    assert torch.equal(ops.gemm_small_m(wide[:, :k], b, epilogue, chained=chained), out)
+
+
+@pytest.mark.parametrize("m, ff, k", [(1, 128, 32), (8, 200, 96), (13, 1000, 256), (32, 392, 2048), (20, 3000, 544)])
+def test_gemm_small_m_silu_mul_epilogue(m, ff, k):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(ff + m)
+    blocks = -(-ff // 128)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    gate = torch.from_numpy(rng.standard_normal((ff, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    up = torch.from_numpy(rng.standard_normal((ff, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    fused = torch.zeros((blocks, 2, 128, k), dtype=torch.bfloat16, device="cuda")
+    for b in range(blocks):
+        rows = min(128, ff - 128 * b)
+        fused[b, 0, :rows] = gate[128 * b:128 * b + rows]
+        fused[b, 1, :rows] = up[128 * b:128 * b + rows]
+    out = ops.gemm_small_m(a, fused.view(-1, k), "silu_mul", n_out=ff)
+    g, u = (a.float() @ gate.float().t()).cpu().numpy(), (a.float() @ up.float().t()).cpu().numpy()
+    want = plain_model.silu(g) * u
+    assert out.shape == (m, ff)
+    assert np.abs(as_np(out) - want).max() <= 2 ** -8 * np.abs(want).max() + 1e-6
+
+
+def test_gemm_small_m_refusals():
+    from paged_kv_serving_b200 import ops
+
+    a = torch.zeros((4, 40), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((16, 40), dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_small_m_supports(a, b)                     # inner size no multiple of 32
+    with pytest.raises(ValueError, match="size"):
+        ops.gemm_small_m(a, b)
+    a = torch.zeros((33, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((512, 64), dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_small_m_supports(a, b)                     # at most 32 rows
+    with pytest.raises(ValueError, match="limit"):
+        ops.gemm_small_m(a, b)
+    assert not ops.gemm_small_m_supports(a, b, "silu_mul")
+    with pytest.raises(ValueError, match="limit"):
+        ops.gemm_small_m(a, b, "silu_mul", n_out=256)
+    assert not ops.gemm_small_m_supports(a[:4].float(), b.float())
+
+
 def test_sampling_kernel_greedy_ties_and_distribution():
     from paged_kv_serving_b200 import ops
 
