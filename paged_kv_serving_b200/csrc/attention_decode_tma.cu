@@ -81,7 +81,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ int abort_flag;
 
   dependents_may_launch();
-  wait_for_prior_kernels();
   const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_seq[blockIdx.z];
   const int group = p.n_heads / p.n_kv;
   const int tok0 = p.seq_starts[s];
@@ -115,6 +114,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (table_cached)
     for (int i = threadIdx.x; i <= entry_last - entry_first; i += DT_THREADS) table_cache[i] = table[entry_first + i];
   __syncthreads();
+  // Up to here only the step's index arrays were read, which the host wrote before the step's
+  // first kernel. The queries and the newest keys and values come from the kernel before this one.
+  wait_for_prior_kernels();
   volatile int* aborted = &abort_flag;
 
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
