@@ -138,6 +138,58 @@ def _register_toys():
                                blocks=blocks, order=[LayerCall(i) for i in range(config.n_layers)], final_norm=final,
                                names=names, embedding_name="embed", head_name=None)
 
+    @registry.register_part("feed_forward", "toy_routed")
+    class RoutedFeedForward(Part):
+        """Top-1 routing among a few small experts: router logits and their softmax in float32,
+        out = p[e] * (relu(x @ w_in[e]) @ w_out[e]) for the expert e with the largest logit
+        (lowest index on ties)."""
+
+        def __init__(self, width, inner, experts):
+            self.width, self.inner, self.experts = width, inner, experts
+            self.router = self.w_in = self.w_out = None
+
+        def param_specs(self):
+            return {"router": ParamSpec((self.width, self.experts)),
+                    "w_in": ParamSpec((self.experts * self.width, self.inner)),
+                    "w_out": ParamSpec((self.experts * self.inner, self.width))}
+
+        def forward(self, x, ctx):
+            logits = gemm.matmul(x, self.router).float()
+            probs = torch.softmax(logits, dim=-1)
+            choice = torch.argmax(logits, dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.experts):
+                rows = torch.nonzero(choice == e).flatten()
+                if rows.numel() == 0:
+                    continue
+                hidden = torch.relu(gemm.matmul(x[rows], self.w_in[e * self.width:(e + 1) * self.width]))
+                expert_out = gemm.matmul(hidden, self.w_out[e * self.inner:(e + 1) * self.inner])
+                out[rows] = (expert_out.float() * probs[rows, e:e + 1]).to(x.dtype)
+            return out
+
+    @registry.register_architecture("ToyRoutedDecoder")
+    class ToyRoutedDecoder:
+        """Llama-style attention in every layer; the feed-forward of odd layers is routed."""
+
+        @staticmethod
+        def layout(config):
+            from paged_kv_serving_b200.models.layout import collect_param_specs
+
+            blocks, names = [], {}
+            for i in range(config.n_layers):
+                mixer = PagedAttention(config.d_model, config.n_heads, config.n_kv_heads, config.head_dim,
+                                       RotaryEncoding(config.head_dim, config.rope_theta, config.max_seq_len))
+                ff = RoutedFeedForward(config.d_model, 40, 3) if i % 2 else SwiGLU(config.d_model, config.d_ff)
+                block = PreNormBlock(RMSNorm(config.d_model, config.norm_eps), mixer,
+                                     RMSNorm(config.d_model, config.norm_eps), ff)
+                blocks.append(block)
+                collect_param_specs(f"blocks.{i}.", block, names)
+            final = RMSNorm(config.d_model, config.norm_eps)
+            names["final.weight"] = (final, "weight")
+            return ModelLayout(width=config.d_model, vocab_size=config.vocab_size, max_positions=config.max_seq_len,
+                               blocks=blocks, order=[LayerCall(i) for i in range(config.n_layers)], final_norm=final,
+                               names=names, embedding_name="embed", head_name=None)
+
     @registry.register_architecture("ToySharedCacheDecoder")
     class ToySharedCacheDecoder:
         """Two Llama-style layers; run order: layer 0, layer 1 reading layer 0's keys and values
@@ -215,6 +267,66 @@ def test_toy_mixer_with_state_and_toy_position_encoding_register_build_and_step(
     # a slot that is taken again starts from a cleared state
     got = session.step([{"id": "c", "tokens": b[:20], "want": [19]}])
     helpers.assert_close(got, want_b[19:20], "float32", "toy reused slot")
+
+
+def test_toy_routed_feed_forward_registers_builds_and_steps():
+    """A feed-forward with routing, defined in this file, beside the dense one in other layers:
+    whole prompt, portions and decoding agree with a plain forward. The router's weights are
+    scaled so that the chosen expert is never a near tie that float32 rounding could flip."""
+    from paged_kv_serving_b200.config import ModelConfig, registry
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+
+    _register_toys()
+    c = dict(TOY, architecture="ToyRoutedDecoder", n_layers=4, n_kv_heads=3)
+    config = ModelConfig.from_dict(c)
+    specs = registry.architecture("ToyRoutedDecoder").layout(config).tensor_specs()
+    rng = np.random.default_rng(21)
+    tensors = {name: ((1 + 0.1 * rng.standard_normal(spec.shape)) if spec.kind == "vector"
+                      else rng.standard_normal(spec.shape) * (2.0 if name.endswith("router") else 0.15)).astype(np.float32)
+               for name, spec in specs.items()}
+
+    def plain(tokens):
+        cos, sin = plain_model.rope_tables(c["max_seq_len"], 16, 10000.0)
+        pos = np.arange(len(tokens))
+        x = tensors["embed"][np.asarray(tokens)]
+        margins = []
+        for i in range(c["n_layers"]):
+            p = f"blocks.{i}."
+            normed = plain_model.rms_norm(x, tensors[p + "mixer_norm.weight"], c["norm_eps"])
+            q, k, v = plain_model.project_qkv(normed, tensors[p + "mixer.qkv_proj"], 3, 3, 16)
+            q, k = plain_model.apply_rope(q, pos, cos, sin), plain_model.apply_rope(k, pos, cos, sin)
+            attended = plain_model.causal_attention(q, k, v, 1 / math.sqrt(16))
+            x = (x + attended.reshape(len(tokens), 48) @ tensors[p + "mixer.out_proj"]).astype(np.float32)
+            normed = plain_model.rms_norm(x, tensors[p + "ff_norm.weight"], c["norm_eps"])
+            if i % 2:
+                logits = (normed @ tensors[p + "feed_forward.router"]).astype(np.float32)
+                top = np.sort(logits, axis=-1)
+                margins.append(top[:, -1] - top[:, -2])
+                probs = np.exp(logits - logits.max(-1, keepdims=True))
+                probs /= probs.sum(-1, keepdims=True)
+                choice = logits.argmax(-1)
+                out = np.zeros_like(normed)
+                for t, e in enumerate(choice):
+                    hidden = np.maximum(normed[t] @ tensors[p + "feed_forward.w_in"][e * 48:(e + 1) * 48], 0)
+                    out[t] = probs[t, e] * (hidden @ tensors[p + "feed_forward.w_out"][e * 40:(e + 1) * 40])
+                x = (x + out).astype(np.float32)
+            else:
+                x = (x + plain_model.swiglu(normed, tensors[p + "feed_forward.gate_proj"],
+                                            tensors[p + "feed_forward.up_proj"],
+                                            tensors[p + "feed_forward.down_proj"])).astype(np.float32)
+        return plain_model.rms_norm(x, tensors["final.weight"], c["norm_eps"]) @ tensors["embed"].T, np.concatenate(margins)
+
+    tokens = [int(t) for t in rng.integers(0, 97, size=60)]
+    want, margins = plain(tokens)
+    assert margins.min() > 1e-3, "the test's weights must not put a token on a routing tie"
+    model = DecoderModel.from_tensors(config, {k: torch.from_numpy(v) for k, v in tensors.items()}, "float32", "cuda")
+    session = ReplaySession(model, max_tokens=128, block_size=8)
+    got = [session.step([{"id": "s", "tokens": tokens[:21], "want": list(range(21))}])]
+    got.append(session.step([{"id": "s", "tokens": tokens[21:23], "want": [0, 1]}]))
+    got.append(session.step([{"id": "s", "tokens": tokens[23:40], "want": list(range(17))}]))
+    got += [session.step([{"id": "s", "tokens": [t], "want": [0]}]) for t in tokens[40:]]
+    helpers.assert_close(np.concatenate(got), want, "float32", "routed feed-forward")
 
 
 def test_layer_order_may_repeat_a_layer_and_read_another_layers_cache():
