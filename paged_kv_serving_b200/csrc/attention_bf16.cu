@@ -306,7 +306,6 @@ __global__ void __launch_bounds__(AT_THREADS) attention_prefill_kernel(const Att
 // ---------------------------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const AttnParams p) {
-  dependents_may_launch();
   wait_for_prior_kernels();
   constexpr int LD = HD + AT_PAD;
   constexpr int KSTEPS = HD / 16;
@@ -434,6 +433,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     __syncthreads();
   }
 
+  dependents_may_launch();   // after the keys are read: see the note in attention_decode_tma.cu
   // ---- merge the four warps (each saw a quarter of the keys) ----
   cp_async_wait<0>();   // a split without tiles still has the copy of its queries in flight
   __syncthreads();

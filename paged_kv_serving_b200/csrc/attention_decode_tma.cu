@@ -80,7 +80,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ int32_t table_cache[DT_TABLE_CACHE];
   __shared__ int abort_flag;
 
-  dependents_may_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_seq[blockIdx.z];
   const int group = p.n_heads / p.n_kv;
   const int tok0 = p.seq_starts[s];
@@ -264,6 +263,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
     }
   }
+
+  // This block has read its keys and values. Once every block has, the next kernel may take the
+  // places that free up (earlier, its blocks would crowd onto the SMs this kernel leaves idle and
+  // start its work unevenly spread).
+  dependents_may_launch();
 
   // ---- merge the four consumer warps (each saw a quarter of the keys) ----
   __syncthreads();           // every copy that was waited for has landed; the ring is free

@@ -11,15 +11,17 @@
 //    both sides and the dot products are unchanged. There is no shared-memory staging and no
 //    barrier in the main loop; two batches of weight loads are in flight per warp, and the
 //    activations, which every block reads again, come from L1 after an SM's first blocks.
-//  * The work (16-row tiles x 32-wide chunks of K) is dealt out evenly to two blocks per SM as
-//    contiguous ranges, whatever N and K are, so no SM idles in a last wave. Inside a block the
-//    eight warps split each tile's share of K and add their sums through shared memory in warp
-//    order. A block's range may begin and end inside a tile; such partial sums go through a
-//    workspace, and the block that delivers the last part of a tile adds the parts in block
-//    order. The result therefore depends on the sizes and the weights only, never on timing or
-//    on how many rows the batch has.
+//  * The work is 16-row tiles x 32-wide chunks of K. A block takes one tile, or, where whole tiles
+//    would leave a last wave of blocks nearly empty, an even contiguous range of the work that may
+//    begin and end inside a tile. Inside a block the eight warps split each tile's share of K and
+//    add their sums through shared memory in warp order. Partial sums of a shared tile go through
+//    a workspace, and the block that delivers the last part adds the parts in block order. The
+//    result therefore depends on the sizes and the weights only, never on timing or on how many
+//    rows the batch has.
 //  * The first weights are requested before `griddepcontrol.wait`: launched as a programmatic
-//    dependent, the kernel streams weights while the kernel that produces its activations ends.
+//    dependent after a kernel that leaves the SMs mostly idle (a norm over a few rows), the
+//    kernel has its first weights on the way while that kernel ends. A block lets the next
+//    kernel start only when it has read its own weights.
 //
 // Epilogues: bfloat16, float32, or silu(gate) * up for gate and up rows interleaved in blocks of
 // 128 (the layout of the fused feed-forward weight); the reference's feed-forward is
@@ -67,6 +69,7 @@ struct SmallParams {
   int* counters;     // [tiles], zero between launches
   int M, N, K, ldx, ld_out, n_out;
   int tiles, chunks;  // 16-row tiles (pairs of them with the fused activation), chunks of K per tile
+  int share, extra;   // units per block: the first `extra` blocks take share + 1, the others share
   float clip;
 };
 
@@ -107,11 +110,13 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
   static_assert(SLOTS * 32 <= SMALL_SLOT_FLOATS, "a block's sums fit a workspace slot");
   __shared__ float red[SMALL_WARPS][SLOTS][32];
   __shared__ int is_last;
+  PKV_TRACE_NOTE(2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const long long units = (long long)p.tiles * p.chunks;
-  const long long n_blocks = gridDim.x, me = blockIdx.x;
-  const long long range_begin = units * me / n_blocks, range_end = units * (me + 1) / n_blocks;
+  // units of work (tile-major) [range_begin, range_end) of this block; fewer than 2^31 in all
+  const int me = blockIdx.x;
+  const int range_begin = me * p.share + min(me, p.extra);
+  const int range_end = range_begin + p.share + (me < p.extra ? 1 : 0);
   const uint64_t policy = stream_policy();
 
   const bf16* xp[MT];
@@ -165,10 +170,10 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
   };
 
   // first segment of this block's range
-  long long u0 = range_begin;
-  int tile = (int)(u0 / p.chunks);
-  int cb = (int)(u0 - (long long)tile * p.chunks);
-  int ce = (int)min((long long)p.chunks, cb + (range_end - u0));
+  int u0 = range_begin;
+  int tile = u0 / p.chunks;
+  int cb = u0 - tile * p.chunks;
+  int ce = min(p.chunks, cb + (range_end - u0));
   int wb = 0, we = 0;
   if (u0 < range_end) {
     point_at_tile(tile);
@@ -197,7 +202,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
     if (u0 < range_end) {
       ++tile;
       cb = 0;
-      ce = (int)min((long long)p.chunks, range_end - u0);
+      ce = min(p.chunks, range_end - u0);
       point_at_tile(tile);
       warp_share(cb, ce, wb, we);
       if (wb < we) load_batch(0, wb);
@@ -232,10 +237,11 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
       }
     } else {
       // part of a tile: leave it in the workspace; the block that brings the last part adds them.
-      // The block that holds unit u is the last one whose range begins at or before u.
-      const long long tile_u0 = (long long)this_tile * p.chunks, tile_u1 = tile_u0 + p.chunks;
-      const long long b_lo = ((tile_u0 + 1) * n_blocks + units - 1) / units - 1;
-      const long long b_hi = (tile_u1 * n_blocks + units - 1) / units - 1;
+      const int tile_u0 = this_tile * p.chunks, tile_u1 = tile_u0 + p.chunks;
+      const int big = p.extra * (p.share + 1);   // units held by the blocks that take share + 1
+      auto block_of = [&](int u) { return u < big ? u / (p.share + 1) : p.extra + (u - big) / p.share; };
+      auto begin_of = [&](int b) { return b * p.share + min(b, p.extra); };
+      const int b_lo = block_of(tile_u0), b_hi = block_of(tile_u1 - 1);
       float* mine = p.partials + ((size_t)me * 2 + (range_begin >= tile_u0 ? 0 : 1)) * SMALL_SLOT_FLOATS;
       for (int idx = threadIdx.x; idx < SLOTS * 32; idx += SMALL_WARPS * 32) {
         const int l = idx & 31, slot = idx >> 5;
@@ -246,16 +252,15 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
       }
       __threadfence();
       __syncthreads();
-      if (threadIdx.x == 0) is_last = atomicAdd(p.counters + this_tile, 1) == (int)(b_hi - b_lo);
+      if (threadIdx.x == 0) is_last = atomicAdd(p.counters + this_tile, 1) == b_hi - b_lo;
       __syncthreads();
       if (is_last) {
         __threadfence();
         for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
           const int l = idx & 31, slot = idx >> 5;
           float s = 0.0f, up = 0.0f;
-          for (long long q = b_lo; q <= b_hi; ++q) {
-            const long long q_begin = units * q / n_blocks;
-            const float* theirs = p.partials + ((size_t)q * 2 + (q_begin >= tile_u0 ? 0 : 1)) * SMALL_SLOT_FLOATS;
+          for (int q = b_lo; q <= b_hi; ++q) {
+            const float* theirs = p.partials + ((size_t)q * 2 + (begin_of(q) >= tile_u0 ? 0 : 1)) * SMALL_SLOT_FLOATS;
             s += __ldcg(theirs + idx);
             if (EPI == EPI_SILU_MUL) up += __ldcg(theirs + idx + MT * 4 * 32);
           }
@@ -281,16 +286,21 @@ int sm_count() {
 }
 
 template <int MT, int RT, int EPI>
-int launch_small(const SmallParams& p, int chained, cudaStream_t stream) {
+int launch_small(SmallParams p, int chained, cudaStream_t stream) {
   // One block per tile is the cheapest arrangement (no tile is shared between blocks), but with a
   // few waves of blocks, two to an SM, the last wave can be nearly empty. Then, and only then,
   // the work is cut into one even range per place instead, at the price of some shared tiles.
+  // (Even ranges for every size were timed too: slower inside a step for 1.3 waves, level for 27.)
   const long long places = 2 * sm_count() < SMALL_MAX_BLOCKS ? 2 * sm_count() : SMALL_MAX_BLOCKS;
   long long blocks = p.tiles;
   if (p.tiles > 2 * places) {
     const long long waves = (p.tiles + places - 1) / places;
     if (waves * places * 10 > p.tiles * 11) blocks = places;   // more than a tenth of the places would idle
   }
+  const long long units = (long long)p.tiles * p.chunks;
+  if (units >= (1ll << 31)) return PKV_ERR_LIMIT;
+  p.share = (int)(units / blocks);
+  p.extra = (int)(units % blocks);
   return pkv::launch_kernel(gemm_small_m_kernel<MT, RT, EPI>, dim3((unsigned)blocks), dim3(SMALL_WARPS * 32), 0, stream,
                             chained != 0, 0, p);
 }

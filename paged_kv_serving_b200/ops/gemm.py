@@ -4,8 +4,8 @@ Weights are held as ``[out, in]`` with the inner size contiguous. In bfloat16, p
 least ``TCGEN05_MIN_ROWS`` rows of activations (prompt portions) can run on the hand-written
 tcgen05/TMA kernels of ``csrc/gemm_tcgen05.cu``: the gate/up product of the feed-forward always
 does, with its SiLU-times-up step fused into the epilogue, the plain products when
-``PLAIN_PRODUCT_KERNEL`` says so. The few rows of a decode step can go to the weight-streaming
-kernel of ``csrc/gemm_small_m.cu`` (``SMALL_M_ROWS``). Everything else, and the float32 path, goes to cuBLAS
+``PLAIN_PRODUCT_KERNEL`` says so. The up to ``SMALL_M_ROWS`` rows of a decode step go to the
+weight-streaming kernel of ``csrc/gemm_small_m.cu``. Everything else, and the float32 path, goes to cuBLAS
 through ``torch.mm``, as the reference's engine hands its products to a library
 (src/paged_kv_serving/engine/model.py:249,258-259,264). Reduced-precision modes are switched
 off: float32 products use true float32 multiply-adds (no TF32), bfloat16 products accumulate in
@@ -35,14 +35,15 @@ USE_TCGEN05 = True
 #: the last wave of tiles), while the fused gate/up product is faster here than cuBLAS followed by
 #: an activation kernel, so the library keeps the plain ones.
 PLAIN_PRODUCT_KERNEL = "library"
-#: Products with at most this many rows (decode steps) go to the weight-streaming kernel of
-#: ``csrc/gemm_small_m.cu`` (it takes up to 32); 0 sends them to cuBLAS. The default is 0: timed
-#: alone, back to back on rotating weights, the kernel is level with cuBLAS plus the activation
-#: kernel at 1 to 8 rows and behind it from 16 rows on (it re-reads the activations for every 16
-#: weight rows), but inside a whole decode step of an 8-billion-parameter model it was 4 to 10 %
-#: slower at batch 8 and 18 % slower at batch 1, so the library keeps these products.
-SMALL_M_ROWS = 0
-#: Whether that kernel is launched as a programmatic dependent of the kernel before it.
+#: Products with at most this many rows (decode steps) and a bfloat16 result go to the
+#: weight-streaming kernel of ``csrc/gemm_small_m.cu`` (it takes up to 32 rows); 0 sends them to
+#: cuBLAS. Inside a decode step of an 8-billion-parameter model the kernel is level with cuBLAS
+#: plus the activation kernel at batch 8 and 3 to 4 % ahead at batch 1; from 16 rows on it falls
+#: behind (it re-reads the activations for every 16 weight rows). The LM head (float32 result, one
+#: long stream per step) stays with cuBLAS, which reaches the memory's copy rate there.
+SMALL_M_ROWS = 8
+#: Whether that kernel is launched as a programmatic dependent where the caller says that the
+#: kernel before it is a light one (``after_light_kernel``).
 SMALL_M_CHAINED = True
 
 
@@ -62,12 +63,18 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     return torch.mm(x, w)
 
 
-def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``x [T, K] @ w_nk [N, K]^T``; ``out_dtype`` float32 keeps the float32 accumulator."""
+def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = None,
+           after_light_kernel: bool = False) -> torch.Tensor:
+    """``x [T, K] @ w_nk [N, K]^T``; ``out_dtype`` float32 keeps the float32 accumulator.
+
+    ``after_light_kernel``: the kernel before this product on the stream leaves most SMs idle (a
+    norm over a few rows), so the weight-streaming kernel may start beside it and request its first
+    weights early. After a kernel that fills the GPU (attention, another product) an early start
+    only spreads its blocks unevenly, and it is launched the ordinary way."""
     wants_f32 = out_dtype == torch.float32
-    if (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
-            and ops.gemm_small_m_supports(x, w_nk, "f32" if wants_f32 else "bf16")):
-        return ops.gemm_small_m(x, w_nk, "f32" if wants_f32 else "bf16", chained=SMALL_M_CHAINED)
+    if (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS and not wants_f32
+            and ops.gemm_small_m_supports(x, w_nk, "bf16")):
+        return ops.gemm_small_m(x, w_nk, "bf16", chained=SMALL_M_CHAINED and after_light_kernel)
     # rows of the output must start on 16-byte boundaries for the kernel's vector stores
     if (PLAIN_PRODUCT_KERNEL == "tcgen05" and w_nk.shape[0] % (4 if wants_f32 else 8) == 0
             and _own_kernel(x, w_nk)):
@@ -75,12 +82,14 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
     return matmul(x, w_nk.t(), out_dtype)
 
 
-def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleave: int, clip: float) -> torch.Tensor:
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleave: int, clip: float,
+                    after_light_kernel: bool = False) -> torch.Tensor:
     """``silu(x @ gate^T) * (x @ up^T)`` for gate and up rows held in one matrix (``interleave``
     as in ``ops.silu_mul``); ``[T, ff]``."""
     if (USE_TCGEN05 and interleave == 128 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
             and ops.gemm_small_m_supports(x, w_gate_up, "silu_mul")):
-        return ops.gemm_small_m(x, w_gate_up, "silu_mul", n_out=ff, clip=clip, chained=SMALL_M_CHAINED)
+        return ops.gemm_small_m(x, w_gate_up, "silu_mul", n_out=ff, clip=clip,
+                                chained=SMALL_M_CHAINED and after_light_kernel)
     if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and _own_kernel(x, w_gate_up):
         # one SM per tile: with this many tiles the two-SM kernel's split of the last wave costs
         # more than it saves

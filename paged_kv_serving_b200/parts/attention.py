@@ -191,7 +191,7 @@ class PagedAttention(Part):
         group = ctx.groups[binding.group]
         k_pool = group.k_pool[binding.index]
         v_pool = group.v_pool[binding.index]
-        qkv = gemm.linear(x, self.qkv_proj)
+        qkv = gemm.linear(x, self.qkv_proj, after_light_kernel=True)
         positions = ctx.ints(ctx.POSITIONS)
         tables = self.position.fused_tables(ctx.device)
         if tables is None:

@@ -65,5 +65,5 @@ class SwiGLU(Part):
         self.down_proj = params["down_proj"].t().contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gated = gemm.linear_silu_mul(x, self.gate_up, self.inner, self.interleave, self.clip)
+        gated = gemm.linear_silu_mul(x, self.gate_up, self.inner, self.interleave, self.clip, after_light_kernel=True)
         return gemm.linear(gated, self.down_proj)
