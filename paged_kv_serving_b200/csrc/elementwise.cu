@@ -144,6 +144,27 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const D* __re
   }
 }
 
+// Completes an RMS norm that a matrix-product kernel left in two pieces (csrc/gemm_small_m.cu,
+// residual epilogue): `xw` is the stream times the norm's weight, `sumsq[part][row]` the sums of
+// squares of the stream per 16-column tile. out = xw / sqrt(sum / d + eps). One block per row.
+__global__ void finish_norm_kernel(const bf16* __restrict__ xw, const float* __restrict__ sumsq, int parts, float eps,
+                                   bf16* __restrict__ out, int d) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  __shared__ float inv_root;
+  const int row = blockIdx.x;
+  if (threadIdx.x < 32) {   // the same order of additions as the product kernel that reads these sums
+    float q = 0.0f;
+    for (int part = threadIdx.x; part < parts; part += 32) q += sumsq[part * 32 + row];
+    q = warp_sum(q);
+    if (threadIdx.x == 0) inv_root = 1.0f / sqrtf(q / (float)d + eps);
+  }
+  __syncthreads();
+  const float r = inv_root;
+  for (int c = threadIdx.x; c < d; c += blockDim.x)
+    out[(size_t)row * d + c] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)row * d + c]) * r);
+}
+
 // ---------------------------------------------------------------------------------------------
 // SiLU(gate) * up over a fused [T, 2*ff] input (gate columns first), output [T, ff]
 // ---------------------------------------------------------------------------------------------
@@ -357,6 +378,14 @@ PKV_EXPORT int pkv_add_rmsnorm(float* hidden, const void* delta, int delta_dtype
   if (delta_dtype == PKV_BF16 && out_dtype == PKV_F32)
     return launch_add_rmsnorm<bf16, float>(hidden, delta, weight, eps, out, rows, n_rows, d, s);
   return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_finish_norm(const void* xw, const float* sumsq, int parts, float eps, void* out, int n_rows, int d,
+                               void* stream) {
+  if (n_rows <= 0) return 0;
+  if (d <= 0 || parts <= 0 || n_rows > 32) return PKV_ERR_SIZE;
+  return launch_kernel(finish_norm_kernel, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, true, 0, (const bf16*)xw, sumsq,
+                       parts, eps, (bf16*)out, d);
 }
 
 PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, int ff, int in_stride,

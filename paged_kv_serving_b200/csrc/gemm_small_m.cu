@@ -37,7 +37,7 @@ constexpr int SMALL_CHUNK = 32;           // k per chunk: 4 lanes x 8 elements
 constexpr int SMALL_MAX_TILES = 65536;    // counters in the workspace
 constexpr int SMALL_MAX_BLOCKS = 320;
 constexpr int SMALL_SLOT_FLOATS = 8 * 4 * 32;  // largest set of sums of a block
-constexpr int EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2;
+constexpr int EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESIDUAL = 3;
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -71,6 +71,17 @@ struct SmallParams {
   int tiles, chunks;  // 16-row tiles (pairs of them with the fused activation), chunks of K per tile
   int share, extra;   // units per block: the first `extra` blocks take share + 1, the others share
   float clip;
+  // epilogue 3 (residual): the product is added to the float32 stream in place, the stream times
+  // the next norm's weight is stored in bfloat16, and each tile leaves the sum of squares of its
+  // 16 columns per row, so that the kernel that reads `xw` can finish the RMS norm by itself
+  float* hidden;             // [M, N]
+  const float* norm_weight;  // [N]
+  float* sumsq_out;          // [tiles][32]
+  // any epilogue: rows of the result are scaled by 1 / sqrt(sum of sumsq_in[.][row] / width + eps),
+  // which completes an RMS norm whose weight the producer already applied to `x`
+  const float* sumsq_in;     // [sumsq_parts][32], or null
+  int sumsq_parts;
+  float inv_width, norm_eps;
 };
 
 template <int RT, int EPI>
@@ -81,25 +92,39 @@ __device__ __forceinline__ int tile_first_row(int tile, int r) {
 
 // Stores one value of a finished tile. Sum number `slot` = (r MT + j) 4 + i of lane l is weight
 // row first_row(r) + l/4 + 8 (i/2) against activation row 8 j + 2 (l%4) + i%2; with the fused
-// activation `s` is the gate sum and `up` the sum of the matching up row.
+// activation `s` is the gate sum and `up` the sum of the matching up row. `inv_root` holds the
+// row scales (null: none). Returns the square of the new stream value (residual epilogue), else 0.
 template <int MT, int RT, int EPI>
-__device__ __forceinline__ void store_value(const SmallParams& p, int tile, int slot, int l, float s, float up) {
+__device__ __forceinline__ float store_value(const SmallParams& p, const float* inv_root, int tile, int slot, int l,
+                                             float s, float up) {
   const int i = slot & 3, j = (slot >> 2) % MT, r = slot / (4 * MT);
   const int m = j * 8 + 2 * (l & 3) + (i & 1);
   const int row_in_tile = (l >> 2) + 8 * (i >> 1);
-  if (m >= p.M) return;
+  if (m >= p.M) return 0.0f;
+  if (inv_root) {
+    s *= inv_root[m];
+    up *= inv_root[m];
+  }
   if (EPI == EPI_SILU_MUL) {
     const int col = (tile >> 3) * 128 + (tile & 7) * 16 + row_in_tile;
-    if (col >= p.n_out) return;
+    if (col >= p.n_out) return 0.0f;
     const float clipped = fminf(fmaxf(s, -p.clip), p.clip);
     const float act = s * (1.0f / (1.0f + expf(-clipped)));
     reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ld_out + col] = __float2bfloat16_rn(act * up);
-  } else {
-    const int col = tile_first_row<RT, EPI>(tile, r) + row_in_tile;
-    if (col >= p.N) return;
-    if (EPI == EPI_F32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ld_out + col] = s;
-    else reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ld_out + col] = __float2bfloat16_rn(s);
+    return 0.0f;
   }
+  const int col = tile_first_row<RT, EPI>(tile, r) + row_in_tile;
+  if (col >= p.N) return 0.0f;
+  const size_t at = (size_t)m * p.ld_out + col;
+  if (EPI == EPI_RESIDUAL) {
+    const float x = p.hidden[at] + s;
+    p.hidden[at] = x;
+    reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(x * p.norm_weight[col]);
+    return x * x;
+  }
+  if (EPI == EPI_F32) reinterpret_cast<float*>(p.out)[at] = s;
+  else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(s);
+  return 0.0f;
 }
 
 // MT: 8-row groups of activations (M <= 8 MT). RT: 16-row weight tiles per unit of work.
@@ -110,6 +135,8 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
   static_assert(SLOTS * 32 <= SMALL_SLOT_FLOATS, "a block's sums fit a workspace slot");
   __shared__ float red[SMALL_WARPS][SLOTS][32];
   __shared__ int is_last;
+  __shared__ float inv_root_s[32];
+  __shared__ float squares[EPI == EPI_RESIDUAL ? SLOTS * 32 : 1];
   PKV_TRACE_NOTE(2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -183,6 +210,18 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
   // the activations come from the kernel before this one; the weights above do not
   pkv::wait_for_prior_kernels();
 
+  const float* inv_root = nullptr;
+  if (p.sumsq_in != nullptr) {
+    // finish the norm of the rows: the parts are added in one fixed order
+    for (int m = warp; m < p.M; m += SMALL_WARPS) {
+      float q = 0.0f;
+      for (int part = lane; part < p.sumsq_parts; part += 32) q += p.sumsq_in[part * 32 + m];
+      q = pkv::warp_sum(q);
+      if (lane == 0) inv_root_s[m] = 1.0f / sqrtf(q * p.inv_width + p.norm_eps);
+    }
+    inv_root = inv_root_s;   // read after the block's next barrier
+  }
+
   while (u0 < range_end) {
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -223,6 +262,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
 
     constexpr int OUT_SLOTS = (EPI == EPI_SILU_MUL) ? MT * 4 : SLOTS;  // with the activation a thread takes gate and up
     const bool whole = this_cb == 0 && this_ce == p.chunks;
+    bool stored = whole;   // whether this block stored the tile (the same for all its threads)
     if (whole) {
       for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
         const int l = idx & 31, slot = idx >> 5;
@@ -233,7 +273,8 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
 #pragma unroll
           for (int wi = 0; wi < SMALL_WARPS; ++wi) up += red[wi][slot + MT * 4][l];
         }
-        store_value<MT, RT, EPI>(p, this_tile, slot, l, s, up);
+        const float q = store_value<MT, RT, EPI>(p, inv_root, this_tile, slot, l, s, up);
+        if (EPI == EPI_RESIDUAL) squares[idx] = q;
       }
     } else {
       // part of a tile: leave it in the workspace; the block that brings the last part adds them.
@@ -254,6 +295,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
       __syncthreads();
       if (threadIdx.x == 0) is_last = atomicAdd(p.counters + this_tile, 1) == b_hi - b_lo;
       __syncthreads();
+      stored = is_last != 0;
       if (is_last) {
         __threadfence();
         for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
@@ -264,12 +306,26 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
             s += __ldcg(theirs + idx);
             if (EPI == EPI_SILU_MUL) up += __ldcg(theirs + idx + MT * 4 * 32);
           }
-          store_value<MT, RT, EPI>(p, this_tile, slot, l, s, up);
+          const float q = store_value<MT, RT, EPI>(p, inv_root, this_tile, slot, l, s, up);
+          if (EPI == EPI_RESIDUAL) squares[idx] = q;
         }
         if (threadIdx.x == 0) p.counters[this_tile] = 0;  // ready for the next launch
       }
     }
-    __syncthreads();  // `red` and `is_last` are written again in the next round
+    if (EPI == EPI_RESIDUAL && stored) {
+      // the tile's sum of squares per activation row: its 16 columns in one fixed order
+      __syncthreads();
+      if (threadIdx.x < p.M) {
+        const int m = threadIdx.x, j = m >> 3, t4 = (m & 7) >> 1, odd = m & 1;
+        float q = 0.0f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int g8 = 0; g8 < 8; ++g8) q += squares[(j * 4 + half * 2 + odd) * 32 + g8 * 4 + t4];
+        p.sumsq_out[this_tile * 32 + m] = q;
+      }
+    }
+    __syncthreads();  // `red`, `is_last` and `squares` are written again in the next round
   }
 }
 
@@ -331,9 +387,17 @@ PKV_EXPORT long long pkv_gemm_small_m_workspace_bytes() {
 // [M, n_out], |gate| clipped to `clip` inside the exponential. K must be a multiple of 32.
 // `chained` non-zero launches as a programmatic dependent of the kernel before it on the stream:
 // the first weights are requested before that kernel has finished, the activations after.
+//
+// Epilogue 3 (residual): hidden [M, N] (float32) += product, in place;
+// out (bfloat16 [M, N]) = hidden * norm_weight; sumsq_out [ceil(N/16)][32] (float32) receives, per
+// 16-column tile and row, the sum of squares of the new stream. A later call that is given that
+// array as `sumsq_in` (with `sumsq_parts` = ceil(N/16), `width` = N and `norm_eps`) and `out` as
+// its `x` scales its result rows by 1 / sqrt(sum / width + eps): together the residual add, the
+// RMS norm and the next product in two launches instead of three.
 PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int epilogue,
                                 int n_out, float clip, int chained, void* workspace, long long workspace_bytes,
-                                void* stream) {
+                                float* hidden, const float* norm_weight, float* sumsq_out, const float* sumsq_in,
+                                int sumsq_parts, int width, float norm_eps, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return PKV_ERR_SIZE;
   if (K % SMALL_CHUNK != 0 || ldx % 8 != 0) return PKV_ERR_SIZE;
   if (M > pkv_gemm_small_m_max_rows(epilogue)) return PKV_ERR_LIMIT;
@@ -346,6 +410,9 @@ PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, 
   p.partials = static_cast<float*>(workspace);
   p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + (size_t)SMALL_MAX_BLOCKS * 2 * SMALL_SLOT_FLOATS * sizeof(float));
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.clip = clip;
+  p.hidden = hidden; p.norm_weight = norm_weight; p.sumsq_out = sumsq_out;
+  p.sumsq_in = sumsq_in; p.sumsq_parts = sumsq_parts; p.norm_eps = norm_eps; p.inv_width = width > 0 ? 1.0f / (float)width : 0.0f;
+  if (sumsq_in && (sumsq_parts <= 0 || width <= 0)) return PKV_ERR_SIZE;
   p.chunks = K / SMALL_CHUNK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (epilogue) {
@@ -354,6 +421,11 @@ PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, 
       p.tiles = (N + 15) / 16; p.ld_out = N; p.n_out = N;
       if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
       return epilogue == EPI_BF16 ? dispatch_small<EPI_BF16>(p, chained, s) : dispatch_small<EPI_F32>(p, chained, s);
+    case EPI_RESIDUAL:
+      if (!hidden || !norm_weight || !sumsq_out) return PKV_ERR_SIZE;
+      p.tiles = (N + 15) / 16; p.ld_out = N; p.n_out = N;
+      if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
+      return dispatch_small<EPI_RESIDUAL>(p, chained, s);
     case EPI_SILU_MUL:
       if (N % 256 != 0 || n_out <= 0 || n_out > N / 2) return PKV_ERR_SIZE;
       p.tiles = (N / 256) * 8; p.ld_out = n_out; p.n_out = n_out;

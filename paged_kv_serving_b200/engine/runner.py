@@ -252,9 +252,16 @@ class ModelRunner:
         data on the host, so the whole sequence can be captured in a CUDA graph."""
         model = self.model
         hidden = ops.embedding_gather(model.embedding, ctx.ints(StepContext.TOKEN_IDS), self._status)
+        blocks = model.layout.blocks
         delta = None
-        for call, binding in zip(self.order, self.bindings):
-            delta = model.layout.blocks[call.layer].forward(hidden, delta, ctx, binding)
+        for i, (call, binding) in enumerate(zip(self.order, self.bindings)):
+            # the block may carry the next block's first norm in the tail of its last kernel; the
+            # last block hands on its plain update (the final norm takes only the wanted rows)
+            following = blocks[self.order[i + 1].layer] if i + 1 < len(self.order) else None
+            if following is not None and getattr(following, "first_norm", None) is not None:
+                delta = blocks[call.layer].forward(hidden, delta, ctx, binding, next_norm=following.first_norm)
+            else:
+                delta = blocks[call.layer].forward(hidden, delta, ctx, binding)
         if not want_logits:
             return None
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))

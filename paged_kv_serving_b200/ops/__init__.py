@@ -19,7 +19,7 @@ __all__ = [
     "attention_decode_blocks_per_sm", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
     "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
-    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "gemm_small_m", "gemm_small_m_supports",
+    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
     "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
     "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
 ]
@@ -450,13 +450,23 @@ def _small_m_workspace(device: torch.device) -> torch.Tensor:
 
 
 def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_out: int = 0, clip: float = 60.0,
-                 chained: bool = True) -> torch.Tensor:
+                 chained: bool = True, residual: tuple[torch.Tensor, torch.Tensor] | None = None,
+                 row_norm: tuple[torch.Tensor, float] | None = None):
     """``a [M, K] @ b_nk [N, K]^T`` for the few rows of a decode step: the weights stream from
     memory through registers into ``mma.sync`` (bfloat16 in, float32 accumulate), every weight
     read once. Epilogues as in ``gemm_tcgen05``. ``chained`` launches the kernel as a programmatic
     dependent of the one before it on the stream, so that it requests its first weights while
-    that kernel is still running; it reads ``a`` only after that kernel has finished."""
-    if epilogue not in GEMM_EPILOGUES:
+    that kernel is still running; it reads ``a`` only after that kernel has finished.
+
+    ``residual = (hidden, norm_weight)`` (instead of an epilogue): the product is added to the
+    float32 stream ``hidden [M, N]`` in place; returned are ``hidden * norm_weight`` in bfloat16 and
+    the sums of squares of the new stream per 16-column tile and row, ``[ceil(N / 16), 32]``.
+    ``row_norm = (sumsq, eps)`` with such sums: ``a`` is taken to be such a weighted stream and the
+    rows of the result are divided by ``sqrt(sum / K + eps)``. The two together are a residual add,
+    an RMS norm and the next product in two launches instead of three."""
+    if residual is not None:
+        epilogue = "residual"
+    if epilogue not in GEMM_EPILOGUES and epilogue != "residual":
         raise ValueError(f"unknown epilogue {epilogue!r}")
     for name, t in (("a", a), ("b_nk", b_nk)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
@@ -467,16 +477,43 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
     n = b_nk.shape[0]
     if b_nk.shape[1] != k:
         raise ValueError("inner sizes differ")
+    hidden = weight = sumsq_out = sumsq_in = None
+    parts, eps = 0, 0.0
+    if residual is not None:
+        hidden, weight = residual
+        _need(hidden, torch.float32, "hidden"); _need(weight, torch.float32, "norm weight")
+        if hidden.shape != (m, n) or weight.numel() != n:
+            raise ValueError("the residual epilogue needs a stream and a norm weight as wide as the product")
+        sumsq_out = torch.empty((-(-n // 16), 32), dtype=torch.float32, device=a.device)
+    if row_norm is not None:
+        sumsq_in, eps = row_norm
+        _need(sumsq_in, torch.float32, "sums of squares")
+        if sumsq_in.dim() != 2 or sumsq_in.shape[1] != 32:
+            raise ValueError("sums of squares must be [parts, 32]")
+        parts = sumsq_in.shape[0]
     if epilogue == "silu_mul":
         out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
     else:
         out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
     fn = _fn("gemm_small_m", "pkv_gemm_small_m",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
-              c_longlong, c_void_p])
+              c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
     workspace = _small_m_workspace(a.device)
-    _check(fn(_ptr(a), _ptr(b_nk), _ptr(out), m, n, k, a.stride(0), GEMM_EPILOGUES[epilogue], int(n_out), float(clip),
-              1 if chained else 0, _ptr(workspace), workspace.numel(), _stream()), "gemm_small_m")
+    code = 3 if epilogue == "residual" else GEMM_EPILOGUES[epilogue]
+    _check(fn(_ptr(a), _ptr(b_nk), _ptr(out), m, n, k, a.stride(0), code, int(n_out), float(clip),
+              1 if chained else 0, _ptr(workspace), workspace.numel(), _ptr(hidden), _ptr(weight), _ptr(sumsq_out),
+              _ptr(sumsq_in), parts, k, float(eps), _stream()), "gemm_small_m")
+    return (out, sumsq_out) if residual is not None else out
+
+
+def finish_norm(xw: torch.Tensor, sumsq: torch.Tensor, eps: float) -> torch.Tensor:
+    """The RMS-normalised rows from the two pieces that ``gemm_small_m(..., residual=...)`` leaves:
+    ``xw / sqrt(sum(sumsq) / width + eps)``, bfloat16."""
+    _need(xw, torch.bfloat16, "xw"); _need(sumsq, torch.float32, "sums of squares")
+    rows, d = xw.shape
+    out = torch.empty_like(xw)
+    fn = _fn("elementwise", "pkv_finish_norm", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(xw), _ptr(sumsq), sumsq.shape[0], float(eps), _ptr(out), rows, d, _stream()), "finish_norm")
     return out
 
 

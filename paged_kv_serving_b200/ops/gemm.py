@@ -18,7 +18,7 @@ import torch
 
 from paged_kv_serving_b200 import ops
 
-__all__ = ["TCGEN05_MIN_ROWS", "linear", "linear_silu_mul", "matmul"]
+__all__ = ["PendingNorm", "TCGEN05_MIN_ROWS", "as_tensor", "linear", "linear_add_norm", "linear_silu_mul", "matmul"]
 
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
@@ -47,6 +47,39 @@ SMALL_M_ROWS = 8
 SMALL_M_CHAINED = True
 
 
+class PendingNorm:
+    """RMS-normalised rows that have not been divided by their root mean square yet: ``weighted``
+    is the stream times the norm's weight (bfloat16), ``sumsq [parts, 32]`` the sums of squares
+    of the stream per 16-column tile and row. ``linear`` and ``linear_silu_mul`` take it in place
+    of a tensor and divide their result rows instead (a product is linear in its rows); anything
+    else calls ``tensor()``."""
+
+    __slots__ = ("weighted", "sumsq", "eps")
+
+    def __init__(self, weighted: torch.Tensor, sumsq: torch.Tensor, eps: float) -> None:
+        self.weighted, self.sumsq, self.eps = weighted, sumsq, float(eps)
+
+    @property
+    def shape(self):
+        return self.weighted.shape
+
+    @property
+    def dtype(self):
+        return self.weighted.dtype
+
+    def tensor(self) -> torch.Tensor:
+        return ops.finish_norm(self.weighted, self.sumsq, self.eps)
+
+
+def as_tensor(x: "torch.Tensor | PendingNorm") -> torch.Tensor:
+    return x.tensor() if isinstance(x, PendingNorm) else x
+
+
+def _small_m(x: torch.Tensor, w_nk: torch.Tensor, epilogue: str) -> bool:
+    return (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
+            and ops.gemm_small_m_supports(x, w_nk, epilogue))
+
+
 def _own_kernel(x: torch.Tensor, w_nk: torch.Tensor) -> bool:
     return (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] >= TCGEN05_MIN_ROWS
             and ops.gemm_tcgen05_supports(x, w_nk))
@@ -72,8 +105,12 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
     weights early. After a kernel that fills the GPU (attention, another product) an early start
     only spreads its blocks unevenly, and it is launched the ordinary way."""
     wants_f32 = out_dtype == torch.float32
-    if (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS and not wants_f32
-            and ops.gemm_small_m_supports(x, w_nk, "bf16")):
+    if isinstance(x, PendingNorm):
+        if not wants_f32 and _small_m(x.weighted, w_nk, "bf16"):
+            return ops.gemm_small_m(x.weighted, w_nk, "bf16", chained=SMALL_M_CHAINED and after_light_kernel,
+                                    row_norm=(x.sumsq, x.eps))
+        x = x.tensor()
+    if not wants_f32 and _small_m(x, w_nk, "bf16"):
         return ops.gemm_small_m(x, w_nk, "bf16", chained=SMALL_M_CHAINED and after_light_kernel)
     # rows of the output must start on 16-byte boundaries for the kernel's vector stores
     if (PLAIN_PRODUCT_KERNEL == "tcgen05" and w_nk.shape[0] % (4 if wants_f32 else 8) == 0
@@ -82,12 +119,31 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
     return matmul(x, w_nk.t(), out_dtype)
 
 
+def linear_add_norm(x: torch.Tensor, w_nk: torch.Tensor, hidden: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                    out_dtype: torch.dtype, after_light_kernel: bool = False) -> "torch.Tensor | PendingNorm":
+    """``hidden += x @ w_nk^T`` (the float32 stream, in place) and the RMS-normalised stream in
+    ``out_dtype``. For the few rows of a decode step the weight-streaming kernel adds the product
+    to the stream in its epilogue and leaves the norm as a ``PendingNorm`` for the product that
+    reads it; otherwise it is the product followed by the add-and-norm kernel."""
+    x = as_tensor(x)
+    if out_dtype == torch.bfloat16 and w_nk.shape[0] % 32 == 0 and _small_m(x, w_nk, "bf16"):
+        # the width of the stream is the inner size of the product that reads it: a multiple of 32
+        weighted, sumsq = ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and after_light_kernel,
+                                           residual=(hidden, norm_weight))
+        return PendingNorm(weighted, sumsq, eps)
+    return ops.add_rmsnorm(hidden, linear(x, w_nk, after_light_kernel=after_light_kernel), norm_weight, eps, out_dtype)
+
+
 def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleave: int, clip: float,
                     after_light_kernel: bool = False) -> torch.Tensor:
     """``silu(x @ gate^T) * (x @ up^T)`` for gate and up rows held in one matrix (``interleave``
     as in ``ops.silu_mul``); ``[T, ff]``."""
-    if (USE_TCGEN05 and interleave == 128 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
-            and ops.gemm_small_m_supports(x, w_gate_up, "silu_mul")):
+    if isinstance(x, PendingNorm):
+        if interleave == 128 and _small_m(x.weighted, w_gate_up, "silu_mul"):
+            return ops.gemm_small_m(x.weighted, w_gate_up, "silu_mul", n_out=ff, clip=clip,
+                                    chained=SMALL_M_CHAINED and after_light_kernel, row_norm=(x.sumsq, x.eps))
+        x = x.tensor()
+    if interleave == 128 and _small_m(x, w_gate_up, "silu_mul"):
         return ops.gemm_small_m(x, w_gate_up, "silu_mul", n_out=ff, clip=clip,
                                 chained=SMALL_M_CHAINED and after_light_kernel)
     if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and _own_kernel(x, w_gate_up):

@@ -2,7 +2,7 @@
 
 from paged_kv_serving_b200.parts.attention import PagedAttention
 from paged_kv_serving_b200.parts.base import (
-    CacheBinding, GroupView, IntArena, PagedKVRequest, ParamSpec, Part, StateRequest, StepContext,
+    CacheBinding, GroupView, IntArena, Normed, PagedKVRequest, ParamSpec, Part, StateRequest, StepContext,
 )
 from paged_kv_serving_b200.parts.block import PreNormBlock
 from paged_kv_serving_b200.parts.feed_forward import SwiGLU
@@ -10,7 +10,7 @@ from paged_kv_serving_b200.parts.norms import RMSNorm
 from paged_kv_serving_b200.parts.position import NoPositionEncoding, PositionEncoding, RotaryEncoding
 
 __all__ = [
-    "CacheBinding", "GroupView", "IntArena", "NoPositionEncoding", "PagedAttention", "PagedKVRequest",
+    "CacheBinding", "GroupView", "IntArena", "NoPositionEncoding", "Normed", "PagedAttention", "PagedKVRequest",
     "ParamSpec", "Part", "PositionEncoding", "PreNormBlock", "RMSNorm", "RotaryEncoding", "StateRequest",
     "StepContext", "SwiGLU",
 ]

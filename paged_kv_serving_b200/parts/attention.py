@@ -187,7 +187,11 @@ class PagedAttention(Part):
         ctx.arena.add(seq_name, work_seq)
         ctx.arena.add(row_name, work_row0)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
+    fuses_last_linear = True
+    accepts_pending_norm = True
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, finish=None) -> torch.Tensor:
+        project_out = finish if finish is not None else gemm.linear
         group = ctx.groups[binding.group]
         k_pool = group.k_pool[binding.index]
         v_pool = group.v_pool[binding.index]
@@ -204,13 +208,13 @@ class PagedAttention(Part):
                           self.n_heads, self.n_kv_heads, self.head_dim, group.page_size)
         if self._fast(ctx):
             attended = self._attend_fast(qkv, ctx, group, k_pool, v_pool)
-            return gemm.linear(attended, self.out_proj)
+            return project_out(attended, self.out_proj)
         seq_name, row_name = self._work_names()
         attended = ops.paged_attention_generic(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.head_dim,
             group.page_size, self.window or 0, self.scale)
-        return gemm.linear(attended, self.out_proj)
+        return project_out(attended, self.out_proj)
 
     def _attend_fast(self, qkv, ctx: StepContext, group, k_pool, v_pool) -> torch.Tensor:
         plan = ctx.scratch[self._fast_key(group.page_size)]

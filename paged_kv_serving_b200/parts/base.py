@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 __all__ = [
-    "CacheBinding", "GroupView", "IntArena", "PagedKVRequest", "ParamSpec", "Part", "StateRequest",
+    "CacheBinding", "GroupView", "IntArena", "Normed", "PagedKVRequest", "ParamSpec", "Part", "StateRequest",
     "StepContext",
 ]
 
@@ -77,10 +77,30 @@ class Part:
     #: data, no host-dependent control flow), so that a step may be captured in a CUDA graph.
     graph_safe = False
 
+    #: True for a mixer or feed-forward whose ``forward`` ends in a matrix product and accepts
+    #: ``finish``: a callable ``finish(x, w_nk)`` that stands for ``x @ w_nk^T`` followed by
+    #: whatever the caller does with it next (the residual add and the following norm), so that
+    #: one kernel can do both. ``forward`` then returns what ``finish`` returned.
+    fuses_last_linear = False
+
+    #: True for a mixer or feed-forward that hands its input straight to ``ops.gemm.linear`` or
+    #: ``linear_silu_mul`` and so can take an ``ops.gemm.PendingNorm`` in place of a tensor.
+    accepts_pending_norm = False
+
     def plan_step(self, ctx: "StepContext", binding: "CacheBinding | None") -> None:
         """Called once per layer call before a step's kernels run, on the host: a part that needs
         integer arrays on the device (work lists, tables) adds them to ``ctx.arena`` here, so that
         everything a step needs crosses to the device in one copy."""
+
+
+@dataclass(slots=True)
+class Normed:
+    """What a block may hand on instead of a pending residual update: the stream has already
+    taken the update, and ``values`` is the stream normalised by ``norm`` (the first norm of the
+    block that comes next)."""
+
+    values: torch.Tensor
+    norm: object
 
 
 class IntArena:

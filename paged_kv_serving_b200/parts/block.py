@@ -5,7 +5,8 @@ from __future__ import annotations
 import torch
 
 from paged_kv_serving_b200.config.registry import register_part
-from paged_kv_serving_b200.parts.base import CacheBinding, Part, StepContext
+from paged_kv_serving_b200.ops import gemm
+from paged_kv_serving_b200.parts.base import CacheBinding, Normed, Part, StepContext
 
 __all__ = ["PreNormBlock"]
 
@@ -42,9 +43,34 @@ class PreNormBlock(Part):
         for child in self.sub_parts().values():
             child.plan_step(ctx, binding)
 
-    def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx: StepContext,
-                binding: CacheBinding | None) -> torch.Tensor:
-        normed = self.mixer_norm.add_norm(hidden, delta, ctx.dtype)
-        mixed = self.mixer.forward(normed, ctx, binding)
-        normed = self.ff_norm.add_norm(hidden, mixed, ctx.dtype)
+    @property
+    def first_norm(self) -> Part:
+        """The norm this block applies to the stream it is given (with the pending update)."""
+        return self.mixer_norm
+
+    def forward(self, hidden: torch.Tensor, pending: "torch.Tensor | Normed | None", ctx: StepContext,
+                binding: CacheBinding | None, next_norm: Part | None = None) -> "torch.Tensor | Normed":
+        """One layer call. ``pending`` is what the block before handed on: its residual update not
+        yet added (a tensor, or None at the start), or a ``Normed`` when it already added it and
+        applied this block's first norm. ``next_norm`` is the first norm of the block that runs
+        next; where the feed-forward can carry the residual add and that norm in the tail of its
+        last product, this block hands on a ``Normed``, else its own pending update.
+        """
+        if isinstance(pending, Normed) and pending.norm is self.mixer_norm:
+            normed = pending.values if self.mixer.accepts_pending_norm else gemm.as_tensor(pending.values)
+        else:
+            if isinstance(pending, Normed):
+                raise ValueError("the stream was normalised for another block than the one that runs next")
+            normed = self.mixer_norm.add_norm(hidden, pending, ctx.dtype)
+        follow = getattr(self.ff_norm, "add_norm_of_linear", None)
+        if self.mixer.fuses_last_linear and follow is not None:
+            normed = self.mixer.forward(normed, ctx, binding, finish=lambda x, w: follow(hidden, x, w, ctx.dtype))
+        else:
+            normed = self.ff_norm.add_norm(hidden, self.mixer.forward(normed, ctx, binding), ctx.dtype)
+        if not self.feed_forward.accepts_pending_norm:
+            normed = gemm.as_tensor(normed)
+        follow = getattr(next_norm, "add_norm_of_linear", None)
+        if self.feed_forward.fuses_last_linear and follow is not None:
+            values = self.feed_forward.forward(normed, ctx, finish=lambda x, w: follow(hidden, x, w, ctx.dtype))
+            return Normed(values, next_norm)
         return self.feed_forward.forward(normed, ctx)

@@ -64,6 +64,11 @@ class SwiGLU(Part):
             self.interleave = 0
         self.down_proj = params["down_proj"].t().contiguous()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    fuses_last_linear = True
+    accepts_pending_norm = True
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, finish=None) -> torch.Tensor:
         gated = gemm.linear_silu_mul(x, self.gate_up, self.inner, self.interleave, self.clip, after_light_kernel=True)
+        if finish is not None:
+            return finish(gated, self.down_proj)
         return gemm.linear(gated, self.down_proj)

@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from paged_kv_serving_b200 import ops
+from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.parts.base import ParamSpec, Part
 
@@ -33,3 +34,9 @@ class RMSNorm(Part):
         """``hidden += delta`` in place, then the normalised rows (all, or only ``rows``; with
         ``rows`` the stream itself is not updated)."""
         return ops.add_rmsnorm(hidden, delta, self.weight, self.eps, out_dtype, rows)
+
+    def add_norm_of_linear(self, hidden: torch.Tensor, x: torch.Tensor, w_nk: torch.Tensor,
+                           out_dtype: torch.dtype) -> torch.Tensor:
+        """``add_norm(hidden, x @ w_nk^T)`` for a producer whose last step is that product: one
+        launch where the product's kernel can carry the add and the norm in its tail."""
+        return gemm.linear_add_norm(x, w_nk, hidden, self.weight, self.eps, out_dtype)

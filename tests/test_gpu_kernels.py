@@ -479,6 +479,38 @@ def test_gemm_small_m_silu_mul_epilogue(m, ff, k):
     assert np.abs(as_np(out) - want).max() <= 2 ** -8 * np.abs(want).max() + 1e-6
 
 
+@pytest.mark.parametrize("m, d, k, n", [(1, 64, 32, 48), (5, 352, 96, 100), (8, 4096, 512, 256), (13, 992, 64, 520),
+                                        (32, 256, 2048, 72)])
+def test_gemm_small_m_residual_epilogue_and_row_norm(m, d, k, n):
+    """Residual add, RMS norm and the next product in two launches: the first product adds itself
+    to the float32 stream and leaves the stream times the norm's weight with per-tile sums of
+    squares; the second divides its rows by the root mean square. Against the plain formulas,
+    twice in a row on the same stream; the small kernel that completes the norm by itself too."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(m + d)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((d, k)).astype(np.float32) * 0.2).cuda().to(torch.bfloat16)
+    nxt = torch.from_numpy(rng.standard_normal((n, d)).astype(np.float32) * 0.2).cuda().to(torch.bfloat16)
+    weight = torch.from_numpy((1 + 0.1 * rng.standard_normal(d)).astype(np.float32)).cuda()
+    stream = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float32)).cuda()
+    eps = 1e-5
+    for _ in range(2):
+        before = as_np(stream)
+        weighted, sumsq = ops.gemm_small_m(a, b, residual=(stream, weight))
+        product = (a.double() @ b.double().t()).cpu().numpy()
+        want_stream = before + product
+        assert np.abs(as_np(stream) - want_stream).max() <= 2e-6 * np.abs(want_stream).max()
+        assert sumsq.shape == (-(-d // 16), 32)
+        assert np.allclose(as_np(sumsq)[:, :m].sum(axis=0), (want_stream ** 2).sum(axis=1), rtol=1e-5)
+        want_normed = plain_model.rms_norm(want_stream.astype(np.float32), as_np(weight), eps)
+        normed = ops.finish_norm(weighted, sumsq, eps)
+        assert np.abs(as_np(normed) - want_normed).max() <= 2 ** -7 * np.abs(want_normed).max() + 1e-6
+        got = ops.gemm_small_m(weighted, nxt, "f32", row_norm=(sumsq, eps))
+        want = want_normed.astype(np.float64) @ as_np(nxt).astype(np.float64).T
+        assert np.abs(as_np(got) - want).max() <= 2 ** -7 * np.abs(want).max() + 1e-5
+
+
 def test_gemm_small_m_refusals():
     from paged_kv_serving_b200 import ops
 
