@@ -37,7 +37,7 @@ constexpr int SMALL_CHUNK = 32;           // k per chunk: 4 lanes x 8 elements
 constexpr int SMALL_MAX_TILES = 65536;    // counters in the workspace
 constexpr int SMALL_MAX_BLOCKS = 320;
 constexpr int SMALL_SLOT_FLOATS = 8 * 4 * 32;  // largest set of sums of a block
-constexpr int EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESIDUAL = 3;
+constexpr int EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESIDUAL = 3, EPI_ROPE_KV = 4;
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -82,6 +82,16 @@ struct SmallParams {
   const float* sumsq_in;     // [sumsq_parts][32], or null
   int sumsq_parts;
   float inv_width, norm_eps;
+  // epilogue 4 (rotary + cache): `w` is a fused q/k/v projection; queries and keys are rotated by
+  // their row's position (half-split pairs), queries go to `out`, keys and values to the paged
+  // pools [pages, n_kv, page_size, head_dim] at `slots` (null or -1: nothing is stored)
+  const int32_t* positions;  // [M]
+  const float* cos_t;        // [positions][head_dim / 2]
+  const float* sin_t;
+  bf16* k_pool;
+  bf16* v_pool;
+  const int32_t* slots;      // [M] or null
+  int n_heads, n_kv, head_dim, page_size;
 };
 
 template <int RT, int EPI>
@@ -96,7 +106,7 @@ __device__ __forceinline__ int tile_first_row(int tile, int r) {
 // row scales (null: none). Returns the square of the new stream value (residual epilogue), else 0.
 template <int MT, int RT, int EPI>
 __device__ __forceinline__ float store_value(const SmallParams& p, const float* inv_root, int tile, int slot, int l,
-                                             float s, float up) {
+                                             float s, float up, float early_a = 0.0f, float early_b = 0.0f) {
   const int i = slot & 3, j = (slot >> 2) % MT, r = slot / (4 * MT);
   const int m = j * 8 + 2 * (l & 3) + (i & 1);
   const int row_in_tile = (l >> 2) + 8 * (i >> 1);
@@ -116,16 +126,56 @@ __device__ __forceinline__ float store_value(const SmallParams& p, const float* 
   const int col = tile_first_row<RT, EPI>(tile, r) + row_in_tile;
   if (col >= p.N) return 0.0f;
   const size_t at = (size_t)m * p.ld_out + col;
-  if (EPI == EPI_RESIDUAL) {
-    const float x = p.hidden[at] + s;
+  if (EPI == EPI_RESIDUAL) {   // early_a, early_b: the stream's value and the norm weight, loaded ahead
+    const float x = early_a + s;
     p.hidden[at] = x;
-    reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(x * p.norm_weight[col]);
+    reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(x * early_b);
     return x * x;
   }
   if (EPI == EPI_F32) reinterpret_cast<float*>(p.out)[at] = s;
   else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(s);
   return 0.0f;
 }
+
+// Rotary epilogue: `lo` and `hi` are element e = 8 (tile % (head_dim / 16)) + l/4 of a head's first
+// half and its partner e + head_dim/2, for activation row 8 j + 2 (l%4) + odd.
+template <int MT>
+__device__ __forceinline__ void store_rotated(const SmallParams& p, const float* inv_root, int tile, int j, int odd, int l,
+                                              float lo, float hi, float c, float sn, int slot) {
+  const int m = j * 8 + 2 * (l & 3) + odd;
+  if (m >= p.M) return;
+  if (inv_root) {
+    lo *= inv_root[m];
+    hi *= inv_root[m];
+  }
+  const int per_head = p.head_dim >> 4, head = tile / per_head, half = p.head_dim >> 1;
+  const int e = (tile - head * per_head) * 8 + (l >> 2);
+  if (head >= p.n_heads + 2 * p.n_kv) return;
+  const bool is_v = head >= p.n_heads + p.n_kv;
+  if (!is_v && p.cos_t != nullptr) {   // c, sn: loaded ahead for this row's position and element e
+    const float a = lo * c - hi * sn, b = hi * c + lo * sn;
+    lo = a;
+    hi = b;
+  }
+  if (head < p.n_heads) {
+    bf16* q = reinterpret_cast<bf16*>(p.out) + (size_t)m * p.ld_out + (size_t)head * p.head_dim + e;
+    q[0] = __float2bfloat16_rn(lo);
+    q[half] = __float2bfloat16_rn(hi);
+    return;
+  }
+  if (slot < 0) return;
+  const int page = slot / p.page_size, off = slot - page * p.page_size;
+  const int kvh = is_v ? head - p.n_heads - p.n_kv : head - p.n_heads;
+  bf16* dst = (is_v ? p.v_pool : p.k_pool) + (((size_t)page * p.n_kv + kvh) * p.page_size + off) * p.head_dim + e;
+  dst[0] = __float2bfloat16_rn(lo);
+  dst[half] = __float2bfloat16_rn(hi);
+}
+
+// How many values (or pairs of values) the threads of a block finish per tile.
+template <int MT, int RT, int EPI>
+struct OUT_COUNT {
+  static constexpr int VALUE = (EPI == EPI_SILU_MUL ? MT * 4 : (EPI == EPI_ROPE_KV ? MT * 2 : RT * MT * 4)) * 32;
+};
 
 // MT: 8-row groups of activations (M <= 8 MT). RT: 16-row weight tiles per unit of work.
 template <int MT, int RT, int EPI>
@@ -153,9 +203,16 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
   auto point_at_tile = [&](int tile) {
 #pragma unroll
     for (int r = 0; r < RT; ++r) {
-      const int row = tile_first_row<RT, EPI>(tile, r) + g;
+      int row = tile_first_row<RT, EPI>(tile, r) + g, partner = row + 8;
+      if (EPI == EPI_ROPE_KV) {
+        // a tile holds 8 elements of a head's first half and the 8 they are rotated with, so that
+        // one thread ends up with both values of a pair
+        const int per_head = p.head_dim >> 4, head = tile / per_head;
+        row = head * p.head_dim + (tile - head * per_head) * 8 + g;
+        partner = row + (p.head_dim >> 1);
+      }
       wp[r][0] = p.w + (size_t)min(row, p.N - 1) * p.K + t * 8;
-      wp[r][1] = p.w + (size_t)min(row + 8, p.N - 1) * p.K + t * 8;
+      wp[r][1] = p.w + (size_t)min(partner, p.N - 1) * p.K + t * 8;
     }
   };
   // the share of one warp in the chunks [cb, ce) of a tile
@@ -222,7 +279,43 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
     inv_root = inv_root_s;   // read after the block's next barrier
   }
 
+  // What an epilogue needs besides the sums (the stream's old values and the norm weight; the
+  // rotation's cosine, sine and cache slot) is requested when a tile begins, not when it ends.
+  constexpr int EARLY = (EPI == EPI_RESIDUAL || EPI == EPI_ROPE_KV) ? (OUT_COUNT<MT, RT, EPI>::VALUE + SMALL_WARPS * 32 - 1) / (SMALL_WARPS * 32) : 1;
+  float early_a[EARLY], early_b[EARLY];
+  int early_slot[EARLY];
+
   while (u0 < range_end) {
+    if (EPI == EPI_RESIDUAL || EPI == EPI_ROPE_KV) {
+#pragma unroll
+      for (int it = 0; it < EARLY; ++it) {
+        const int idx = threadIdx.x + it * SMALL_WARPS * 32;
+        early_a[it] = early_b[it] = 0.0f;
+        early_slot[it] = -1;
+        if (idx >= OUT_COUNT<MT, RT, EPI>::VALUE) continue;
+        const int l = idx & 31;
+        if (EPI == EPI_RESIDUAL) {
+          const int slot = idx >> 5, i = slot & 3, j = (slot >> 2) % MT;
+          const int m = j * 8 + 2 * (l & 3) + (i & 1), col = tile * 16 + (l >> 2) + 8 * (i >> 1);
+          if (m < p.M && col < p.N) {
+            early_a[it] = p.hidden[(size_t)m * p.ld_out + col];
+            early_b[it] = p.norm_weight[col];
+          }
+        } else {
+          const int m = (idx >> 6) * 8 + 2 * (l & 3) + ((idx >> 5) & 1);
+          if (m < p.M) {
+            const int per_head = p.head_dim >> 4, head = tile / per_head;
+            const int e = (tile - head * per_head) * 8 + (l >> 2);
+            if (p.cos_t != nullptr && head < p.n_heads + p.n_kv) {
+              const size_t at = (size_t)p.positions[m] * (p.head_dim >> 1) + e;
+              early_a[it] = p.cos_t[at];
+              early_b[it] = p.sin_t[at];
+            }
+            if (p.slots != nullptr && head >= p.n_heads) early_slot[it] = p.slots[m];
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int r = 0; r < RT; ++r)
 #pragma unroll
@@ -260,21 +353,34 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
         for (int i = 0; i < 4; ++i) red[warp][(r * MT + j) * 4 + i][lane] = acc[r][j][i];
     __syncthreads();
 
-    constexpr int OUT_SLOTS = (EPI == EPI_SILU_MUL) ? MT * 4 : SLOTS;  // with the activation a thread takes gate and up
+    // A thread finishes one sum, or two that belong together: gate and up of the fused activation
+    // (slots s and s + 4 MT), or a rotary pair (slots 4 j + odd and 4 j + 2 + odd).
+    constexpr int OUT_SLOTS = (EPI == EPI_SILU_MUL) ? MT * 4 : (EPI == EPI_ROPE_KV ? MT * 2 : SLOTS);
+    auto first_slot = [](int idx) { return EPI == EPI_ROPE_KV ? ((idx >> 6) * 4 + ((idx >> 5) & 1)) : (idx >> 5); };
+    constexpr int SECOND = EPI == EPI_SILU_MUL ? MT * 4 : 2;   // distance to the second slot, where there is one
+    constexpr bool PAIRED = EPI == EPI_SILU_MUL || EPI == EPI_ROPE_KV;
+    auto emit = [&](int idx, int slot, int l, float s, float up) {
+      const int it = EARLY > 1 ? idx / (SMALL_WARPS * 32) : 0;
+      if (EPI == EPI_ROPE_KV) {
+        store_rotated<MT>(p, inv_root, this_tile, slot >> 2, slot & 1, l, s, up, early_a[it], early_b[it], early_slot[it]);
+      } else {
+        const float q = store_value<MT, RT, EPI>(p, inv_root, this_tile, slot, l, s, up, early_a[it], early_b[it]);
+        if (EPI == EPI_RESIDUAL) squares[idx] = q;
+      }
+    };
     const bool whole = this_cb == 0 && this_ce == p.chunks;
     bool stored = whole;   // whether this block stored the tile (the same for all its threads)
     if (whole) {
       for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
-        const int l = idx & 31, slot = idx >> 5;
+        const int l = idx & 31, slot = first_slot(idx);
         float s = 0.0f, up = 0.0f;
 #pragma unroll
         for (int wi = 0; wi < SMALL_WARPS; ++wi) s += red[wi][slot][l];
-        if (EPI == EPI_SILU_MUL) {
+        if (PAIRED) {
 #pragma unroll
-          for (int wi = 0; wi < SMALL_WARPS; ++wi) up += red[wi][slot + MT * 4][l];
+          for (int wi = 0; wi < SMALL_WARPS; ++wi) up += red[wi][slot + SECOND][l];
         }
-        const float q = store_value<MT, RT, EPI>(p, inv_root, this_tile, slot, l, s, up);
-        if (EPI == EPI_RESIDUAL) squares[idx] = q;
+        emit(idx, slot, l, s, up);
       }
     } else {
       // part of a tile: leave it in the workspace; the block that brings the last part adds them.
@@ -299,15 +405,14 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, 2) gemm_small_m_kernel(const
       if (is_last) {
         __threadfence();
         for (int idx = threadIdx.x; idx < OUT_SLOTS * 32; idx += SMALL_WARPS * 32) {
-          const int l = idx & 31, slot = idx >> 5;
+          const int l = idx & 31, slot = first_slot(idx);
           float s = 0.0f, up = 0.0f;
           for (int q = b_lo; q <= b_hi; ++q) {
             const float* theirs = p.partials + ((size_t)q * 2 + (begin_of(q) >= tile_u0 ? 0 : 1)) * SMALL_SLOT_FLOATS;
-            s += __ldcg(theirs + idx);
-            if (EPI == EPI_SILU_MUL) up += __ldcg(theirs + idx + MT * 4 * 32);
+            s += __ldcg(theirs + slot * 32 + l);
+            if (PAIRED) up += __ldcg(theirs + (slot + SECOND) * 32 + l);
           }
-          const float q = store_value<MT, RT, EPI>(p, inv_root, this_tile, slot, l, s, up);
-          if (EPI == EPI_RESIDUAL) squares[idx] = q;
+          emit(idx, slot, l, s, up);
         }
         if (threadIdx.x == 0) p.counters[this_tile] = 0;  // ready for the next launch
       }
@@ -394,10 +499,19 @@ PKV_EXPORT long long pkv_gemm_small_m_workspace_bytes() {
 // array as `sumsq_in` (with `sumsq_parts` = ceil(N/16), `width` = N and `norm_eps`) and `out` as
 // its `x` scales its result rows by 1 / sqrt(sum / width + eps): together the residual add, the
 // RMS norm and the next product in two launches instead of three.
+//
+// Epilogue 4 (rotary + cache): `w` is a fused query/key/value projection of n_heads + 2 n_kv heads
+// of head_dim (a multiple of 16) columns. Queries and keys are rotated by `positions[row]` with
+// the tables cos_t, sin_t [positions][head_dim / 2] (half-split pairs; null tables: no rotation);
+// `out` [M, N] receives the queries (its key and value columns are left unwritten); keys and
+// values go to the pools [pages, n_kv, page_size, head_dim] at `slots[row]` (null or negative:
+// not stored).
 PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int epilogue,
                                 int n_out, float clip, int chained, void* workspace, long long workspace_bytes,
                                 float* hidden, const float* norm_weight, float* sumsq_out, const float* sumsq_in,
-                                int sumsq_parts, int width, float norm_eps, void* stream) {
+                                int sumsq_parts, int width, float norm_eps, const int* positions, const float* cos_t,
+                                const float* sin_t, void* k_pool, void* v_pool, const int* slots, int n_heads, int n_kv,
+                                int head_dim, int page_size, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return PKV_ERR_SIZE;
   if (K % SMALL_CHUNK != 0 || ldx % 8 != 0) return PKV_ERR_SIZE;
   if (M > pkv_gemm_small_m_max_rows(epilogue)) return PKV_ERR_LIMIT;
@@ -413,6 +527,9 @@ PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, 
   p.hidden = hidden; p.norm_weight = norm_weight; p.sumsq_out = sumsq_out;
   p.sumsq_in = sumsq_in; p.sumsq_parts = sumsq_parts; p.norm_eps = norm_eps; p.inv_width = width > 0 ? 1.0f / (float)width : 0.0f;
   if (sumsq_in && (sumsq_parts <= 0 || width <= 0)) return PKV_ERR_SIZE;
+  p.positions = positions; p.cos_t = cos_t; p.sin_t = sin_t; p.k_pool = static_cast<bf16*>(k_pool);
+  p.v_pool = static_cast<bf16*>(v_pool); p.slots = slots; p.n_heads = n_heads; p.n_kv = n_kv; p.head_dim = head_dim;
+  p.page_size = page_size;
   p.chunks = K / SMALL_CHUNK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (epilogue) {
@@ -421,6 +538,14 @@ PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, 
       p.tiles = (N + 15) / 16; p.ld_out = N; p.n_out = N;
       if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
       return epilogue == EPI_BF16 ? dispatch_small<EPI_BF16>(p, chained, s) : dispatch_small<EPI_F32>(p, chained, s);
+    case EPI_ROPE_KV:
+      if (head_dim <= 0 || head_dim % 16 != 0 || n_heads <= 0 || n_kv <= 0 || N != (n_heads + 2 * n_kv) * head_dim)
+        return PKV_ERR_SIZE;
+      if (!positions || (cos_t != nullptr) != (sin_t != nullptr) || page_size <= 0) return PKV_ERR_SIZE;
+      if (slots && (!k_pool || !v_pool)) return PKV_ERR_SIZE;
+      p.tiles = N / 16; p.ld_out = N; p.n_out = N;
+      if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
+      return dispatch_small<EPI_ROPE_KV>(p, chained, s);
     case EPI_RESIDUAL:
       if (!hidden || !norm_weight || !sumsq_out) return PKV_ERR_SIZE;
       p.tiles = (N + 15) / 16; p.ld_out = N; p.n_out = N;

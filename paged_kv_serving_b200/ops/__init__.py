@@ -451,7 +451,7 @@ def _small_m_workspace(device: torch.device) -> torch.Tensor:
 
 def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_out: int = 0, clip: float = 60.0,
                  chained: bool = True, residual: tuple[torch.Tensor, torch.Tensor] | None = None,
-                 row_norm: tuple[torch.Tensor, float] | None = None):
+                 row_norm: tuple[torch.Tensor, float] | None = None, rope_kv: tuple | None = None):
     """``a [M, K] @ b_nk [N, K]^T`` for the few rows of a decode step: the weights stream from
     memory through registers into ``mma.sync`` (bfloat16 in, float32 accumulate), every weight
     read once. Epilogues as in ``gemm_tcgen05``. ``chained`` launches the kernel as a programmatic
@@ -463,10 +463,17 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
     the sums of squares of the new stream per 16-column tile and row, ``[ceil(N / 16), 32]``.
     ``row_norm = (sumsq, eps)`` with such sums: ``a`` is taken to be such a weighted stream and the
     rows of the result are divided by ``sqrt(sum / K + eps)``. The two together are a residual add,
-    an RMS norm and the next product in two launches instead of three."""
+    an RMS norm and the next product in two launches instead of three.
+
+    ``rope_kv = (positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size)``
+    (instead of an epilogue): ``b_nk`` is a fused query/key/value projection; what
+    ``rope_kv_store`` would do to the product happens in the epilogue, and the result ``[M, N]``
+    holds the rotated queries (its key and value columns are not written)."""
     if residual is not None:
         epilogue = "residual"
-    if epilogue not in GEMM_EPILOGUES and epilogue != "residual":
+    if rope_kv is not None:
+        epilogue = "rope_kv"
+    if epilogue not in GEMM_EPILOGUES and epilogue not in ("residual", "rope_kv"):
         raise ValueError(f"unknown epilogue {epilogue!r}")
     for name, t in (("a", a), ("b_nk", b_nk)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
@@ -491,18 +498,33 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
         if sumsq_in.dim() != 2 or sumsq_in.shape[1] != 32:
             raise ValueError("sums of squares must be [parts, 32]")
         parts = sumsq_in.shape[0]
+    positions = cos = sin = k_pool = v_pool = slots = None
+    n_heads = n_kv = head_dim = page_size = 0
+    if rope_kv is not None:
+        positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size = rope_kv
+        _need(positions, torch.int32, "positions"); _need(k_pool, torch.bfloat16, "k_pool"); _need(v_pool, torch.bfloat16, "v_pool")
+        if cos is not None:
+            _need(cos, torch.float32, "cos"); _need(sin, torch.float32, "sin")
+            if cos.shape[1] != head_dim // 2:
+                raise ValueError("rotary tables must be [positions, head_dim/2]")
+        if slots is not None:
+            _need(slots, torch.int32, "slots")
+        if n != (n_heads + 2 * n_kv) * head_dim or positions.numel() < m:
+            raise ValueError("the projection's rows do not match (n_heads + 2*n_kv) * head_dim, or positions are missing")
     if epilogue == "silu_mul":
         out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
     else:
         out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
     fn = _fn("gemm_small_m", "pkv_gemm_small_m",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
-              c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+              c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     workspace = _small_m_workspace(a.device)
-    code = 3 if epilogue == "residual" else GEMM_EPILOGUES[epilogue]
+    code = {"residual": 3, "rope_kv": 4}.get(epilogue) or GEMM_EPILOGUES[epilogue]
     _check(fn(_ptr(a), _ptr(b_nk), _ptr(out), m, n, k, a.stride(0), code, int(n_out), float(clip),
               1 if chained else 0, _ptr(workspace), workspace.numel(), _ptr(hidden), _ptr(weight), _ptr(sumsq_out),
-              _ptr(sumsq_in), parts, k, float(eps), _stream()), "gemm_small_m")
+              _ptr(sumsq_in), parts, k, float(eps), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_pool), _ptr(v_pool),
+              _ptr(slots), int(n_heads), int(n_kv), int(head_dim), int(page_size), _stream()), "gemm_small_m")
     return (out, sumsq_out) if residual is not None else out
 
 

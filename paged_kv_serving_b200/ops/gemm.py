@@ -18,7 +18,8 @@ import torch
 
 from paged_kv_serving_b200 import ops
 
-__all__ = ["PendingNorm", "TCGEN05_MIN_ROWS", "as_tensor", "linear", "linear_add_norm", "linear_silu_mul", "matmul"]
+__all__ = ["PendingNorm", "TCGEN05_MIN_ROWS", "as_tensor", "linear", "linear_add_norm", "linear_rope_kv_store",
+           "linear_silu_mul", "matmul"]
 
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
@@ -117,6 +118,28 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
             and _own_kernel(x, w_nk)):
         return ops.gemm_tcgen05(x, w_nk, ops.status_word(x.device), "f32" if wants_f32 else "bf16")
     return matmul(x, w_nk.t(), out_dtype)
+
+
+def linear_rope_kv_store(x: "torch.Tensor | PendingNorm", w_nk: torch.Tensor, positions: torch.Tensor,
+                         cos: torch.Tensor | None, sin: torch.Tensor | None, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                         slots: torch.Tensor | None, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+                         after_light_kernel: bool = False) -> torch.Tensor:
+    """The fused query/key/value projection ``x @ w_nk^T`` followed by ``ops.rope_kv_store``: the
+    queries rotated in the returned ``[T, (H + 2 KV) hd]`` matrix, keys (rotated) and values in the
+    pools at ``slots``. For the few rows of a decode step one kernel does both."""
+    fused_ok = head_dim % 16 == 0 and k_pool.dtype == torch.bfloat16
+    if isinstance(x, PendingNorm):
+        if fused_ok and _small_m(x.weighted, w_nk, "bf16"):
+            return ops.gemm_small_m(x.weighted, w_nk, chained=SMALL_M_CHAINED and after_light_kernel,
+                                    row_norm=(x.sumsq, x.eps),
+                                    rope_kv=(positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size))
+        x = x.tensor()
+    if fused_ok and _small_m(x, w_nk, "bf16"):
+        return ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and after_light_kernel,
+                                rope_kv=(positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size))
+    qkv = linear(x, w_nk, after_light_kernel=after_light_kernel)
+    ops.rope_kv_store(qkv, positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size)
+    return qkv
 
 
 def linear_add_norm(x: torch.Tensor, w_nk: torch.Tensor, hidden: torch.Tensor, norm_weight: torch.Tensor, eps: float,

@@ -195,17 +195,19 @@ class PagedAttention(Part):
         group = ctx.groups[binding.group]
         k_pool = group.k_pool[binding.index]
         v_pool = group.v_pool[binding.index]
-        qkv = gemm.linear(x, self.qkv_proj, after_light_kernel=True)
         positions = ctx.ints(ctx.POSITIONS)
+        slots = ctx.ints(group.slots_name) if binding.write else None
         tables = self.position.fused_tables(ctx.device)
         if tables is None:
+            qkv = gemm.linear(x, self.qkv_proj, after_light_kernel=True)
             self.position.apply_qk(qkv, positions, self.n_heads, self.n_kv_heads, self.head_dim)
-            cos = sin = None
+            ops.rope_kv_store(qkv, positions, None, None, k_pool, v_pool, slots,
+                              self.n_heads, self.n_kv_heads, self.head_dim, group.page_size)
         else:
-            cos, sin = tables
-        slots = ctx.ints(group.slots_name) if binding.write else None
-        ops.rope_kv_store(qkv, positions, cos, sin, k_pool, v_pool, slots,
-                          self.n_heads, self.n_kv_heads, self.head_dim, group.page_size)
+            # projection, rotation and cache write: one kernel for the few rows of a decode step
+            qkv = gemm.linear_rope_kv_store(x, self.qkv_proj, positions, tables[0], tables[1], k_pool, v_pool, slots,
+                                            self.n_heads, self.n_kv_heads, self.head_dim, group.page_size,
+                                            after_light_kernel=True)
         if self._fast(ctx):
             attended = self._attend_fast(qkv, ctx, group, k_pool, v_pool)
             return project_out(attended, self.out_proj)

@@ -511,6 +511,50 @@ def test_gemm_small_m_residual_epilogue_and_row_norm(m, d, k, n):
         assert np.abs(as_np(got) - want).max() <= 2 ** -7 * np.abs(want).max() + 1e-5
 
 
+@pytest.mark.parametrize("m, h, kv, hd, k, page", [(1, 2, 1, 16, 32, 4), (5, 3, 3, 32, 96, 8), (8, 8, 2, 64, 256, 16),
+                                                    (8, 32, 8, 128, 512, 16), (20, 6, 2, 48, 160, 16)])
+def test_gemm_small_m_rotary_and_cache_epilogue(m, h, kv, hd, k, page):
+    """The fused projection whose epilogue rotates queries and keys and writes keys and values into
+    the paged pools, against the projection followed by the plain rotation; one row is not
+    stored (slot -1), and a second call without slots leaves the pools alone."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(m + h + hd)
+    n = (h + 2 * kv) * hd
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    w = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    cos, sin = plain_model.rope_tables(64, hd, 10000.0)
+    positions = rng.integers(0, 64, size=m).astype(np.int32)
+    pages = 2 * m // page + 3
+    slots = rng.permutation(pages * page)[:m].astype(np.int32)
+    if m > 1:
+        slots[1] = -1
+    k_pool = torch.zeros((pages, kv, page, hd), dtype=torch.bfloat16, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    out = ops.gemm_small_m(a, w, rope_kv=(dev(positions), dev(cos), dev(sin), k_pool, v_pool, dev(slots), h, kv, hd, page))
+    product = (a.double() @ w.double().t()).cpu().numpy().astype(np.float32)
+    q = plain_model.apply_rope(product[:, :h * hd].reshape(m, h, hd), positions, cos, sin)
+    kk = plain_model.apply_rope(product[:, h * hd:(h + kv) * hd].reshape(m, kv, hd), positions, cos, sin)
+    vv = product[:, (h + kv) * hd:].reshape(m, kv, hd)
+    bound = 2 ** -7 * np.abs(product).max()
+    assert np.abs(as_np(out)[:, :h * hd].reshape(m, h, hd) - q).max() <= bound
+    got_k, got_v = as_np(k_pool), as_np(v_pool)
+    for row in range(m):
+        if slots[row] < 0:
+            continue
+        pg, off = divmod(int(slots[row]), page)
+        assert np.abs(got_k[pg, :, off] - kk[row]).max() <= bound
+        assert np.abs(got_v[pg, :, off] - vv[row]).max() <= bound
+    written = np.zeros((pages, page), dtype=bool)
+    for sl in slots[slots >= 0]:
+        written[divmod(int(sl), page)] = True
+    untouched = ~written[:, None, :].repeat(kv, axis=1)
+    assert not got_k[untouched].any() and not got_v[untouched].any(), "only the named slots are written"
+    before = k_pool.clone()
+    again = ops.gemm_small_m(a, w, rope_kv=(dev(positions), dev(cos), dev(sin), k_pool, v_pool, None, h, kv, hd, page))
+    assert torch.equal(k_pool, before) and torch.equal(again[:, :h * hd], out[:, :h * hd])
+
+
 def test_gemm_small_m_refusals():
     from paged_kv_serving_b200 import ops
 
