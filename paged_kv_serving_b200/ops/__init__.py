@@ -224,6 +224,8 @@ def attention_bf16_rows() -> tuple[int, int]:
 
 def attention_tcgen05_supports(head_dim: int, page_size: int, q_row_stride: int) -> bool:
     """Whether the tcgen05 prefill attention takes these sizes (head 64 or 128, pages of 8k keys)."""
+    if head_dim not in (64, 128) or page_size % 8:
+        return False     # known without building the library for a model that cannot use it
     lib = library("attention_tcgen05")
     lib.pkv_attention_tcgen05_supports.restype = c_int
     lib.pkv_attention_tcgen05_supports.argtypes = [c_int, c_int, c_int]
@@ -261,6 +263,8 @@ _DECODE_TMA_BLOCKS: dict[tuple[int, bool], int] = {}
 
 def attention_decode_tma_supports(head_dim: int, page_size: int, q_row_stride: int) -> bool:
     """Whether the TMA-fed decode attention takes these sizes (head 64 or 128, pages of 8k keys)."""
+    if head_dim not in (64, 128) or page_size % 8:
+        return False     # known without building the library for a model that cannot use it
     lib = library("attention_decode_tma")
     lib.pkv_attention_decode_tma_supports.restype = c_int
     lib.pkv_attention_decode_tma_supports.argtypes = [c_int, c_int, c_int]
