@@ -95,9 +95,23 @@ __device__ __forceinline__ void trace_note(int what) {
     trace_ring[i].block = (int)blockDim.x;
   }
 }
+// the same from the first thread of every block (what >= 16), to see how far apart blocks finish
+__device__ __forceinline__ void trace_note_block(int what) {
+  if (threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned int i = atomicAdd(&trace_count, 1u) & 8191u;
+    trace_ring[i].t = t;
+    trace_ring[i].what = what;
+    trace_ring[i].grid = (int)(gridDim.x * gridDim.y * gridDim.z);
+    trace_ring[i].block = (int)blockIdx.x;
+  }
+}
 #define PKV_TRACE_NOTE(what) pkv::trace_note(what)
+#define PKV_TRACE_NOTE_BLOCK(what) pkv::trace_note_block(what)
 #else
 #define PKV_TRACE_NOTE(what)
+#define PKV_TRACE_NOTE_BLOCK(what)
 #endif
 
 __device__ __forceinline__ void dependents_may_launch() {

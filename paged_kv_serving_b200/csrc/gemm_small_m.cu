@@ -344,6 +344,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, PER_SM) gemm_small_m_kernel(
       // places that free up and request its own first weights. (Earlier would be no gain: its
       // blocks would sit beside blocks of this kernel that still wait for a place.)
       pkv::dependents_may_launch();
+      PKV_TRACE_NOTE_BLOCK(16);
     }
 
 #pragma unroll
@@ -433,6 +434,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, PER_SM) gemm_small_m_kernel(
     }
     __syncthreads();  // `red`, `is_last` and `squares` are written again in the next round
   }
+  PKV_TRACE_NOTE_BLOCK(17);
 }
 
 int sm_count() {
