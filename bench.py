@@ -212,7 +212,9 @@ def run(args) -> dict:
     torch.cuda.empty_cache()
 
     # ---- end to end through the Python entry point ----------------------------------------------
-    new_tokens = args.warmup + args.steps + 4
+    # sequences whose prompt is finished early decode while the others are still being prefilled
+    prefill_steps = -(-batch * prompt_len // 4096) + batch
+    new_tokens = args.warmup + args.steps + 4 + prefill_steps
     engine = Engine(model, EngineConfig(
         block_size=block, num_blocks=batch * (-(-(prompt_len + new_tokens) // block) + 1), max_batched_tokens=4096,
         max_running_seqs=batch, max_prompt_tokens=prompt_len, max_new_tokens=new_tokens,
