@@ -329,6 +329,61 @@ def test_toy_routed_feed_forward_registers_builds_and_steps():
     helpers.assert_close(np.concatenate(got), want, "float32", "routed feed-forward")
 
 
+def test_parts_that_know_nothing_of_fused_norms_get_plain_tensors_in_bfloat16():
+    """In bfloat16, the products of a decode step carry the residual add and leave the norm to the
+    product that reads it. A mixer defined here, which knows nothing of that, must still receive
+    an ordinary normalised tensor: the toy architecture at a width the fused kernels take, decoded
+    token by token, against its plain forward on the bfloat16-rounded weights."""
+    from paged_kv_serving_b200.config import ModelConfig, registry
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+    from paged_kv_serving_b200.ops import gemm
+
+    _register_toys()
+    c = dict(TOY, d_model=64, n_heads=4, n_kv_heads=2, d_ff=128, n_layers=4)
+    config = ModelConfig.from_dict(c)
+    specs = registry.architecture("ToyStateDecoder").layout(config).tensor_specs()
+    rng = np.random.default_rng(33)
+    tensors = {name: ((1 + 0.1 * rng.standard_normal(spec.shape)) if spec.kind == "vector"
+                      else plain_model.round_to_bfloat16(rng.standard_normal(spec.shape) * 0.12)).astype(np.float32)
+               for name, spec in specs.items()}
+
+    def plain(tokens):
+        x = tensors["embed"][np.asarray(tokens)]
+        positions = np.arange(len(tokens))
+        for i in range(c["n_layers"]):
+            p = f"blocks.{i}."
+            normed = plain_model.rms_norm(x, tensors[p + "mixer_norm.weight"], c["norm_eps"])
+            if i % 2 == 0:
+                mean = np.cumsum(normed, axis=0) / np.arange(1, len(tokens) + 1)[:, None]
+                mixed = mean.astype(np.float32) @ tensors[p + "mixer.proj"]
+            else:
+                q, k, v = plain_model.project_qkv(normed, tensors[p + "mixer.qkv_proj"], 4, 2, 16)
+                factor = (1.0 / (1.0 + positions / 64.0)).astype(np.float32)[:, None, None]
+                attended = plain_model.causal_attention(q * factor, k * factor, v, 1 / math.sqrt(16), window=16)
+                mixed = attended.reshape(len(tokens), 64) @ tensors[p + "mixer.out_proj"]
+            x = (x + mixed).astype(np.float32)
+            normed = plain_model.rms_norm(x, tensors[p + "ff_norm.weight"], c["norm_eps"])
+            x = (x + plain_model.swiglu(normed, tensors[p + "feed_forward.gate_proj"], tensors[p + "feed_forward.up_proj"],
+                                        tensors[p + "feed_forward.down_proj"])).astype(np.float32)
+        return plain_model.rms_norm(x, tensors["final.weight"], c["norm_eps"]) @ tensors["embed"].T
+
+    tokens = [int(t) for t in rng.integers(0, 97, size=40)]
+    want = plain(tokens)
+    model = DecoderModel.from_tensors(config, {k: torch.from_numpy(v) for k, v in tensors.items()}, "bfloat16", "cuda")
+    handed_on = []
+    original = gemm.PendingNorm.tensor
+    gemm.PendingNorm.tensor = lambda self: handed_on.append(1) or original(self)
+    try:
+        session = ReplaySession(model, max_tokens=64, block_size=4)
+        got = [session.step([{"id": "s", "tokens": tokens[:19], "want": [18]}])]
+        got += [session.step([{"id": "s", "tokens": [t], "want": [0]}]) for t in tokens[19:]]
+    finally:
+        gemm.PendingNorm.tensor = original
+    assert handed_on, "the decode steps of this model must have gone through the fused feed-forward"
+    helpers.assert_close(np.concatenate(got), want[18:], "bfloat16", "toy mixer behind a fused feed-forward")
+
+
 def test_layer_order_may_repeat_a_layer_and_read_another_layers_cache():
     from paged_kv_serving_b200.engine.replay import ReplaySession
 
