@@ -8,8 +8,11 @@
 // attention_generic.cu (float32) take the sizes this kernel refuses: it wants bfloat16, a head
 // size of 64 or 128 and a page size that is a multiple of 8.
 //
-// One block handles 128 queries of one sequence for one head and walks the keys in tiles of 128
-// absolute positions (aligned to multiples of 128 from position 0), with six warps:
+// One block handles 128 queries of one sequence for one head and walks the keys in tiles of KT
+// absolute positions (aligned to multiples of KT from position 0), with six warps. With KT = 64
+// (pages of up to 64 keys) a block needs half of an SM's shared memory, registers and tensor
+// memory, and two blocks share an SM: one block's softmax runs while the other's products do.
+// With KT = 128 (pages of 128 keys) one block fills the SM.
 //   warp 0     TMA: the query tile from the fused qkv buffer, then for every key tile the pages
 //              the block table names, page by page, into 128-byte-swizzled shared memory (a page
 //              that was given back, or that lies past the last key, is fetched from outside the
@@ -27,7 +30,6 @@
 namespace pkv {
 
 constexpr int FA_BM = 128;        // queries per block
-constexpr int FA_BN = 128;        // keys per tile
 constexpr int FA_THREADS = 192;
 constexpr int FA_TABLE_CACHE = 1024;
 constexpr float FA_RESCALE_STEP = 8.0f;   // log2: rescale the accumulator when the maximum grew by 2^8
@@ -52,22 +54,26 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+template <int HD, int KT>
+__global__ void __launch_bounds__(FA_THREADS, KT == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const FaParams p) {
-  constexpr int PANELS = HD / 64;                        // 64-column panels of a row of Q, K or V
-  constexpr uint32_t PANEL_BYTES = 128 * 128;            // 128 rows of 128 bytes
-  constexpr uint32_t TILE_BYTES = PANELS * PANEL_BYTES;  // a Q, K or V tile
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t S_COL = 0, O_COL = 256;
+  constexpr int FA_BN = KT;                               // keys per tile
+  constexpr int PANELS = HD / 64;                         // 64-column panels of a row of Q, K or V
+  constexpr uint32_t PANEL_BYTES = 128 * 128;             // a panel of Q or P: 128 rows of 128 bytes
+  constexpr uint32_t Q_BYTES = PANELS * PANEL_BYTES;      // the query tile
+  constexpr uint32_t KV_PANEL_BYTES = KT * 128;           // a panel of K or V: KT rows of 128 bytes
+  constexpr uint32_t TILE_BYTES = PANELS * KV_PANEL_BYTES;   // a K or V tile
+  constexpr int VSTAGES = KT == 64 ? 1 : 2;               // value tiles in flight (one, where two blocks share an SM)
+  constexpr uint32_t TMEM_COLS = KT == 64 ? 256 : 512;    // two score buffers of KT columns, then the accumulator
+  constexpr uint32_t S_COL = 0, O_COL = 2 * KT;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = base;
-  uint8_t* k_s = q_s + TILE_BYTES;           // [2][TILE_BYTES]
-  uint8_t* v_s = k_s + 2 * TILE_BYTES;       // [2][TILE_BYTES]
-  uint8_t* p_s = v_s + 2 * TILE_BYTES;       // probabilities: 128 rows x 128 keys, two panels
+  uint8_t* k_s = q_s + Q_BYTES;                  // [2][TILE_BYTES]
+  uint8_t* v_s = k_s + 2 * TILE_BYTES;           // [VSTAGES][TILE_BYTES]
+  uint8_t* p_s = v_s + VSTAGES * TILE_BYTES;     // probabilities: 128 rows x KT keys, panels of 64 keys
   __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -118,7 +124,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // Lane 0 waits for a free slot and announces the bytes; then every lane issues one box
     // (one page of one 64-column panel), so the many small copies of a tile start together.
     if (lane == 0) {
-      mbar_expect_tx(&q_full, TILE_BYTES);
+      mbar_expect_tx(&q_full, Q_BYTES);
       for (int pn = 0; pn < PANELS; ++pn)
         tma_load_2d(q_s + pn * PANEL_BYTES, &map_q, &q_full, head * HD + 64 * pn, tok0 + q0);
     }
@@ -126,41 +132,48 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int boxes = pages_per_tile * PANELS;
     bool ok = true;
     int loaded_k = 0, loaded_v = 0;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int stage = j & 1;
+    // one tile of keys (which = 0) or values (1): wait for its slot, announce the bytes, one box a lane
+    auto load_tile = [&](int which, int j) {
+      const int stage = which ? j % VSTAGES : j & 1;
+      const int round = which ? j / VSTAGES : j >> 1;
       const int tile_base = (tile_begin + j) * FA_BN;
-      for (int which = 0; which < 2 && ok; ++which) {      // 0: keys, 1: values
-        uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
-        uint64_t* full = which ? &v_full[stage] : &k_full[stage];
-        if (lane == 0) {
-          if (j >= 2 && !mbar_wait(empty, ((j >> 1) - 1) & 1, aborted)) ok = false;
-          if (ok) mbar_expect_tx(full, TILE_BYTES);
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        uint8_t* dst = (which ? v_s : k_s) + stage * TILE_BYTES;
-        for (int b = lane; b < boxes; b += 32) {
-          const int i = b / PANELS, pn = b - i * PANELS;
-          const int pos = tile_base + i * p.page_size;
-          int row = p.pool_rows;                               // outside the pool: zeros
-          if (pos < key_hi && pos + p.page_size > key_lo) {
-            const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-            const int page = table_cached ? table_cache[e - entry_first] : table[e];
-            if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
-          }
-          tma_load_2d(dst + pn * PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
-        }
-        __syncwarp();
-        if (which) loaded_v = j + 1; else loaded_k = j + 1;
+      uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
+      uint64_t* full = which ? &v_full[stage] : &k_full[stage];
+      if (lane == 0) {
+        if (round >= 1 && !mbar_wait(empty, (round - 1) & 1, aborted)) ok = false;
+        if (ok) mbar_expect_tx(full, TILE_BYTES);
       }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) return;
+      uint8_t* dst = (which ? v_s : k_s) + stage * TILE_BYTES;
+      for (int b = lane; b < boxes; b += 32) {
+        const int i = b / PANELS, pn = b - i * PANELS;
+        const int pos = tile_base + i * p.page_size;
+        int row = p.pool_rows;                               // outside the pool: zeros
+        if (pos < key_hi && pos + p.page_size > key_lo) {
+          const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+          const int page = table_cached ? table_cache[e - entry_first] : table[e];
+          if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+        }
+        tma_load_2d(dst + pn * KV_PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
+      }
+      __syncwarp();
+      if (which) loaded_v = j + 1; else loaded_k = j + 1;
+    };
+    // the keys of tile j + 1 are asked for before the values of tile j: the next scores are
+    // computed while this tile's softmax runs, the values are needed only after it
+    load_tile(0, 0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) load_tile(0, j + 1);
+      if (ok) load_tile(1, j);
     }
     if (lane == 0 && *aborted) {   // let the copies in flight land before the shared memory is given up
       const long long start = clock64();
       while (!mbar_try_wait(&q_full, 0) && clock64() - start < GM_WAIT_CYCLES) {}
       for (int j = max(0, loaded_k - 2); j < loaded_k; ++j)
         while (!mbar_try_wait(&k_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
-      for (int j = max(0, loaded_v - 2); j < loaded_v; ++j)
-        while (!mbar_try_wait(&v_full[j & 1], (j >> 1) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
+      for (int j = max(0, loaded_v - VSTAGES); j < loaded_v; ++j)
+        while (!mbar_try_wait(&v_full[j % VSTAGES], (j / VSTAGES) & 1) && clock64() - start < GM_WAIT_CYCLES) {}
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------ MMA issuer
@@ -174,9 +187,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s + stage * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * PANEL_BYTES;
-          umma_bf16(tmem_base + S_COL + stage * FA_BN, umma_desc(q_addr + off) + 2 * (ks & 3),
-                    umma_desc(k_addr + off) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
+          umma_bf16(tmem_base + S_COL + stage * FA_BN, umma_desc(q_addr + (ks >> 2) * PANEL_BYTES) + 2 * (ks & 3),
+                    umma_desc(k_addr + (ks >> 2) * KV_PANEL_BYTES) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(&k_empty[stage]);
         umma_commit(&s_full[stage]);
@@ -195,16 +207,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           tc_fence_after();
           issue_scores(j + 1);
         }
-        ok = mbar_wait(&p_full, j & 1, aborted) && mbar_wait(&v_full[j & 1], (j >> 1) & 1, aborted);
+        ok = mbar_wait(&p_full, j & 1, aborted) && mbar_wait(&v_full[j % VSTAGES], (j / VSTAGES) & 1, aborted);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t p_addr = smem_addr(p_s), v_addr = smem_addr(v_s + (j & 1) * TILE_BYTES);
+        const uint32_t p_addr = smem_addr(p_s), v_addr = smem_addr(v_s + (j % VSTAGES) * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FA_BN / 16; ++ks) {
           umma_bf16(tmem_base + O_COL, umma_desc(p_addr + (ks >> 2) * PANEL_BYTES) + 2 * (ks & 3),
-                    umma_desc_mn(v_addr + ks * 16 * 128, PANEL_BYTES, 1024), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_desc_mn(v_addr + ks * 16 * 128, KV_PANEL_BYTES, 1024), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&v_empty[j & 1]);
+        umma_commit(&v_empty[j % VSTAGES]);
         umma_commit(&pv_done);
       }
     }
@@ -304,12 +316,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       if (tile_base + FA_BN > key_hi) {
         // slots of the last page past the last key may hold anything (0 x NaN = NaN): clear them
-        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[buf], (j >> 1) & 1, aborted) ? 1 : 0) != 0;
+        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[j % VSTAGES], (j / VSTAGES) & 1, aborted) ? 1 : 0) != 0;
         if (!ok) break;
         const int r = key_hi - tile_base + (int)threadIdx.x - 64;     // threads 64..191 take one row each
         if (r < FA_BN)
           for (int pn = 0; pn < PANELS; ++pn) {
-            uint4* dst = reinterpret_cast<uint4*>(v_s + buf * TILE_BYTES + pn * PANEL_BYTES + r * 128);
+            uint4* dst = reinterpret_cast<uint4*>(v_s + (j % VSTAGES) * TILE_BYTES + pn * KV_PANEL_BYTES + r * 128);
 #pragma unroll
             for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
           }
@@ -373,17 +385,19 @@ static const CUtensorMap* pool_map(const void* base, long long rows, int hd, int
   return &slot.map;
 }
 
-template <int HD>
+template <int HD, int KT>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
                      cudaStream_t s) {
-  const size_t smem = (size_t)(HD / 64) * 128 * 128 * 5 + 2 * 128 * 128 + 1024;
+  // the query tile, two key tiles, one or two value tiles, the probabilities, and room to align
+  const size_t panels = HD / 64;
+  const size_t smem = panels * 128 * 128 + (2 + (KT == 64 ? 1 : 2)) * panels * KT * 128 + (size_t)(KT / 64) * 128 * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_tcgen05_kernel<HD><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
+  attention_tcgen05_kernel<HD, KT><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
   return launch_status();
 }
 
@@ -393,7 +407,7 @@ using namespace pkv;
 
 // 1 when this kernel takes the sizes, 0 when another attention kernel must be used.
 PKV_EXPORT int pkv_attention_tcgen05_supports(int hd, int page_size, int q_row_stride) {
-  return ((hd == 64 || hd == 128) && page_size >= 8 && page_size % 8 == 0 && FA_BN % page_size == 0 &&
+  return ((hd == 64 || hd == 128) && page_size >= 8 && page_size % 8 == 0 && 128 % page_size == 0 &&
           q_row_stride % 8 == 0) ? 1 : 0;
 }
 
@@ -423,6 +437,11 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   FaParams p{(bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size,
              shift, window, scale * 1.4426950408889634f, (int)pool_rows, status};
   cudaStream_t s = (cudaStream_t)stream;
-  if (hd == 128) return launch_fa<128>(map_q, *map_k, *map_v, p, n_work, s);
-  return launch_fa<64>(map_q, *map_k, *map_v, p, n_work, s);
+  // tiles of 64 keys (two blocks to an SM) wherever a page fits one
+  if (page_size <= 64) {
+    if (hd == 128) return launch_fa<128, 64>(map_q, *map_k, *map_v, p, n_work, s);
+    return launch_fa<64, 64>(map_q, *map_k, *map_v, p, n_work, s);
+  }
+  if (hd == 128) return launch_fa<128, 128>(map_q, *map_k, *map_v, p, n_work, s);
+  return launch_fa<64, 128>(map_q, *map_k, *map_v, p, n_work, s);
 }
