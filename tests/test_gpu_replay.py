@@ -125,6 +125,27 @@ def test_mixed_requests_with_page_reuse(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name, d_ff, vocab, n_kv", [("A", 173, 257, 2), ("B", 75, 1001, 1), ("D", 333, 515, 2)])
+def test_odd_feed_forward_and_vocabulary_sizes(name, d_ff, vocab, n_kv, dtype):
+    """Inner sizes and vocabularies that are odd numbers (no multiple of 8, so no 16-byte rows):
+    a prompt, a portion of two tokens and decoding, against the plain implementation."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    config = dict(helpers.CONFIGS[name], d_ff=d_ff, vocab_size=vocab, n_kv_heads=n_kv)
+    tensors = plain_model.random_tensors(config, seed=3, std=0.06)
+    if dtype == "bfloat16":
+        tensors = {k: (plain_model.round_to_bfloat16(v) if v.ndim == 2 else v) for k, v in tensors.items()}
+    model = helpers.build_model(config, tensors, dtype)
+    tokens = helpers.random_tokens(config, 70, seed=5)
+    want = plain_model.forward(config, tensors, np.asarray(tokens))
+    session = ReplaySession(model, max_tokens=128, block_size=helpers.PAGE_SIZE[name])
+    got = [session.step([{"id": "a", "tokens": tokens[:37], "want": list(range(37))}])]
+    got.append(session.step([{"id": "a", "tokens": tokens[37:39], "want": [0, 1]}]))
+    got += [session.step([{"id": "a", "tokens": [t], "want": [0]}]) for t in tokens[39:]]
+    helpers.assert_close(np.concatenate(got), want, dtype, f"odd sizes {name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_and_single_token_prompt(dtype):
     session, tensors = _session("B", dtype, 256)
     tokens = helpers.random_tokens(helpers.TINY_B, 5, seed=14)
