@@ -40,7 +40,12 @@ class PreNormBlock(Part):
         return self.mixer.cache_request()
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
-        for child in self.sub_parts().values():
+        # only the children that plan anything (this runs for every layer of every step)
+        planners = self.__dict__.get("_planners")
+        if planners is None:
+            planners = self._planners = [child for child in self.sub_parts().values()
+                                         if type(child).plan_step is not Part.plan_step]
+        for child in planners:
             child.plan_step(ctx, binding)
 
     @property

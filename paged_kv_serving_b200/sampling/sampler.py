@@ -24,6 +24,7 @@ class Sampler:
     def __init__(self, device: torch.device | str = "cuda") -> None:
         self.device = torch.device(device)
         self._probs: torch.Tensor | None = None
+        self._greedy: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams],
                generators: list[np.random.Generator]) -> list[int]:
@@ -31,18 +32,27 @@ class Sampler:
         rows, vocab = logits.shape
         if rows != len(params) or rows != len(generators):
             raise ValueError("one SamplingParams and one generator per logits row are required")
-        host = np.zeros((rows, 4), dtype=np.float64)
-        for i, (p, rng) in enumerate(zip(params, generators)):
-            host[i, 0] = p.temperature
-            host[i, 1] = p.top_p
-            host[i, 2] = 0.0 if p.greedy else float(rng.random())
-        staged = torch.from_numpy(host)
-        if torch.cuda.is_available():
-            staged = staged.pin_memory()
-        dev = staged.to(self.device, non_blocking=True)
-        temperature = dev[:, 0].to(torch.float32).contiguous()
-        top_p = dev[:, 1].to(torch.float32).contiguous()
-        uniform = dev[:, 2].contiguous()
+        if all(p.greedy for p in params):
+            # nothing to send: no draw is made for a greedy row (cached zeros and ones per row count)
+            cached = self._greedy.get(rows)
+            if cached is None:
+                cached = self._greedy[rows] = (torch.zeros(rows, dtype=torch.float32, device=self.device),
+                                               torch.ones(rows, dtype=torch.float32, device=self.device),
+                                               torch.zeros(rows, dtype=torch.float64, device=self.device))
+            temperature, top_p, uniform = cached
+        else:
+            # one pinned buffer, one copy: [rows] float64 draws, then [rows] float32 temperatures and top-p
+            staged = torch.empty((rows * 16,), dtype=torch.uint8, pin_memory=torch.cuda.is_available())
+            draws = staged[:rows * 8].view(torch.float64).numpy()
+            floats = staged[rows * 8:].view(torch.float32).numpy()
+            for i, (p, rng) in enumerate(zip(params, generators)):
+                floats[i] = p.temperature
+                floats[rows + i] = p.top_p
+                draws[i] = 0.0 if p.greedy else float(rng.random())
+            dev = staged.to(self.device, non_blocking=True)
+            uniform = dev[:rows * 8].view(torch.float64)
+            temperature = dev[rows * 8:rows * 12].view(torch.float32)
+            top_p = dev[rows * 12:].view(torch.float32)
         if self._probs is None or self._probs.numel() < rows * vocab:
             self._probs = torch.empty((rows * vocab,), dtype=torch.float32, device=self.device)
         ids = ops.sample(logits, temperature, top_p, uniform, GREEDY_TEMPERATURE, self._probs)
