@@ -265,7 +265,7 @@ class ModelRunner:
         if not want_logits:
             return None
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
-        return gemm.linear(normed, model.head, out_dtype=torch.float32, after_light_kernel=True)
+        return gemm.linear(normed, model.head, out_dtype=torch.float32, chain=True)
 
     def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None) -> StepResult:
         """Run one batch: writes the cache for every token given, returns logits where wanted.

@@ -43,8 +43,8 @@ PLAIN_PRODUCT_KERNEL = "library"
 #: behind (it re-reads the activations for every 16 weight rows). The LM head (float32 result, one
 #: long stream per step) stays with cuBLAS, which reaches the memory's copy rate there.
 SMALL_M_ROWS = 8
-#: Whether that kernel is launched as a programmatic dependent where the caller says that the
-#: kernel before it is a light one (``after_light_kernel``).
+#: Whether that kernel is launched as a programmatic dependent where the caller asks for it
+#: (``chain=True``).
 SMALL_M_CHAINED = True
 
 
@@ -98,21 +98,22 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 
 def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = None,
-           after_light_kernel: bool = False) -> torch.Tensor:
+           chain: bool = False) -> torch.Tensor:
     """``x [T, K] @ w_nk [N, K]^T``; ``out_dtype`` float32 keeps the float32 accumulator.
 
-    ``after_light_kernel``: the kernel before this product on the stream leaves most SMs idle (a
-    norm over a few rows), so the weight-streaming kernel may start beside it and request its first
-    weights early. After a kernel that fills the GPU (attention, another product) an early start
-    only spreads its blocks unevenly, and it is launched the ordinary way."""
+    ``chain``: launch the decode kernel as a programmatic dependent of the kernel before it on the
+    stream, so that it requests its first weights while that kernel ends. Measured inside a decode
+    step: this pays after a norm and after another product of this module (which lets its
+    dependents start only when its own reads are done); after the attention kernels it costs 50 us
+    a launch (the blocks land unevenly on the SMs), so a mixer's output projection is not chained."""
     wants_f32 = out_dtype == torch.float32
     if isinstance(x, PendingNorm):
         if not wants_f32 and _small_m(x.weighted, w_nk, "bf16"):
-            return ops.gemm_small_m(x.weighted, w_nk, "bf16", chained=SMALL_M_CHAINED and after_light_kernel,
+            return ops.gemm_small_m(x.weighted, w_nk, "bf16", chained=SMALL_M_CHAINED and chain,
                                     row_norm=(x.sumsq, x.eps))
         x = x.tensor()
     if not wants_f32 and _small_m(x, w_nk, "bf16"):
-        return ops.gemm_small_m(x, w_nk, "bf16", chained=SMALL_M_CHAINED and after_light_kernel)
+        return ops.gemm_small_m(x, w_nk, "bf16", chained=SMALL_M_CHAINED and chain)
     # rows of the output must start on 16-byte boundaries for the kernel's vector stores
     if (PLAIN_PRODUCT_KERNEL == "tcgen05" and w_nk.shape[0] % (4 if wants_f32 else 8) == 0
             and _own_kernel(x, w_nk)):
@@ -123,27 +124,27 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
 def linear_rope_kv_store(x: "torch.Tensor | PendingNorm", w_nk: torch.Tensor, positions: torch.Tensor,
                          cos: torch.Tensor | None, sin: torch.Tensor | None, k_pool: torch.Tensor, v_pool: torch.Tensor,
                          slots: torch.Tensor | None, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                         after_light_kernel: bool = False) -> torch.Tensor:
+                         chain: bool = False) -> torch.Tensor:
     """The fused query/key/value projection ``x @ w_nk^T`` followed by ``ops.rope_kv_store``: the
     queries rotated in the returned ``[T, (H + 2 KV) hd]`` matrix, keys (rotated) and values in the
     pools at ``slots``. For the few rows of a decode step one kernel does both."""
     fused_ok = head_dim % 16 == 0 and k_pool.dtype == torch.bfloat16
     if isinstance(x, PendingNorm):
         if fused_ok and _small_m(x.weighted, w_nk, "bf16"):
-            return ops.gemm_small_m(x.weighted, w_nk, chained=SMALL_M_CHAINED and after_light_kernel,
+            return ops.gemm_small_m(x.weighted, w_nk, chained=SMALL_M_CHAINED and chain,
                                     row_norm=(x.sumsq, x.eps),
                                     rope_kv=(positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size))
         x = x.tensor()
     if fused_ok and _small_m(x, w_nk, "bf16"):
-        return ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and after_light_kernel,
+        return ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and chain,
                                 rope_kv=(positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size))
-    qkv = linear(x, w_nk, after_light_kernel=after_light_kernel)
+    qkv = linear(x, w_nk, chain=chain)
     ops.rope_kv_store(qkv, positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size)
     return qkv
 
 
 def linear_add_norm(x: torch.Tensor, w_nk: torch.Tensor, hidden: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                    out_dtype: torch.dtype, after_light_kernel: bool = False) -> "torch.Tensor | PendingNorm":
+                    out_dtype: torch.dtype, chain: bool = False) -> "torch.Tensor | PendingNorm":
     """``hidden += x @ w_nk^T`` (the float32 stream, in place) and the RMS-normalised stream in
     ``out_dtype``. For the few rows of a decode step the weight-streaming kernel adds the product
     to the stream in its epilogue and leaves the norm as a ``PendingNorm`` for the product that
@@ -151,24 +152,24 @@ def linear_add_norm(x: torch.Tensor, w_nk: torch.Tensor, hidden: torch.Tensor, n
     x = as_tensor(x)
     if out_dtype == torch.bfloat16 and w_nk.shape[0] % 32 == 0 and _small_m(x, w_nk, "bf16"):
         # the width of the stream is the inner size of the product that reads it: a multiple of 32
-        weighted, sumsq = ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and after_light_kernel,
+        weighted, sumsq = ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and chain,
                                            residual=(hidden, norm_weight))
         return PendingNorm(weighted, sumsq, eps)
-    return ops.add_rmsnorm(hidden, linear(x, w_nk, after_light_kernel=after_light_kernel), norm_weight, eps, out_dtype)
+    return ops.add_rmsnorm(hidden, linear(x, w_nk, chain=chain), norm_weight, eps, out_dtype)
 
 
 def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleave: int, clip: float,
-                    after_light_kernel: bool = False) -> torch.Tensor:
+                    chain: bool = False) -> torch.Tensor:
     """``silu(x @ gate^T) * (x @ up^T)`` for gate and up rows held in one matrix (``interleave``
     as in ``ops.silu_mul``); ``[T, ff]``."""
     if isinstance(x, PendingNorm):
         if interleave == 128 and _small_m(x.weighted, w_gate_up, "silu_mul"):
             return ops.gemm_small_m(x.weighted, w_gate_up, "silu_mul", n_out=ff, clip=clip,
-                                    chained=SMALL_M_CHAINED and after_light_kernel, row_norm=(x.sumsq, x.eps))
+                                    chained=SMALL_M_CHAINED and chain, row_norm=(x.sumsq, x.eps))
         x = x.tensor()
     if interleave == 128 and _small_m(x, w_gate_up, "silu_mul"):
         return ops.gemm_small_m(x, w_gate_up, "silu_mul", n_out=ff, clip=clip,
-                                chained=SMALL_M_CHAINED and after_light_kernel)
+                                chained=SMALL_M_CHAINED and chain)
     if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and _own_kernel(x, w_gate_up):
         # one SM per tile: with this many tiles the two-SM kernel's split of the last wave costs
         # more than it saves

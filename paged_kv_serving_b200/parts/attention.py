@@ -199,7 +199,7 @@ class PagedAttention(Part):
         slots = ctx.ints(group.slots_name) if binding.write else None
         tables = self.position.fused_tables(ctx.device)
         if tables is None:
-            qkv = gemm.linear(x, self.qkv_proj, after_light_kernel=True)
+            qkv = gemm.linear(x, self.qkv_proj, chain=True)
             self.position.apply_qk(qkv, positions, self.n_heads, self.n_kv_heads, self.head_dim)
             ops.rope_kv_store(qkv, positions, None, None, k_pool, v_pool, slots,
                               self.n_heads, self.n_kv_heads, self.head_dim, group.page_size)
@@ -207,7 +207,7 @@ class PagedAttention(Part):
             # projection, rotation and cache write: one kernel for the few rows of a decode step
             qkv = gemm.linear_rope_kv_store(x, self.qkv_proj, positions, tables[0], tables[1], k_pool, v_pool, slots,
                                             self.n_heads, self.n_kv_heads, self.head_dim, group.page_size,
-                                            after_light_kernel=True)
+                                            chain=True)
         if self._fast(ctx):
             attended = self._attend_fast(qkv, ctx, group, k_pool, v_pool)
             return project_out(attended, self.out_proj)

@@ -76,6 +76,8 @@ class PreNormBlock(Part):
             normed = gemm.as_tensor(normed)
         follow = getattr(next_norm, "add_norm_of_linear", None)
         if self.feed_forward.fuses_last_linear and follow is not None:
-            values = self.feed_forward.forward(normed, ctx, finish=lambda x, w: follow(hidden, x, w, ctx.dtype))
+            # the feed-forward's last product follows its first one: chained (see ops.gemm.linear)
+            values = self.feed_forward.forward(
+                normed, ctx, finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=True))
             return Normed(values, next_norm)
         return self.feed_forward.forward(normed, ctx)

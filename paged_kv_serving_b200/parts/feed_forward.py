@@ -68,7 +68,7 @@ class SwiGLU(Part):
     accepts_pending_norm = True
 
     def forward(self, x: torch.Tensor, ctx: StepContext, finish=None) -> torch.Tensor:
-        gated = gemm.linear_silu_mul(x, self.gate_up, self.inner, self.interleave, self.clip, after_light_kernel=True)
+        gated = gemm.linear_silu_mul(x, self.gate_up, self.inner, self.interleave, self.clip, chain=True)
         if finish is not None:
             return finish(gated, self.down_proj)
-        return gemm.linear(gated, self.down_proj)
+        return gemm.linear(gated, self.down_proj, chain=True)

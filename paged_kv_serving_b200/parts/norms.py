@@ -36,7 +36,8 @@ class RMSNorm(Part):
         return ops.add_rmsnorm(hidden, delta, self.weight, self.eps, out_dtype, rows)
 
     def add_norm_of_linear(self, hidden: torch.Tensor, x: torch.Tensor, w_nk: torch.Tensor,
-                           out_dtype: torch.dtype) -> torch.Tensor:
-        """``add_norm(hidden, x @ w_nk^T)`` for a producer whose last step is that product: one
-        launch where the product's kernel can carry the add and the norm in its tail."""
-        return gemm.linear_add_norm(x, w_nk, hidden, self.weight, self.eps, out_dtype)
+                           out_dtype: torch.dtype, chain: bool = False) -> torch.Tensor:
+        """``add_norm(hidden, x @ w_nk^T)`` for a producer whose last step is that product: the
+        product's kernel carries the residual add, and the norm is left to the product that reads
+        the result, where the kernels can do that. ``chain`` as in ``ops.gemm.linear``."""
+        return gemm.linear_add_norm(x, w_nk, hidden, self.weight, self.eps, out_dtype, chain=chain)
