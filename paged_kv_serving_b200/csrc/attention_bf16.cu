@@ -433,7 +433,6 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     __syncthreads();
   }
 
-  dependents_may_launch();   // after the keys are read: see the note in attention_decode_tma.cu
   // ---- merge the four warps (each saw a quarter of the keys) ----
   cp_async_wait<0>();   // a split without tiles still has the copy of its queries in flight
   __syncthreads();
@@ -528,6 +527,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     }
     cluster.sync();     // the others keep their shared memory until block 0 has read it
   }
+  dependents_may_launch();   // at the very end: see the note in attention_decode_tma.cu
 }
 
 // merge of the splits: one warp per (token, head) output row named by the work list

@@ -264,11 +264,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   }
 
-  // This block has read its keys and values. Once every block has, the next kernel may take the
-  // places that free up (earlier, its blocks would crowd onto the SMs this kernel leaves idle and
-  // start its work unevenly spread).
-  dependents_may_launch();
-
   // ---- merge the four consumer warps (each saw a quarter of the keys) ----
   __syncthreads();           // every copy that was waited for has landed; the ring is free
   float* o_s = reinterpret_cast<float*>(ring);                       // [4][DT_ROWS][HD]
@@ -357,6 +352,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
     cluster.sync();
   }
+  // Only now may the next kernel start: launched while blocks of this kernel were still merging,
+  // the product that follows ran 50 us longer; launched here, it gains its launch time.
+  dependents_may_launch();
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 2);
 }
 

@@ -191,7 +191,7 @@ class PagedAttention(Part):
     accepts_pending_norm = True
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, finish=None) -> torch.Tensor:
-        project_out = finish if finish is not None else gemm.linear
+        project_out = finish if finish is not None else (lambda a, w: gemm.linear(a, w, chain=True))
         group = ctx.groups[binding.group]
         k_pool = group.k_pool[binding.index]
         v_pool = group.v_pool[binding.index]

@@ -69,7 +69,8 @@ class PreNormBlock(Part):
             normed = self.mixer_norm.add_norm(hidden, pending, ctx.dtype)
         follow = getattr(self.ff_norm, "add_norm_of_linear", None)
         if self.mixer.fuses_last_linear and follow is not None:
-            normed = self.mixer.forward(normed, ctx, binding, finish=lambda x, w: follow(hidden, x, w, ctx.dtype))
+            normed = self.mixer.forward(normed, ctx, binding,
+                                        finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=True))
         else:
             normed = self.ff_norm.add_norm(hidden, self.mixer.forward(normed, ctx, binding), ctx.dtype)
         if not self.feed_forward.accepts_pending_norm:
