@@ -8,13 +8,17 @@
 //
 // A decode step reads each cached key and value once and does little arithmetic on it, so the
 // kernel is built around keeping many bytes in flight per SM. One block per (split of the key
-// range, key/value head, entry): a producer warp walks the block table and issues one TMA box per
+// range, key/value head, entry): two producer warps walk the block table and issue one TMA box per
 // page and 64-column panel into a ring of up to six 64-key stages (128-byte swizzle, completion on
 // mbarriers); four consumer warps each take 16 keys of every stage with mma.sync (the at most 16
 // (query token, head in group) rows of the entry form one MMA row tile), keep their own running
-// (maximum, sum, accumulator) and hand the stage back. Warps are merged through shared memory,
-// the splits of one entry through the shared memory of their thread-block cluster.
+// (maximum, sum, accumulator) and hand the stage back. Warps are merged through shared memory;
+// the splits of one entry are the blocks of a thread-block cluster, and the first block merges
+// them: the others push their states into its shared memory and leave (or, when the states do
+// not fit there, it fetches them out of theirs).
 // Every mbarrier wait is bounded; a give-up sets status code 2 and the block leaves in order.
+// Build switches for comparisons: -DDT_PRODUCERS=1 (one producer warp), -DDT_NO_PUSH (always
+// fetch the other splits' states).
 #include <cooperative_groups.h>
 
 #include "tcgen05.cuh"
@@ -25,7 +29,10 @@ namespace pkv {
 
 constexpr int DT_BN = 64;          // keys per stage
 constexpr int DT_ROWS = 16;        // rows of an entry per key/value head
-constexpr int DT_THREADS = 160;    // four consumer warps and one producer warp
+#ifndef DT_PRODUCERS
+#define DT_PRODUCERS 2
+#endif
+constexpr int DT_THREADS = 128 + 32 * DT_PRODUCERS;    // four consumer warps and the producer warps
 constexpr int DT_TABLE_CACHE = 512;
 
 struct DecTmaParams {
@@ -62,6 +69,20 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Pushing a split's state into the first block of its cluster: a store into that block's shared
+// memory which counts its bytes on that block's mbarrier when it has landed.
+__device__ __forceinline__ uint32_t in_first_block(uint32_t local_addr) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local_addr));
+  return remote;
+}
+__device__ __forceinline__ void push_f32(uint32_t remote, float v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+               ::"r"(remote), "f"(v), "r"(remote_bar) : "memory");
+}
+
+constexpr int DT_LANDING_FLOATS = 2640;   // in the first block, for the other splits' states (six splits of four rows of 128)
+
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -79,6 +100,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ float part_m[DT_ROWS], part_l[DT_ROWS];
   __shared__ int32_t table_cache[DT_TABLE_CACHE];
   __shared__ int abort_flag;
+  __shared__ __align__(16) float landing[DT_LANDING_FLOATS];
+  __shared__ __align__(8) uint64_t landing_bar;
 
   const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_seq[blockIdx.z];
   const int group = p.n_heads / p.n_kv;
@@ -99,12 +122,28 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int32_t* table = p.block_table + (size_t)s * p.table_stride;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
     abort_flag = 0;
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&full_bar[i], 1);
+      mbar_init(&full_bar[i], DT_PRODUCERS);   // every producer warp announces its own bytes
       mbar_init(&empty_bar[i], 4);          // one arrival per consumer warp
     }
+    mbar_init(&landing_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // The splits of an entry are the blocks of one cluster. When their states fit, the other
+  // blocks push them into the first block's `landing` (rows x HD sums, then the rows' maxima and
+  // weights) and leave; the first block has announced the bytes and waits for them. Otherwise it
+  // fetches the states out of the others' shared memory between two cluster barriers.
+  const int slot_floats = rows_valid * (HD + 2);
+#ifdef DT_NO_PUSH
+  const bool push = false;
+#else
+  const bool push = p.num_splits > 1 && (p.num_splits - 1) * slot_floats <= DT_LANDING_FLOATS;
+#endif
+  if (push) {
+    if (split == 0 && threadIdx.x == 0) mbar_expect_tx(&landing_bar, (uint32_t)((p.num_splits - 1) * slot_floats * 4));
   }
   const int entry_first = n_tiles ? (p.page_shift >= 0 ? (tile_begin * DT_BN) >> p.page_shift : (tile_begin * DT_BN) / p.page_size) : 0;
   const int entry_last = n_tiles ? (p.page_shift >= 0 ? (min(key_hi, (tile_end + 1) * DT_BN) - 1) >> p.page_shift
@@ -113,6 +152,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (table_cached)
     for (int i = threadIdx.x; i <= entry_last - entry_first; i += DT_THREADS) table_cache[i] = table[entry_first + i];
   __syncthreads();
+  // the first block's barrier is ready before anyone pushes: arrive here, wait before pushing
+  if (push) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   // Up to here only the step's index arrays were read, which the host wrote before the step's
   // first kernel. The queries and the newest keys and values come from the kernel before this one.
   wait_for_prior_kernels();
@@ -123,35 +164,44 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
   for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------------ producer
+  if (warp >= 4) {
+    // ------------------------------------------------------------------------ producers
+    // Issuing the boxes of a tile takes a warp about a microsecond at 16 boxes, more than the
+    // consumers need for the tile: the producer warps share the boxes.
+    const int pw = warp - 4;
     const int pages_per_tile = DT_BN / p.page_size;
     const int boxes = pages_per_tile * PANELS * 2;      // keys and values
+    const int my_boxes = (boxes - pw + DT_PRODUCERS - 1) / DT_PRODUCERS;
+    const uint32_t my_bytes = (uint32_t)my_boxes * p.page_size * 128;
+    // at most 32 boxes a tile (pages of 8 keys, two panels, keys and values): one box a lane,
+    // and what does not change from tile to tile is worked out once
+    const int b = pw + lane * DT_PRODUCERS;
+    const bool has_box = b < boxes;
+    const int which = b / (pages_per_tile * PANELS);              // 0: keys, 1: values
+    const int rest = b - which * pages_per_tile * PANELS;
+    const int page_in_tile = rest / PANELS, pn = rest - page_in_tile * PANELS;
+    const int key_in_tile = page_in_tile * p.page_size;
+    const uint32_t dst_offset = which * HALF_BYTES + pn * PANEL_BYTES + key_in_tile * 128;
+    const CUtensorMap* map = which ? &map_v : &map_k;
     bool ok = true;
     int issued = 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int stage = j % STAGES;
       if (lane == 0) {
         if (j >= STAGES && !mbar_wait(&empty_bar[stage], ((j / STAGES) - 1) & 1, aborted)) ok = false;
-        if (ok) mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+        if (ok) mbar_expect_tx(&full_bar[stage], my_bytes);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      const int tile_base = (tile_begin + j) * DT_BN;
-      uint8_t* dst = ring + (size_t)stage * STAGE_BYTES;
-      for (int b = lane; b < boxes; b += 32) {
-        const int which = b / (pages_per_tile * PANELS);          // 0: keys, 1: values
-        const int rest = b - which * pages_per_tile * PANELS;
-        const int i = rest / PANELS, pn = rest - i * PANELS;
-        const int pos = tile_base + i * p.page_size;
+      if (has_box) {
+        const int pos = (tile_begin + j) * DT_BN + key_in_tile;
         int row = p.pool_rows;                                     // outside the pool: zeros
         if (pos < key_hi && pos + p.page_size > key_lo) {
           const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
           if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
         }
-        tma_load_2d(dst + which * HALF_BYTES + pn * PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k,
-                    &full_bar[stage], 64 * pn, row);
+        tma_load_2d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 64 * pn, row);
       }
       __syncwarp();
       issued = j + 1;
@@ -284,6 +334,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   }
   __syncthreads();
+  if (push) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // passed long ago
+  const uint32_t landing_bar_remote = in_first_block(smem_addr(&landing_bar));
   const size_t out_stride = (size_t)p.n_heads * HD;
   for (int idx = threadIdx.x; idx < rows_valid * HD; idx += DT_THREADS) {
     const int row = idx / HD, d = idx - row * HD;
@@ -300,6 +352,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (p.num_splits == 1) {
       const int q_local = row / group, head = kvh * group + row % group;
       p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(l > 0.0f ? acc / l : 0.0f);
+    } else if (push && split > 0) {
+      const uint32_t slot = smem_addr(landing) + (uint32_t)((split - 1) * slot_floats) * 4u;
+      push_f32(in_first_block(slot + (uint32_t)(row * HD + d) * 4u), acc, landing_bar_remote);
+      if (d == 0) {
+        push_f32(in_first_block(slot + (uint32_t)(rows_valid * HD + 2 * row) * 4u), m, landing_bar_remote);
+        push_f32(in_first_block(slot + (uint32_t)(rows_valid * HD + 2 * row + 1) * 4u), l, landing_bar_remote);
+      }
     } else {
       part_o[row * HD + d] = acc;
       if (d == 0) {
@@ -308,14 +367,57 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
     }
   }
-  if (p.num_splits > 1) {
+  __shared__ float weight[8][DT_ROWS];    // per row, the weight of every split's sums: exp2(m_r - M) / L
+  if (push && split == 0) {
+    __syncthreads();                                   // this block's own state is in part_o, part_m, part_l
+    bool landed = mbar_wait(&landing_bar, 0, aborted);  // the others' states have landed
+    if (!landed) {
+      // given up elsewhere in this block: the others still push, and this block's shared memory
+      // must outlive their stores
+      const long long start = clock64();
+      while (!mbar_try_wait(&landing_bar, 0) && clock64() - start < GM_WAIT_CYCLES) {}
+    }
+    if (landed) {
+      if (threadIdx.x < rows_valid) {
+        const int row = threadIdx.x;
+        float mr[8], lr[8];
+        mr[0] = part_m[row]; lr[0] = part_l[row];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) {
+          const float* ml = landing + (r - 1) * slot_floats + rows_valid * HD + 2 * row;
+          mr[r] = r < p.num_splits ? ml[0] : -INFINITY;
+          lr[r] = r < p.num_splits ? ml[1] : 0.0f;
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) m = fmaxf(m, mr[r]);
+        float l = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          mr[r] = mr[r] > -INFINITY ? exp2f(mr[r] - m) : 0.0f;
+          l += lr[r] * mr[r];
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) weight[r][row] = mr[r] * inv;
+      }
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < rows_valid * HD; idx += DT_THREADS) {
+        const int row = idx / HD, d = idx - row * HD;
+        float acc = part_o[row * HD + d] * weight[0][row];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+          if (r < p.num_splits) acc += landing[(r - 1) * slot_floats + row * HD + d] * weight[r][row];
+        const int q_local = row / group, head = kvh * group + row % group;
+        p.out[(size_t)(tok0 + q_local) * out_stride + (size_t)head * HD + d] = from_float<bf16>(acc);
+      }
+    }
+  } else if (p.num_splits > 1 && !push) {
     // the splits of this (entry, kv head) are the blocks of one cluster: block 0 folds the others'
     // states out of their shared memory
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
     if (split == 0) {
-      // per row: the weight of every split's accumulator, exp2(m_r - M) / L, computed once
-      __shared__ float weight[8][DT_ROWS];
       if (threadIdx.x < rows_valid) {
         const int row = threadIdx.x;
         float mr[8], lr[8];
@@ -410,6 +512,12 @@ template <int HD, int STAGES> static int dec_blocks_per_sm() {
   cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_tma_kernel<HD, STAGES>, DT_THREADS, smem);
   return blocks;
+}
+
+// Most splits whose states the first block of a cluster can take in its shared memory (the
+// faster way to merge them) for entries of `rows` (query token, head in group) rows.
+PKV_EXPORT int pkv_attention_decode_tma_pushed_splits(int hd, int rows) {
+  return rows > 0 ? 1 + DT_LANDING_FLOATS / (rows * (hd + 2)) : 1;
 }
 
 PKV_EXPORT int pkv_attention_decode_tma_blocks_per_sm(int hd, int deep_ring) {

@@ -95,7 +95,8 @@ __device__ __forceinline__ void trace_note(int what) {
     trace_ring[i].block = (int)blockDim.x;
   }
 }
-// the same from the first thread of every block (what >= 16), to see how far apart blocks finish
+// the same from the first thread of every block (what >= 16; with -DPKV_TRACE_BLOCKS as well), to
+// see how far apart blocks finish
 __device__ __forceinline__ void trace_note_block(int what) {
   if (threadIdx.x == 0) {
     unsigned long long t;
@@ -108,7 +109,11 @@ __device__ __forceinline__ void trace_note_block(int what) {
   }
 }
 #define PKV_TRACE_NOTE(what) pkv::trace_note(what)
+#ifdef PKV_TRACE_BLOCKS
 #define PKV_TRACE_NOTE_BLOCK(what) pkv::trace_note_block(what)
+#else
+#define PKV_TRACE_NOTE_BLOCK(what)
+#endif
 #else
 #define PKV_TRACE_NOTE(what)
 #define PKV_TRACE_NOTE_BLOCK(what)

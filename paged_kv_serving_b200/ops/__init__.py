@@ -17,7 +17,7 @@ from paged_kv_serving_b200.ops.build import build_all, library, library_names
 __all__ = [
     "add_rmsnorm", "attention_bf16_rows", "attention_bf16_supports", "attention_decode_bf16",
     "attention_decode_blocks_per_sm", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
-    "attention_decode_tma_supports",
+    "attention_decode_tma_pushed_splits", "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
     "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
     "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
@@ -280,6 +280,15 @@ def attention_decode_tma_blocks_per_sm(head_dim: int, deep_ring: bool) -> int:
         lib.pkv_attention_decode_tma_blocks_per_sm.argtypes = [c_int, c_int]
         _DECODE_TMA_BLOCKS[key] = max(1, int(lib.pkv_attention_decode_tma_blocks_per_sm(int(head_dim), int(deep_ring))))
     return _DECODE_TMA_BLOCKS[key]
+
+
+def attention_decode_tma_pushed_splits(head_dim: int, rows: int) -> int:
+    """Most splits that the TMA decode kernel merges the fast way (the other blocks of a cluster
+    push their states into the first one) for entries of ``rows`` (token, head in group) rows."""
+    lib = library("attention_decode_tma")
+    lib.pkv_attention_decode_tma_pushed_splits.restype = c_int
+    lib.pkv_attention_decode_tma_pushed_splits.argtypes = [c_int, c_int]
+    return int(lib.pkv_attention_decode_tma_pushed_splits(int(head_dim), int(rows)))
 
 
 def attention_decode_tma(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

@@ -103,10 +103,11 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
 
     ``chain``: launch the decode kernel as a programmatic dependent of the kernel before it on the
     stream, so that it requests its first weights while that kernel ends. Measured inside a decode
-    step: this pays after a norm, after another product of this module (which lets its dependents
-    start when its own reads are done) and after the decode attention kernels (which let theirs
-    start only at their very end: started while they still merged their splits, the product that
-    follows ran 50 us longer)."""
+    step: this pays after a norm and after another product of this module (which lets its
+    dependents start when its own reads are done). It must not follow a kernel that needs most of
+    an SM's memory as shared memory (the attention kernels): an SM changes its division between
+    L1 and shared memory only when idle, and a product whose blocks arrive beside such a kernel's
+    keeps the small L1 and streams at half speed, and so do the products chained after it."""
     wants_f32 = out_dtype == torch.float32
     if isinstance(x, PendingNorm):
         if not wants_f32 and _small_m(x.weighted, w_nk, "bf16"):

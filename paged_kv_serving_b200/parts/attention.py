@@ -99,6 +99,13 @@ class PagedAttention(Part):
 
     #: Set to False to keep runs of queries on the mma.sync kernel (tests compare the two).
     USE_TCGEN05 = True
+    #: The attention kernels need nearly all of an SM's memory as shared memory; the decode
+    #: products stream their weights through L1. An SM changes the division only when it is idle:
+    #: blocks of a product that arrive while attention blocks are still resident keep the small
+    #: L1, run at half speed, and hand the division on to the products chained after them (the
+    #: gate/up product then took 92 us instead of 46, at random). So the output projection starts
+    #: only after the attention kernel has left the SMs.
+    chains_last_linear = False
 
     def _tcgen05(self, page_size: int) -> bool:
         """Whether runs of queries go to the tcgen05 kernel (head 64 or 128, pages of 8k keys)."""
@@ -156,11 +163,19 @@ class PagedAttention(Part):
                 # the three-stage ring (two blocks per SM) measured at least as fast as the six-stage
                 # one (one block per SM) at every batch size and context length tried
                 deep_ring = False
-                per_sm = ops.attention_decode_tma_blocks_per_sm(self.head_dim, deep_ring)
+                # (more than two blocks of a cluster per SM measured slower than fewer splits)
+                per_sm = min(2, ops.attention_decode_tma_blocks_per_sm(self.head_dim, deep_ring))
             else:
                 per_sm = ops.attention_decode_blocks_per_sm(self.head_dim)
             resident = per_sm * _sm_count(ctx.device)
             num_splits = int(max(1, min(tiles, 8, resident // blocks_per_split)))
+            if self._decode_tma(page_size) and num_splits > 4:
+                # up to a number of splits the kernel merges them the fast way; a few splits less
+                # cost less than the slow merge
+                rows = int(lens[decode_entries].max()) * self.group_size
+                pushed = ops.attention_decode_tma_pushed_splits(self.head_dim, rows)
+                if 4 <= pushed < num_splits:
+                    num_splits = pushed
         names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq")}
         ctx.arena.add(names["prefill_seq"], work_seq[order] if len(order) else [0])
         ctx.arena.add(names["prefill_q0"], work_q0[order] if len(order) else [0])
@@ -191,7 +206,7 @@ class PagedAttention(Part):
     accepts_pending_norm = True
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, finish=None) -> torch.Tensor:
-        project_out = finish if finish is not None else (lambda a, w: gemm.linear(a, w, chain=True))
+        project_out = finish if finish is not None else (lambda a, w: gemm.linear(a, w, chain=self.chains_last_linear))
         group = ctx.groups[binding.group]
         k_pool = group.k_pool[binding.index]
         v_pool = group.v_pool[binding.index]

@@ -83,6 +83,11 @@ class Part:
     #: one kernel can do both. ``forward`` then returns what ``finish`` returned.
     fuses_last_linear = False
 
+    #: Whether that last product may be launched as a programmatic dependent of the part's kernel
+    #: before it (see ``ops.gemm.linear``). False where that kernel leaves the SMs divided between
+    #: L1 cache and shared memory in a way that slows the product down.
+    chains_last_linear = True
+
     #: True for a mixer or feed-forward that hands its input straight to ``ops.gemm.linear`` or
     #: ``linear_silu_mul`` and so can take an ``ops.gemm.PendingNorm`` in place of a tensor.
     accepts_pending_norm = False

@@ -69,16 +69,17 @@ class PreNormBlock(Part):
             normed = self.mixer_norm.add_norm(hidden, pending, ctx.dtype)
         follow = getattr(self.ff_norm, "add_norm_of_linear", None)
         if self.mixer.fuses_last_linear and follow is not None:
+            chain = self.mixer.chains_last_linear
             normed = self.mixer.forward(normed, ctx, binding,
-                                        finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=True))
+                                        finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=chain))
         else:
             normed = self.ff_norm.add_norm(hidden, self.mixer.forward(normed, ctx, binding), ctx.dtype)
         if not self.feed_forward.accepts_pending_norm:
             normed = gemm.as_tensor(normed)
         follow = getattr(next_norm, "add_norm_of_linear", None)
         if self.feed_forward.fuses_last_linear and follow is not None:
-            # the feed-forward's last product follows its first one: chained (see ops.gemm.linear)
+            chain = self.feed_forward.chains_last_linear
             values = self.feed_forward.forward(
-                normed, ctx, finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=True))
+                normed, ctx, finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=chain))
             return Normed(values, next_norm)
         return self.feed_forward.forward(normed, ctx)
