@@ -21,14 +21,12 @@
 // fetch the other splits' states).
 #include <cooperative_groups.h>
 
-#include "tcgen05.cuh"
+#include "attention_decode_common.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace pkv {
 
-constexpr int DT_BN = 64;          // keys per stage
-constexpr int DT_ROWS = 16;        // rows of an entry per key/value head
 #ifndef DT_PRODUCERS
 #define DT_PRODUCERS 2
 #endif
@@ -49,25 +47,8 @@ struct DecTmaParams {
   int num_splits;
   int pool_rows;
   int* status;
+  int landing_floats;           // room behind the ring for the states the other splits push (0: they are fetched)
 };
-
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // Pushing a split's state into the first block of its cluster: a store into that block's shared
 // memory which counts its bytes on that block's mbarrier when it has landed.
@@ -100,8 +81,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ float part_m[DT_ROWS], part_l[DT_ROWS];
   __shared__ int32_t table_cache[DT_TABLE_CACHE];
   __shared__ int abort_flag;
-  __shared__ __align__(16) float landing[DT_LANDING_FLOATS];
   __shared__ __align__(8) uint64_t landing_bar;
+  float* landing = reinterpret_cast<float*>(ring + (size_t)STAGES * STAGE_BYTES);   // p.landing_floats, behind the ring
 
   const int split = blockIdx.x, kvh = blockIdx.y, s = p.work_seq[blockIdx.z];
   const int group = p.n_heads / p.n_kv;
@@ -140,7 +121,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #ifdef DT_NO_PUSH
   const bool push = false;
 #else
-  const bool push = p.num_splits > 1 && (p.num_splits - 1) * slot_floats <= DT_LANDING_FLOATS;
+  const bool push = p.num_splits > 1 && (p.num_splits - 1) * slot_floats <= p.landing_floats;
 #endif
   if (push) {
     if (split == 0 && threadIdx.x == 0) mbar_expect_tx(&landing_bar, (uint32_t)((p.num_splits - 1) * slot_floats * 4));
@@ -159,10 +140,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   wait_for_prior_kernels();
   volatile int* aborted = &abort_flag;
 
-  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
-  float o[DTILES][4];
-#pragma unroll
-  for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  DecodeState<HD> st;
+  st.reset();
+  float (&o)[DTILES][4] = st.o;
+  float &m_a = st.m_a, &m_b = st.m_b, &l_a = st.l_a, &l_b = st.l_b;
 
   if (warp >= 4) {
     // ------------------------------------------------------------------------ producers
@@ -236,79 +217,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int stage = j % STAGES;
       ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (j / STAGES) & 1, aborted) ? 1 : 0) != 0;
       if (!ok) break;
-      const uint32_t k_base = smem_addr(ring + (size_t)stage * STAGE_BYTES);
-      const uint32_t v_base = k_base + HALF_BYTES;
       const int wbase = (tile_begin + j) * DT_BN + warp * 16;
-      if (wbase < key_hi && wbase + 15 >= key_lo) {
-        if (wbase + 16 > key_hi) {
-          // slots of the last page past the last key may hold anything (0 x NaN = NaN): clear the
-          // value rows this warp will read
-          for (int idx = lane; idx < 16 * PANELS * 8; idx += 32) {
-            const int r = idx / (PANELS * 8), c = idx - r * (PANELS * 8);
-            if (wbase + r >= key_hi)
-              *reinterpret_cast<uint4*>(ring + (size_t)stage * STAGE_BYTES + HALF_BYTES + (c >> 3) * PANEL_BYTES +
-                                        (warp * 16 + r) * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-          }
-          __syncwarp();
-        }
-        float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
-#pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-          // keys as the B operand: rows are keys, 16-byte chunks swizzled by the row number
-          const int krow = warp * 16 + (lane & 7) + 8 * (lane >> 4);
-          const int chunk = kk * 2 + ((lane >> 3) & 1);
-          uint32_t b[4];
-          ldsm_x4(b, k_base + (chunk >> 3) * PANEL_BYTES + krow * 128 + (((chunk & 7) ^ (krow & 7)) << 4));
-          mma16816(sc[0], qa[kk], b[0], b[1]);
-          mma16816(sc[1], qa[kk], b[2], b[3]);
-        }
-        float tmax_a = -INFINITY, tmax_b = -INFINITY;
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int kpos = wbase + jj * 8 + 2 * t4 + (e & 1);
-            const int qpos = (e < 2) ? qpos_a : qpos_b;
-            const bool visible = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
-            const float v = visible ? sc[jj][e] * p.scale_log2 : -INFINITY;
-            sc[jj][e] = v;
-            if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
-          }
-        }
-        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
-        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
-        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
-        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
-        const float new_a = fmaxf(m_a, tmax_a), new_b = fmaxf(m_b, tmax_b);
-        const float shift_a = new_a == -INFINITY ? 0.0f : new_a, shift_b = new_b == -INFINITY ? 0.0f : new_b;
-        const float resc_a = exp2f(m_a - shift_a), resc_b = exp2f(m_b - shift_b);
-        m_a = new_a; m_b = new_b;
-        float sum_a = 0.0f, sum_b = 0.0f;
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          sc[jj][0] = exp2f(sc[jj][0] - shift_a); sc[jj][1] = exp2f(sc[jj][1] - shift_a);
-          sc[jj][2] = exp2f(sc[jj][2] - shift_b); sc[jj][3] = exp2f(sc[jj][3] - shift_b);
-          sum_a += sc[jj][0] + sc[jj][1];
-          sum_b += sc[jj][2] + sc[jj][3];
-        }
-        l_a = l_a * resc_a + sum_a;
-        l_b = l_b * resc_b + sum_b;
-        uint32_t a[4];
-        a[0] = pack2(sc[0][0], sc[0][1]); a[1] = pack2(sc[0][2], sc[0][3]);
-        a[2] = pack2(sc[1][0], sc[1][1]); a[3] = pack2(sc[1][2], sc[1][3]);
-#pragma unroll
-        for (int dd = 0; dd < DTILES / 2; ++dd) {
-          // values as the B operand (transposed load): rows are keys, columns dims
-          const int vrow = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-          const int chunk = dd * 2 + (lane >> 4);
-          uint32_t b[4];
-          ldsm_x4_trans(b, v_base + (chunk >> 3) * PANEL_BYTES + vrow * 128 + (((chunk & 7) ^ (vrow & 7)) << 4));
-          o[2 * dd][0] *= resc_a; o[2 * dd][1] *= resc_a; o[2 * dd][2] *= resc_b; o[2 * dd][3] *= resc_b;
-          o[2 * dd + 1][0] *= resc_a; o[2 * dd + 1][1] *= resc_a; o[2 * dd + 1][2] *= resc_b; o[2 * dd + 1][3] *= resc_b;
-          mma16816(o[2 * dd], a, b[0], b[1]);
-          mma16816(o[2 * dd + 1], a, b[2], b[3]);
-        }
-      }
+      decode_tile<HD>(ring + (size_t)stage * STAGE_BYTES, warp, lane, qa, st, wbase, key_lo, key_hi, qpos_a, qpos_b,
+                      p.window, p.scale_log2);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
     }
@@ -460,37 +371,23 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 2);
 }
 
-struct DecMapKey {
-  const void* base;
-  long long rows;
-  int hd, box;
-  CUtensorMap map;
-};
-
-static const CUtensorMap* dec_pool_map(const void* base, long long rows, int hd, int box_rows) {
-  static DecMapKey cache[512];
-  static int used = 0;
-  for (int i = 0; i < used; ++i)
-    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) return &cache[i].map;
-  DecMapKey& slot = cache[used < 512 ? used : 511];
-  if (make_tile_map(&slot.map, base, rows, hd, hd, box_rows)) return nullptr;
-  slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows;
-  if (used < 512) ++used;
-  return &slot.map;
-}
-
 template <int HD, int STAGES>
 static size_t dec_smem() { return (size_t)STAGES * 2 * (HD / 64) * DT_BN * 128 + 1024; }
 
 template <int HD, int STAGES>
 static int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecTmaParams& p, int n_work, cudaStream_t s) {
-  const size_t smem = dec_smem<HD, STAGES>();
+  const size_t most = dec_smem<HD, STAGES>() + DT_LANDING_FLOATS * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+    if (e != cudaSuccess) return (int)e;
+    // two blocks per SM need nearly all of its memory as shared memory; left to itself the
+    // driver may choose a division in which only one fits
+    e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  const size_t smem = dec_smem<HD, STAGES>() + (size_t)p.landing_floats * sizeof(float);
   return launch_kernel(attention_decode_tma_kernel<HD, STAGES>, dim3(p.num_splits, p.n_kv, n_work), dim3(DT_THREADS), smem, s,
                        true, p.num_splits, mk, mv, p);
 }
@@ -508,8 +405,9 @@ PKV_EXPORT int pkv_attention_decode_tma_supports(int hd, int page_size, int q_ro
 // Blocks of this kernel that fit on one SM (the host sizes the number of splits with it).
 template <int HD, int STAGES> static int dec_blocks_per_sm() {
   int blocks = 0;
-  const size_t smem = dec_smem<HD, STAGES>();
-  cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = dec_smem<HD, STAGES>();      // without room for pushed states (one split needs none)
+  cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       (int)(smem + DT_LANDING_FLOATS * sizeof(float)));
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_tma_kernel<HD, STAGES>, DT_THREADS, smem);
   return blocks;
 }
@@ -540,14 +438,17 @@ PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void*
   const long long pool_rows = n_pages * n_kv * page_size;
   if (pool_rows >= (1LL << 31) - page_size) return PKV_ERR_LIMIT;
   if ((uintptr_t)qkv % 4 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16) return PKV_ERR_ALIGN;
-  const CUtensorMap* map_k = dec_pool_map(k_pool, pool_rows, hd, page_size);
-  const CUtensorMap* map_v = dec_pool_map(v_pool, pool_rows, hd, page_size);
+  const CUtensorMap* map_k = decode_pool_map(k_pool, pool_rows, hd, page_size);
+  const CUtensorMap* map_v = decode_pool_map(v_pool, pool_rows, hd, page_size);
   if (!map_k || !map_v) return PKV_ERR_SIZE;
   int shift = -1;
   for (int i = 0; i < 31; ++i)
     if ((1 << i) == page_size) shift = i;
   DecTmaParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq,
-                 n_heads, n_kv, page_size, shift, window, scale * 1.4426950408889634f, num_splits, (int)pool_rows, status};
+                 n_heads, n_kv, page_size, shift, window, scale * 1.4426950408889634f, num_splits, (int)pool_rows, status, 0};
+  // room for the pushed states of the largest entry, when that fits beside two blocks per SM
+  const int most_floats = (num_splits - 1) * max_entry_tokens * (n_heads / n_kv) * (hd + 2);
+  if (num_splits > 1 && most_floats <= DT_LANDING_FLOATS) p.landing_floats = (most_floats + 3) / 4 * 4;
   cudaStream_t s = (cudaStream_t)stream;
   // deep ring: one block per SM with six stages in flight (few blocks, long key ranges);
   // shallow ring: three stages, two blocks per SM, so that one block's start and merge hide

@@ -16,7 +16,8 @@ from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
     "add_rmsnorm", "attention_bf16_rows", "attention_bf16_supports", "attention_decode_bf16",
-    "attention_decode_blocks_per_sm", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
+    "attention_decode_blocks_per_sm", "attention_decode_flat", "attention_decode_flat_blocks_per_sm",
+    "attention_decode_flat_supports", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
     "attention_decode_tma_pushed_splits", "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
     "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
@@ -311,6 +312,73 @@ def attention_decode_tma(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
               block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), work_seq.numel(),
               int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(num_splits),
               int(bool(deep_ring)), _ptr(status), _stream()), "attention_decode_tma")
+
+
+_DECODE_FLAT_BLOCKS: dict[int, int] = {}
+_DECODE_FLAT_SCRATCH: dict[str, list[tuple[torch.Tensor, torch.Tensor]]] = {}
+
+
+def attention_decode_flat_supports(head_dim: int, page_size: int, q_row_stride: int) -> bool:
+    """Whether the even-shares decode kernel takes these sizes (answered without building it)."""
+    return attention_decode_tma_supports(head_dim, page_size, q_row_stride)
+
+
+def attention_decode_flat_blocks_per_sm(head_dim: int) -> int:
+    """Blocks of the even-shares decode kernel that one SM holds."""
+    if head_dim not in _DECODE_FLAT_BLOCKS:
+        lib = library("attention_decode_flat")
+        lib.pkv_attention_decode_flat_blocks_per_sm.restype = c_int
+        lib.pkv_attention_decode_flat_blocks_per_sm.argtypes = [c_int]
+        _DECODE_FLAT_BLOCKS[head_dim] = max(1, int(lib.pkv_attention_decode_flat_blocks_per_sm(int(head_dim))))
+    return _DECODE_FLAT_BLOCKS[head_dim]
+
+
+def _decode_flat_scratch(device: torch.device, floats: int, pairs: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Workspace and arrival counters of ``attention_decode_flat`` on a device. Counters are zeroed
+    once and left zero by every launch. A buffer that has become too small is replaced but kept
+    alive, since captured graphs may still point at it."""
+    key = str(torch.device(device))
+    kept = _DECODE_FLAT_SCRATCH.setdefault(key, [])
+    if not kept or kept[-1][0].numel() < floats or kept[-1][1].numel() < pairs:
+        kept.append((torch.empty((max(floats, 1 << 21),), dtype=torch.float32, device=device),
+                     torch.zeros((max(pairs, 1 << 18),), dtype=torch.int32, device=device)))
+    return kept[-1]
+
+
+def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                          block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
+                          work_seq: torch.Tensor, unit_starts: torch.Tensor, max_entry_tokens: int, n_heads: int,
+                          n_kv: int, head_dim: int, page_size: int, window: int, scale: float, blocks: int,
+                          status: torch.Tensor) -> None:
+    """Decode attention over even shares of the step's keys: the 64-key tiles of all entries in
+    ``work_seq`` and all kv heads, laid end to end, are cut into ``blocks`` equal ranges, one per
+    block; parts of one (entry, head) are added up by the block that finishes last.
+    ``unit_starts [entries + 1]``: the number of tiles of the entries before each entry, a tile
+    being 64 key positions counted from position 0 (entry i has tiles ``key_lo // 64`` to
+    ``(key_hi - 1) // 64`` with ``key_hi`` its context length after this step and ``key_lo`` the
+    first position inside the window of its first query). Writes the rows of its entries into ``out``."""
+    for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("unit_starts", unit_starts), ("status", status)):
+        _need(t, torch.int32, name)
+    n_work = work_seq.numel()
+    if unit_starts.numel() != n_work + 1:
+        raise ValueError("unit_starts needs one more element than there are entries")
+    lib = library("attention_decode_flat")
+    lib.pkv_attention_decode_flat_workspace_floats.restype = c_longlong
+    lib.pkv_attention_decode_flat_workspace_floats.argtypes = [c_int, c_int]
+    floats = int(lib.pkv_attention_decode_flat_workspace_floats(int(head_dim), int(blocks)))
+    workspace, counters = _decode_flat_scratch(qkv.device, floats, n_work * n_kv)
+    fn = _fn("attention_decode_flat", "pkv_attention_decode_flat",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p,
+              c_longlong, c_void_p, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
+              block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(unit_starts), n_work,
+              int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(blocks),
+              _ptr(workspace), workspace.numel(), _ptr(counters), counters.numel(), _ptr(status), _stream()),
+           "attention_decode_flat")
 
 
 _DECODE_BLOCKS: dict[int, int] = {}

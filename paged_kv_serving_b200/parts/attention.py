@@ -99,6 +99,15 @@ class PagedAttention(Part):
 
     #: Set to False to keep runs of queries on the mma.sync kernel (tests compare the two).
     USE_TCGEN05 = True
+    #: When decode entries go to the kernel that cuts the step's keys into even shares
+    #: (``ops.attention_decode_flat``) rather than to one block per (entry, head, split):
+    #: "auto" where measurement says so, "always" (where it takes the sizes) or "never".
+    #: The even shares cost about 4 us more per launch (parts meet in global memory, all blocks
+    #: start and end together), so they pay only when the other kernel's last round of blocks
+    #: would be nearly empty: 320 (entry, head) pairs on 296 places, 34 against 37 us at 1,100
+    #: keys and 83 against 112 us at 4,096; not at 512 pairs on 296 places (59 against 52 us).
+    FLAT_DECODE = "auto"
+    FLAT_DECODE_IDLE_SHARE = 0.4
     #: The attention kernels need nearly all of an SM's memory as shared memory; the decode
     #: products stream their weights through L1. An SM changes the division only when it is idle:
     #: blocks of a product that arrive while attention blocks are still resident keep the small
@@ -124,6 +133,14 @@ class PagedAttention(Part):
             qkv_width = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
             self._tcgen05_ok[key] = self.USE_TCGEN05 and ops.attention_decode_tma_supports(self.head_dim, page_size, qkv_width)
         return self._tcgen05_ok[key]
+
+    def _flat_pays(self, entries: int, device: torch.device) -> bool:
+        if self.FLAT_DECODE != "auto":
+            return self.FLAT_DECODE == "always"
+        places = 2 * _sm_count(device)
+        pairs = entries * self.n_kv_heads
+        rounds = pairs / places
+        return pairs > places and 1.0 - rounds / math.ceil(rounds) > self.FLAT_DECODE_IDLE_SHARE
 
     def _fast_key(self, page_size: int) -> str:
         return f"attention/fast/g{self.group_size}/{'t' if self._tcgen05(page_size) else 'm'}"
@@ -176,14 +193,29 @@ class PagedAttention(Part):
                 pushed = ops.attention_decode_tma_pushed_splits(self.head_dim, rows)
                 if 4 <= pushed < num_splits:
                     num_splits = pushed
-        names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq")}
+        names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq", "decode_units")}
         ctx.arena.add(names["prefill_seq"], work_seq[order] if len(order) else [0])
         ctx.arena.add(names["prefill_q0"], work_q0[order] if len(order) else [0])
         ctx.arena.add(names["decode_seq"], decode_entries if len(decode_entries) else [0])
+        flat_blocks = 0
+        if len(decode_entries) and self._decode_tma(page_size) and self._flat_pays(len(decode_entries), ctx.device):
+            # the even-shares kernel: 64-key tiles of every entry, as many blocks as the GPU holds
+            # at once (a captured graph keeps its grid: sized for the planning length)
+            key_hi = first[decode_entries] + lens[decode_entries]
+            key_lo = np.maximum(0, first[decode_entries] - self.window + 1) if self.window else np.zeros_like(key_hi)
+            tiles = (key_hi - 1) // 64 - key_lo // 64 + 1
+            ctx.arena.add(names["decode_units"], np.concatenate([[0], np.cumsum(tiles)]))
+            planned = int(tiles.sum())
+            if ctx.planning_context_len is not None:
+                planned = len(decode_entries) * -(-ctx.planning_context_len // 64)
+            per_sm = min(2, ops.attention_decode_flat_blocks_per_sm(self.head_dim))
+            flat_blocks = int(max(1, min(per_sm * _sm_count(ctx.device), planned * self.n_kv_heads)))
+        else:
+            ctx.arena.add(names["decode_units"], [0])
         ctx.scratch[key] = {
             "names": names, "n_prefill": int(len(order)), "n_decode": int(len(decode_entries)),
             "max_small_tokens": int(lens[decode_entries].max()) if len(decode_entries) else 0,
-            "num_splits": num_splits, "deep_ring": deep_ring,
+            "num_splits": num_splits, "deep_ring": deep_ring, "flat_blocks": flat_blocks,
         }
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
@@ -247,7 +279,12 @@ class PagedAttention(Part):
             ops.attention_prefill_bf16(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["prefill_seq"]),
                                        ctx.ints(names["prefill_q0"]), self.n_heads, self.n_kv_heads, self.head_dim,
                                        group.page_size, self.window or 0, self.scale)
-        if plan["n_decode"] and self._decode_tma(group.page_size):
+        if plan["n_decode"] and plan["flat_blocks"]:
+            ops.attention_decode_flat(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["decode_seq"]),
+                                      ctx.ints(names["decode_units"]), plan["max_small_tokens"], self.n_heads,
+                                      self.n_kv_heads, self.head_dim, group.page_size, self.window or 0, self.scale,
+                                      plan["flat_blocks"], ops.status_word(qkv.device))
+        elif plan["n_decode"] and self._decode_tma(group.page_size):
             ops.attention_decode_tma(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["decode_seq"]),
                                      plan["max_small_tokens"], self.n_heads, self.n_kv_heads, self.head_dim,
                                      group.page_size, self.window or 0, self.scale, plan["num_splits"],

@@ -147,7 +147,7 @@ def test_rope_kv_store(dtype, heads, kv, hd):
 
 
 def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True, fast=False, splits=1,
-                    tcgen05=False, deep_ring=True):
+                    tcgen05=False, deep_ring=True, flat_blocks=None):
     """Random sequences already in the cache (``contexts`` tokens each), of which the last
     ``queries`` tokens are this step's queries. Returns device inputs and the plain answer."""
     from paged_kv_serving_b200 import ops
@@ -211,7 +211,18 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
                                        dev(np.asarray([s for s, _ in large], dtype=np.int32)),
                                        dev(np.asarray([q for _, q in large], dtype=np.int32)),
                                        heads, kv, hd, page, window or 0, 1.0 / math.sqrt(hd))
-        if small and tcgen05 and ops.attention_decode_tma_supports(hd, page, qkv.shape[1]):
+        if small and flat_blocks:
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            hi = np.asarray([contexts[s] for s in small])
+            lo = np.asarray([max(0, contexts[s] - queries[s] - window + 1) if window else 0 for s in small])
+            units = np.concatenate([[0], np.cumsum((hi - 1) // 64 - lo // 64 + 1)])
+            for _ in range(2):      # twice: the arrival counters must be back at zero
+                out[:] = float("nan")
+                ops.attention_decode_flat(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
+                                          dev(units.astype(np.int32)), max(queries[s] for s in small), heads, kv, hd,
+                                          page, window or 0, 1.0 / math.sqrt(hd), flat_blocks, status)
+            assert int(status.item()) == 0
+        elif small and tcgen05 and ops.attention_decode_tma_supports(hd, page, qkv.shape[1]):
             status = torch.zeros(1, dtype=torch.int32, device="cuda")
             ops.attention_decode_tma(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
                                      max(queries[s] for s in small), heads, kv, hd, page, window or 0,
@@ -308,6 +319,35 @@ def test_attention_decode_tma(heads, kv, hd, page, splits, deep_ring):
     got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
                                 contexts=[300, 1, 65, 1500, 128, 64, 513, 1000], queries=[1, 1, few, 1, min(few, 2), 1, 1, few],
                                 dtype="bfloat16", fast=True, splits=splits, tcgen05=True, deep_ring=deep_ring)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("blocks", [1, 3, 7, 40, 296, 5000])
+@pytest.mark.parametrize("heads, kv, hd, page", [(32, 8, 128, 16), (8, 8, 128, 64), (12, 4, 64, 8), (16, 1, 64, 32)])
+def test_attention_decode_flat(heads, kv, hd, page, blocks):
+    """The even-shares decode kernel alone, with ranges that begin and end inside an (entry,
+    head) pair, cover several pairs, or are empty: contexts from 1 to 1500 keys, partial last
+    pages filled with NaN, a far key that dominates; run twice on the same counters."""
+    from paged_kv_serving_b200 import ops
+
+    assert ops.attention_decode_flat_supports(hd, page, (heads + 2 * kv) * hd)
+    group = heads // kv
+    few = max(1, 16 // group)
+    rng = np.random.default_rng(hd + page + blocks)
+    got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
+                                contexts=[300, 1, 65, 1500, 128, 64, 513, 1000], queries=[1, 1, few, 1, min(few, 2), 1, 1, few],
+                                dtype="bfloat16", fast=True, flat_blocks=blocks)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
+@pytest.mark.parametrize("window", [1, 63, 64, 65, 300])
+def test_attention_decode_flat_window_edges(window):
+    rng = np.random.default_rng(window)
+    got, want = _attention_case(rng, heads=4, kv=2, hd=64, page=8, window=window,
+                                contexts=[400, 128, 31, 640, 65], queries=[1, 2, 1, 8, 1],
+                                dtype="bfloat16", fast=True, flat_blocks=5)
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 

@@ -193,3 +193,31 @@ def test_captured_decode_steps_equal_eager_ones(dtype):
     want = plain_model.forward(helpers.TINY_C, tensors, prompts[1])
     helpers.assert_close(outputs[0][-1:], want[74:75], dtype, "graph decode against plain")
     assert np.abs(outputs[0] - outputs[1]).max() <= (1e-5 if dtype == "float32" else helpers.bf16_atol(outputs[1]))
+
+
+@pytest.mark.parametrize("use_graphs", [True, False])
+def test_even_shares_decode_attention_in_the_engine(monkeypatch, use_graphs):
+    """Decode steps of config D in bfloat16 with the even-shares decode kernel forced: three
+    requests of unequal length, so that a block's range ends inside one request and begins in
+    the next; against the plain implementation."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+    from paged_kv_serving_b200.parts.attention import PagedAttention
+
+    monkeypatch.setattr(PagedAttention, "FLAT_DECODE", "always")
+    tensors = helpers.tensors_for("D", "bfloat16")
+    model = helpers.build_model(helpers.TINY_D, tensors, "bfloat16")
+    prompts = [helpers.random_tokens(helpers.TINY_D, n, seed=90 + n) for n in (330, 140, 70)]
+    session = ReplaySession(model, max_tokens=1024, block_size=16)
+    session.runner.use_graphs = use_graphs
+    session.runner.storage.fill(float("nan"))
+    for i, p in enumerate(prompts):
+        session.step([{"id": f"s{i}", "tokens": p[:len(p) - 40], "want": []}])
+    got = {i: [] for i in range(len(prompts))}
+    for k in range(40, 0, -1):
+        entries = [{"id": f"s{i}", "tokens": [p[len(p) - k]], "want": [0]} for i, p in enumerate(prompts)]
+        logits = session.step(entries)
+        for i in range(len(prompts)):
+            got[i].append(logits[i])
+    for i, p in enumerate(prompts):
+        want = plain_model.forward(helpers.TINY_D, tensors, p)
+        helpers.assert_close(np.stack(got[i]), want[len(p) - 40:], "bfloat16", f"even shares, request {i}")
