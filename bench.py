@@ -7,9 +7,12 @@ baseline list) with random bfloat16 weights: 8 sequences, each with a 1,024-toke
 in the cache, decode one token per step. A "step" is one decode step of the whole batch. One JSON
 line is printed with
 
-* ``value``      decoded tokens a second, timed on the device with CUDA events over K steps
+* ``value``      decoded tokens a second, timed on the device with CUDA events over K steps;
+                 each step runs the model and samples, the ids stay on the device and the host
+                 prepares step k + 1 while the GPU runs step k (synchronised before and after the K steps)
 * ``e2e``        the same through the Python entry point (``Engine.step``): host token ids in,
-                 sampled ids out, with the host-to-device and device-to-host bytes of a step
+                 sampled ids read back every step, with the host-to-device and device-to-host
+                 bytes of a step
 * ``prefill``    one 2,048-token prompt in one step: tokens a second, milliseconds and the
                  fraction of the bfloat16 matrix peak its flops reach
 * ``roofline``   the bytes a decode step must read (every weight once, the cache of the live
@@ -185,7 +188,10 @@ def run(args) -> dict:
             entries = tuple(BatchEntry(f"s{i}", (int(prompts[i, position]),), position, (tables[i],), (0,))
                             for i in range(num_seqs))
             result = runner.step(ExecutionBatch(entries))
-            sampler.sample(result.logits, [greedy] * num_seqs, [None] * num_seqs)
+            # sampled on the device and left there: between the synchronisations around the timed
+            # steps the host prepares step k + 1 while the GPU runs step k (the end-to-end number
+            # below reads every step's tokens back)
+            sampler.sample_on_device(result.logits, [greedy] * num_seqs, [None] * num_seqs)
         for k in range(warmup):
             one(k)
         before = ops.launch_count()
@@ -251,6 +257,7 @@ def run(args) -> dict:
             "d_ff": config.d_ff, "vocab_size": config.vocab_size, "global_batch": batch, "seq_len": prompt_len,
             "kv_block_size": block, "prefill_tokens": args.prefill_tokens, "parallelism": "single-gpu",
             "l2": "weights read each step (GBs) exceed L2; no flush", "peaks": peaks["source"],
+            "value_timing": "K steps back to back between two synchronisations; e2e reads tokens back every step",
         },
         "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
         "clocks": clocks.summary(),

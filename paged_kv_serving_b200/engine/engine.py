@@ -358,7 +358,10 @@ class Engine:
                 logits = device_logits.index_select(0, torch.tensor(index, device=device_logits.device))
             self.h2d_bytes_last_step += 32 * len(samplers)
             self.d2h_bytes_last_step = 4 * len(samplers)
-            return self.sampler.sample(logits, params, generators)
+            ids = self.sampler.sample_on_device(logits, params, generators)
+            # the GPU is busy with this step: the host gets the arrays of the next one ready
+            self.runner.prepare_next()
+            return [int(t) for t in ids.cpu().tolist()]
         # rows of a stand-in executor (tests without a GPU): the caller's sampler, else the argmax
         if self.host_sampler is not None:
             return [int(self.host_sampler(np.asarray(host_rows[row]), p, g))

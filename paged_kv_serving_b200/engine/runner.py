@@ -141,6 +141,8 @@ class ModelRunner:
         self.use_graphs = use_graphs
         self._graph_safe = all(block.graph_safe for block in model.layout.blocks) and model.layout.final_norm.graph_safe
         self._graphs: dict[tuple[int, int], dict] = {}
+        self._last_graph_step: tuple[ExecutionBatch, tuple[int, int]] | None = None
+        self._ahead: dict | None = None
         self._graph_pool = torch.cuda.graph_pool_handle() if use_graphs else None
 
     # --- storage behind the cache manager -------------------------------------------------
@@ -278,6 +280,7 @@ class ModelRunner:
             return StepResult(None, [], 0, 0)
         self._validate(batch)
         self.steps_run += 1
+        self._last_graph_step = None
         if self.use_graphs and self._graph_safe and not clear_state_slots and \
                 all(e.num_tokens == 1 and e.logits_at == (0,) for e in batch.entries):
             return self._step_graph(batch)
@@ -301,14 +304,22 @@ class ModelRunner:
             size = -(-count // 256) * 256
         widest = max(len(t) for e in batch.entries for t in e.block_tables) if self.groups else 1
         width = -(-widest // self.GRAPH_TABLE_STEP) * self.GRAPH_TABLE_STEP
-        ctx, rows = self._context(batch, table_width=width, pad_to=size)
-        ctx.planning_context_len = width * self.block_size
-        self._plan(ctx)
-        rows = rows[:count]
         key = (size, width)
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None and ahead["key"] == key and self._as_expected(batch, ahead["batch"]):
+            # prepared while the GPU ran the step before: only the token ids were not known then
+            ctx, rows = ahead["ctx"], ahead["rows"]
+            tokens = [e.token_ids[0] for e in batch.entries] + [0] * (size - count)
+            ctx.arena.patch(StepContext.TOKEN_IDS, tokens)
+        else:
+            ctx, rows = self._context(batch, table_width=width, pad_to=size)
+            ctx.planning_context_len = width * self.block_size
+            self._plan(ctx)
+        self._last_graph_step = (batch, key)
+        rows = rows[:count]
         entry = self._graphs.get(key)
         if entry is not None and entry["signature"] == ctx.arena.signature():
-            ctx.arena.upload(self.model.device, into=entry["ints"])
+            ctx.arena.upload(self.model.device, into=entry["ints"], views=False)
             entry["graph"].replay()
             ops.LAUNCHES["count"] += entry["launches"]     # the kernels of this module that the graph holds
             return StepResult(entry["logits"][:count], rows, count, ctx.arena.bytes_uploaded)
@@ -328,6 +339,44 @@ class ModelRunner:
         self._graphs[key] = {"graph": graph, "ints": ints, "logits": captured, "signature": ctx.arena.signature(),
                              "launches": launches}
         return StepResult(logits[:count], rows, count, ctx.arena.bytes_uploaded)
+
+    def prepare_next(self) -> None:
+        """Call after a step was launched and before its results are waited for: if that step
+        was a captured decode step, the integer arrays of the step that most likely follows (the
+        same requests, each one position on, the same pages) are built and packed now, while the
+        GPU is busy. The next ``step`` uses them if its batch is the expected one and builds its
+        own otherwise; the arrays are the same either way, only earlier."""
+        last, self._last_graph_step = self._last_graph_step, None
+        self._ahead = None
+        if last is None:
+            return
+        batch, key = last
+        size, width = key
+        entries = []
+        for e in batch.entries:
+            position = e.first_position + 1
+            if position >= self.model.layout.max_positions or \
+                    any(position // self.block_size >= len(t) or t[position // self.block_size] == NULL_PAGE
+                        for t in e.block_tables):
+                return                      # a request ends or needs a page the table does not have yet
+            entries.append(BatchEntry(e.seq_id, (0,), position, e.block_tables, (0,), e.state_slot))
+        expected = ExecutionBatch(tuple(entries))
+        ctx, rows = self._context(expected, table_width=width, pad_to=size)
+        ctx.planning_context_len = width * self.block_size
+        self._plan(ctx)
+        ctx.arena.stage()
+        self._ahead = {"key": key, "batch": expected, "ctx": ctx, "rows": rows}
+
+    @staticmethod
+    def _as_expected(batch: ExecutionBatch, expected: ExecutionBatch) -> bool:
+        """Whether ``batch`` differs from ``expected`` in nothing but its token ids."""
+        if len(batch.entries) != len(expected.entries):
+            return False
+        for e, x in zip(batch.entries, expected.entries):
+            if e.seq_id != x.seq_id or e.first_position != x.first_position or e.state_slot != x.state_slot \
+                    or e.block_tables != x.block_tables or e.logits_at != x.logits_at or len(e.token_ids) != 1:
+                return False
+        return True
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault since the last check (this synchronises)."""

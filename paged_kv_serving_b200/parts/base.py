@@ -114,6 +114,9 @@ class IntArena:
     def __init__(self) -> None:
         self._arrays: dict[str, np.ndarray] = {}
         self._device: dict[str, torch.Tensor] = {}
+        self._pinned: torch.Tensor | None = None      # kept alive until the copy has run
+        self._offsets: dict[str, int] = {}
+        self._total = 0
         self.uploaded = False
         self.bytes_uploaded = 0
 
@@ -135,12 +138,11 @@ class IntArena:
     def total_ints(self) -> int:
         return max(4, sum((a.size + 3) // 4 * 4 for a in self._arrays.values()))
 
-    def upload(self, device: torch.device, into: torch.Tensor | None = None) -> None:
-        """Copy every array to the device in one transfer: into a fresh buffer, or into ``into``
-        (an int32 device tensor of ``total_ints()`` elements that a captured graph reads)."""
+    def stage(self) -> None:
+        """Pack every array into one pinned host buffer (each starts on a 16-byte boundary).
+        A step prepared ahead of time stops here; ``patch`` may still change values."""
         names = list(self._arrays)
         sizes = [self._arrays[n].size for n in names]
-        # every array starts on a 16-byte boundary (4 int32)
         offsets, total = [], 0
         for size in sizes:
             offsets.append(total)
@@ -149,6 +151,25 @@ class IntArena:
         view = host.numpy()
         for name, offset, size in zip(names, offsets, sizes):
             view[offset:offset + size] = self._arrays[name].reshape(-1)
+        self._pinned, self._offsets, self._total = host, dict(zip(names, offsets)), total
+
+    def patch(self, name: str, values: Any) -> None:
+        """Overwrite a staged array (same size) before it is sent."""
+        if self.uploaded or self._pinned is None:
+            raise RuntimeError("only a staged, unsent arena can be patched")
+        array = np.ascontiguousarray(np.asarray(values, dtype=np.int32)).reshape(self._arrays[name].shape)
+        self._arrays[name] = array
+        offset = self._offsets[name]
+        self._pinned.numpy()[offset:offset + array.size] = array.reshape(-1)
+
+    def upload(self, device: torch.device, into: torch.Tensor | None = None, views: bool = True) -> None:
+        """Copy every array to the device in one transfer: into a fresh buffer, or into ``into``
+        (an int32 device tensor of ``total_ints()`` elements that a captured graph reads).
+        ``views=False`` skips the per-array device views (a graph replay reads ``into`` by the
+        addresses it captured and asks for none)."""
+        if self._pinned is None:
+            self.stage()
+        host = self._pinned
         if into is None:
             dev = host.to(device, non_blocking=True)
         else:
@@ -156,11 +177,12 @@ class IntArena:
                 raise ValueError("the static integer buffer does not fit this step's arrays")
             dev = into
             dev[:host.numel()].copy_(host, non_blocking=True)
-        self._pinned = host  # keep alive until the copy has run
-        for name, offset, size in zip(names, offsets, sizes):
-            self._device[name] = dev[offset:offset + size].view(self._arrays[name].shape)
+        if views:
+            for name, offset in self._offsets.items():
+                array = self._arrays[name]
+                self._device[name] = dev[offset:offset + array.size].view(array.shape)
         self.uploaded = True
-        self.bytes_uploaded = total * 4
+        self.bytes_uploaded = self._total * 4
 
     def __getitem__(self, name: str) -> torch.Tensor:
         return self._device[name]

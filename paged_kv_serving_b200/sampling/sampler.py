@@ -28,7 +28,12 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams],
                generators: list[np.random.Generator]) -> list[int]:
-        """One token per row of ``logits [R, V]`` (float32, on the device)."""
+        """One token per row of ``logits [R, V]`` (float32, on the device), read back to the host."""
+        return [int(t) for t in self.sample_on_device(logits, params, generators).cpu().tolist()]
+
+    def sample_on_device(self, logits: torch.Tensor, params: list[SamplingParams],
+                         generators: list[np.random.Generator]) -> torch.Tensor:
+        """The same ids as an int32 tensor on the device: nothing waits for the GPU."""
         rows, vocab = logits.shape
         if rows != len(params) or rows != len(generators):
             raise ValueError("one SamplingParams and one generator per logits row are required")
@@ -55,5 +60,4 @@ class Sampler:
             top_p = dev[rows * 12:].view(torch.float32)
         if self._probs is None or self._probs.numel() < rows * vocab:
             self._probs = torch.empty((rows * vocab,), dtype=torch.float32, device=self.device)
-        ids = ops.sample(logits, temperature, top_p, uniform, GREEDY_TEMPERATURE, self._probs)
-        return [int(t) for t in ids.cpu().tolist()]
+        return ops.sample(logits, temperature, top_p, uniform, GREEDY_TEMPERATURE, self._probs)

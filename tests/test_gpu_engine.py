@@ -41,6 +41,51 @@ def _plain_greedy_with_margin(config, tensors, prompt, count):
     return tokens[len(prompt):], margin
 
 
+def test_decode_steps_prepared_ahead_are_the_steps_built_afresh():
+    """While the GPU runs a decode step the runner builds the integer arrays of the next one.
+    They must be the arrays it would build when the step arrives, it must use them only when the
+    batch is the expected one, and a page boundary or another batch must make it build afresh."""
+    from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+    from paged_kv_serving_b200.engine.runner import ModelRunner
+    from paged_kv_serving_b200.parts.base import StepContext
+
+    config = helpers.TINY_D
+    tensors = helpers.tensors_for("D", "bfloat16")
+    model = helpers.build_model(config, tensors, "bfloat16")
+    prompts = [helpers.random_tokens(config, n, seed=300 + n) for n in (60, 37)]
+    pages = 6
+    tables = [tuple(range(i * pages, (i + 1) * pages)) for i in range(2)]
+    outputs = {}
+    for ahead in (True, False):
+        runner = ModelRunner(model, num_blocks=2 * pages, block_size=16, max_running_seqs=2)
+        for i, p in enumerate(prompts):
+            runner.step(ExecutionBatch((BatchEntry(f"s{i}", tuple(p[:30]), 0, (tables[i],), ()),)))
+        rows, used = [], 0
+        for k in range(30, 37):
+            batch = ExecutionBatch(tuple(BatchEntry(f"s{i}", (p[k],), k, (tables[i],), (0,)) for i, p in enumerate(prompts)))
+            was_ready = runner._ahead is not None
+            result = runner.step(batch)
+            used += was_ready and runner._ahead is None
+            if ahead:
+                runner.prepare_next()
+                if k == 31:     # position 32 starts a new page of this table: it is there, so the step is prepared
+                    assert runner._ahead is not None
+                    fresh, _ = runner._context(runner._ahead["batch"], table_width=32, pad_to=2)
+                    for name, shape in fresh.arena.signature():
+                        if name != StepContext.TOKEN_IDS:
+                            assert np.array_equal(fresh.arena.host(name), runner._ahead["ctx"].arena.host(name)), name
+            rows.append(result.logits.float().cpu().numpy())
+        # another batch than the expected one: one request alone
+        runner.prepare_next() if ahead else None
+        alone = runner.step(ExecutionBatch((BatchEntry("s0", (prompts[0][37],), 37, (tables[0],), (0,)),)))
+        rows.append(alone.logits.float().cpu().numpy())
+        outputs[ahead] = np.concatenate(rows)
+        assert (used > 0) == ahead
+    assert np.array_equal(outputs[True], outputs[False])
+    want = plain_model.forward(config, tensors, prompts[0][:38])
+    helpers.assert_close(outputs[True][-1:], want[37:38], "bfloat16", "prepared-ahead decode")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
