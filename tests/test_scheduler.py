@@ -323,3 +323,58 @@ def test_abort_gives_everything_back():
     engine.flush_prefix_cache()
     engine.check_invariants()
     assert engine.cache.num_free_blocks == engine.config.num_blocks
+
+
+def test_step_arrays_are_packed_once_and_can_be_patched_before_they_are_sent():
+    """The integer arrays of a step: every array starts on a 16-byte boundary of one buffer; a
+    step prepared ahead is staged, its token ids patched when they are known, then sent."""
+    import torch
+
+    from paged_kv_serving_b200.parts.base import IntArena
+
+    arena = IntArena()
+    arena.add("token_ids", [0, 0, 0])
+    arena.add("positions", [7, 8, 9])
+    arena.add("table", np.arange(10).reshape(2, 5))
+    assert arena.signature() == (("token_ids", (3,)), ("positions", (3,)), ("table", (2, 5)))
+    assert arena.total_ints() == 4 + 4 + 12
+    arena.stage()
+    arena.patch("token_ids", [5, 6, 7])
+    with pytest.raises(ValueError):
+        arena.patch("token_ids", [1, 2])
+    target = torch.full((arena.total_ints(),), -1, dtype=torch.int32)
+    arena.upload(torch.device("cpu"), into=target)
+    assert target[:3].tolist() == [5, 6, 7] and target[4:7].tolist() == [7, 8, 9]
+    assert arena["table"].tolist() == np.arange(10).reshape(2, 5).tolist()
+    assert arena.host("token_ids").tolist() == [5, 6, 7] and arena.bytes_uploaded == 80
+    with pytest.raises(RuntimeError):
+        arena.patch("token_ids", [1, 2, 3])     # already sent
+    with pytest.raises(RuntimeError):
+        arena.add("more", [1])
+
+
+def test_even_shares_decode_kernel_is_chosen_only_when_a_round_of_blocks_would_be_nearly_empty():
+    import torch
+
+    from paged_kv_serving_b200.parts import attention
+    from paged_kv_serving_b200.parts.position import RotaryEncoding
+
+    def part(n_kv):
+        return attention.PagedAttention(width=64 * n_kv, n_heads=n_kv, n_kv_heads=n_kv, head_dim=64,
+                                        position=RotaryEncoding(64, 10000.0, 128))
+
+    saved = attention._sm_count
+    attention._sm_count = lambda device: 148
+    try:
+        cpu = torch.device("cpu")
+        assert not part(8)._flat_pays(8, cpu)        # 64 pairs on 296 places: one round
+        assert not part(8)._flat_pays(64, cpu)       # 512 pairs: 1.7 rounds, the second one well filled
+        assert part(40)._flat_pays(8, cpu)           # 320 pairs: the second round holds 24 blocks
+        assert not part(40)._flat_pays(64, cpu)      # 2,560 pairs: 8.6 rounds
+        forced = part(8)
+        forced.FLAT_DECODE = "always"
+        assert forced._flat_pays(1, cpu)
+        forced.FLAT_DECODE = "never"
+        assert not forced._flat_pays(1000, cpu)
+    finally:
+        attention._sm_count = saved
