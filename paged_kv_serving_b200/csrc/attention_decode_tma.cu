@@ -227,8 +227,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   // ---- merge the four consumer warps (each saw a quarter of the keys) ----
   __syncthreads();           // every copy that was waited for has landed; the ring is free
-  float* o_s = reinterpret_cast<float*>(ring);                       // [4][DT_ROWS][HD]
-  float* part_o = o_s + 4 * DT_ROWS * HD;                            // [DT_ROWS][HD]
+  constexpr int OS = HD + 4;   // row stride of o_s: four floats on, the rows of a warp's store fall into different banks
+  float* o_s = reinterpret_cast<float*>(ring);                       // [4][DT_ROWS][OS]
+  float* part_o = o_s + 4 * DT_ROWS * OS;                            // [DT_ROWS][HD]
   if (warp < 4) {
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
@@ -238,10 +239,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) {
-      float* da = o_s + ((size_t)warp * DT_ROWS + g) * HD + i * 8 + 2 * t4;
-      float* db = o_s + ((size_t)warp * DT_ROWS + g + 8) * HD + i * 8 + 2 * t4;
-      da[0] = o[i][0]; da[1] = o[i][1];
-      db[0] = o[i][2]; db[1] = o[i][3];
+      float* da = o_s + ((size_t)warp * DT_ROWS + g) * OS + i * 8 + 2 * t4;
+      float* db = o_s + ((size_t)warp * DT_ROWS + g + 8) * OS + i * 8 + 2 * t4;
+      if (g < rows_valid) { da[0] = o[i][0]; da[1] = o[i][1]; }
+      if (g + 8 < rows_valid) { db[0] = o[i][2]; db[1] = o[i][3]; }
     }
   }
   __syncthreads();
@@ -257,7 +258,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       for (int w = 0; w < 4; ++w) {
         const float f = exp2f(warp_m[w][row] - m);
         l += warp_l[w][row] * f;
-        acc += o_s[((size_t)w * DT_ROWS + row) * HD + d] * f;
+        acc += o_s[((size_t)w * DT_ROWS + row) * OS + d] * f;
       }
     }
     if (p.num_splits == 1) {
