@@ -100,8 +100,11 @@ def _cache(config, batch: int, context: int, page: int):
     kv, hd = config.n_kv_heads, config.head_dim
     pages_per = -(-context // page)
     pages = batch * pages_per
-    k = torch.randn((LAYERS, pages, kv, page, hd), device="cuda", dtype=torch.bfloat16)
-    v = torch.randn((LAYERS, pages, kv, page, hd), device="cuda", dtype=torch.bfloat16)
+    # as many layers' pools as fit in 16 GiB each for keys and values (at least two, so that a
+    # replay does not find its keys in L2): callers rotate over k.shape[0]
+    layers = int(max(2, min(LAYERS, (16 << 30) // max(1, pages * kv * page * hd * 2))))
+    k = torch.randn((layers, pages, kv, page, hd), device="cuda", dtype=torch.bfloat16)
+    v = torch.randn((layers, pages, kv, page, hd), device="cuda", dtype=torch.bfloat16)
     table = torch.tensor([[j * batch + i for j in range(pages_per)] for i in range(batch)], dtype=torch.int32, device="cuda")
     return k, v, table
 
@@ -124,10 +127,10 @@ def bench_prefill_attention(config, page: int) -> None:
             if name == "tcgen05":
                 if not ops.attention_tcgen05_supports(hd, page, qkv.shape[1]):
                     continue
-                fn = lambda i: ops.attention_prefill_tcgen05(qkv, out, k[i % LAYERS], v[i % LAYERS], table, starts, first,
+                fn = lambda i: ops.attention_prefill_tcgen05(qkv, out, k[i % k.shape[0]], v[i % k.shape[0]], table, starts, first,
                                                              seq, q0, h, kv, hd, page, 0, 1 / math.sqrt(hd), status)
             else:
-                fn = lambda i: ops.attention_prefill_bf16(qkv, out, k[i % LAYERS], v[i % LAYERS], table, starts, first,
+                fn = lambda i: ops.attention_prefill_bf16(qkv, out, k[i % k.shape[0]], v[i % k.shape[0]], table, starts, first,
                                                           seq, q0, h, kv, hd, page, 0, 1 / math.sqrt(hd))
             us = timed(fn, launches=8)
             print(f"prefill attention {name:8s} {batch} x {queries} queries over {context} keys: {us:8.1f} us "
@@ -148,14 +151,24 @@ def bench_decode_attention(config, page: int) -> None:
         work = torch.arange(batch, dtype=torch.int32, device="cuda")
         nbytes = 2.0 * batch * context * kv * hd * 2
         if ops.attention_decode_tma_supports(hd, page, qkv.shape[1]):
-            resident = ops.attention_decode_tma_blocks_per_sm(hd, False) * sms
+            resident = min(2, ops.attention_decode_tma_blocks_per_sm(hd, False)) * sms
             splits = max(1, min(8, -(-context // 64), resident // (batch * kv)))
-            us = timed(lambda i: ops.attention_decode_tma(qkv, out, k[i % LAYERS], v[i % LAYERS], table, starts, first, work,
+            pushed = ops.attention_decode_tma_pushed_splits(hd, h // kv)
+            if splits > 4 and 4 <= pushed < splits:
+                splits = pushed
+            us = timed(lambda i: ops.attention_decode_tma(qkv, out, k[i % k.shape[0]], v[i % k.shape[0]], table, starts, first, work,
                                                           1, h, kv, hd, page, 0, 1 / math.sqrt(hd), splits, status, False))
             print(f"decode attention TMA      batch {batch:3d} context {context}: {splits} splits {us:7.1f} us {nbytes / us / 1e6:5.2f} TB/s")
+        if ops.attention_decode_flat_supports(hd, page, qkv.shape[1]):
+            tiles = -(-context // 64)
+            units = torch.arange(0, batch + 1, dtype=torch.int32, device="cuda") * tiles
+            blocks = min(min(2, ops.attention_decode_flat_blocks_per_sm(hd)) * sms, batch * kv * tiles)
+            us = timed(lambda i: ops.attention_decode_flat(qkv, out, k[i % k.shape[0]], v[i % k.shape[0]], table, starts, first, work,
+                                                           units, 1, h, kv, hd, page, 0, 1 / math.sqrt(hd), blocks, status))
+            print(f"decode attention even shares batch {batch:3d} context {context}: {blocks} blocks {us:7.1f} us {nbytes / us / 1e6:5.2f} TB/s")
         resident = ops.attention_decode_blocks_per_sm(hd) * sms
         splits = max(1, min(8, -(-context // 64), resident // (batch * kv)))
-        us = timed(lambda i: ops.attention_decode_bf16(qkv, out, k[i % LAYERS], v[i % LAYERS], table, starts, first, work,
+        us = timed(lambda i: ops.attention_decode_bf16(qkv, out, k[i % k.shape[0]], v[i % k.shape[0]], table, starts, first, work,
                                                        1, h, kv, hd, page, 0, 1 / math.sqrt(hd), splits, None))
         print(f"decode attention cp.async batch {batch:3d} context {context}: {splits} splits {us:7.1f} us {nbytes / us / 1e6:5.2f} TB/s")
     assert int(status.item()) == 0
