@@ -378,3 +378,28 @@ def test_even_shares_decode_kernel_is_chosen_only_when_a_round_of_blocks_would_b
         assert not forced._flat_pays(1000, cpu)
     finally:
         attention._sm_count = saved
+
+
+def test_a_prepared_step_is_used_only_for_the_batch_it_was_prepared_for():
+    from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+    from paged_kv_serving_b200.engine.runner import ModelRunner
+
+    def batch(*entries):
+        return ExecutionBatch(tuple(entries))
+
+    expected = batch(BatchEntry("a", (0,), 40, ((3, 4, 5),), (0,), None), BatchEntry("b", (0,), 17, ((9, 8),), (0,), None))
+    same = batch(BatchEntry("a", (123,), 40, ((3, 4, 5),), (0,), None), BatchEntry("b", (7,), 17, ((9, 8),), (0,), None))
+    assert ModelRunner._as_expected(same, expected)
+    others = [
+        batch(same.entries[0]),                                                                   # a request left
+        batch(same.entries[1], same.entries[0]),                                                  # another order
+        batch(BatchEntry("a", (1,), 41, ((3, 4, 5),), (0,), None), same.entries[1]),               # another position
+        batch(BatchEntry("a", (1,), 40, ((3, 4, 6),), (0,), None), same.entries[1]),               # a page copied on write
+        batch(BatchEntry("a", (1,), 40, ((3, 4, 5, 6),), (0,), None), same.entries[1]),            # a page more
+        batch(BatchEntry("c", (1,), 40, ((3, 4, 5),), (0,), None), same.entries[1]),               # another request
+        batch(BatchEntry("a", (1, 2), 40, ((3, 4, 5),), (1,), None), same.entries[1]),             # a portion of a prompt
+        batch(BatchEntry("a", (1,), 40, ((3, 4, 5),), (), None), same.entries[1]),                 # no logits wanted
+        batch(BatchEntry("a", (1,), 40, ((3, 4, 5),), (0,), 2), same.entries[1]),                  # another state slot
+    ]
+    for other in others:
+        assert not ModelRunner._as_expected(other, expected)
