@@ -283,13 +283,19 @@ def attention_decode_tma_blocks_per_sm(head_dim: int, deep_ring: bool) -> int:
     return _DECODE_TMA_BLOCKS[key]
 
 
+_DECODE_TMA_PUSHED: dict[tuple[int, int], int] = {}
+
+
 def attention_decode_tma_pushed_splits(head_dim: int, rows: int) -> int:
     """Most splits that the TMA decode kernel merges the fast way (the other blocks of a cluster
     push their states into the first one) for entries of ``rows`` (token, head in group) rows."""
-    lib = library("attention_decode_tma")
-    lib.pkv_attention_decode_tma_pushed_splits.restype = c_int
-    lib.pkv_attention_decode_tma_pushed_splits.argtypes = [c_int, c_int]
-    return int(lib.pkv_attention_decode_tma_pushed_splits(int(head_dim), int(rows)))
+    key = (int(head_dim), int(rows))
+    if key not in _DECODE_TMA_PUSHED:
+        lib = library("attention_decode_tma")
+        lib.pkv_attention_decode_tma_pushed_splits.restype = c_int
+        lib.pkv_attention_decode_tma_pushed_splits.argtypes = [c_int, c_int]
+        _DECODE_TMA_PUSHED[key] = int(lib.pkv_attention_decode_tma_pushed_splits(*key))
+    return _DECODE_TMA_PUSHED[key]
 
 
 def attention_decode_tma(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
