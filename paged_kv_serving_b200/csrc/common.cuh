@@ -73,59 +73,11 @@ inline int launch_status() {
 // the stream has finished, not only its direct predecessor. Kernels call both at their top
 // (the calls do nothing in a kernel launched the ordinary way); only what is constant during a
 // step (weights) may be touched before the wait.
-#ifdef PKV_TRACE
-// Development aid (-DPKV_TRACE): the first thread of every kernel notes the global nanosecond
-// timer when it passes `dependents_may_launch()` (what = 0) and when its dependency wait returns
-// (what = 1), in a ring that each library keeps; `pkv_trace_read` copies the ring out. The time
-// at which a kernel's wait returns is also the time at which the kernel before it had finished.
-struct TraceRecord {
-  unsigned long long t;
-  int what, grid, block, pad;
-};
-static __device__ TraceRecord trace_ring[8192];
-static __device__ unsigned int trace_count;
-__device__ __forceinline__ void trace_note(int what) {
-  if ((blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const unsigned int i = atomicAdd(&trace_count, 1u) & 8191u;
-    trace_ring[i].t = t;
-    trace_ring[i].what = what;
-    trace_ring[i].grid = (int)(gridDim.x * gridDim.y * gridDim.z);
-    trace_ring[i].block = (int)blockDim.x;
-  }
-}
-// the same from the first thread of every block (what >= 16; with -DPKV_TRACE_BLOCKS as well), to
-// see how far apart blocks finish
-__device__ __forceinline__ void trace_note_block(int what) {
-  if (threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const unsigned int i = atomicAdd(&trace_count, 1u) & 8191u;
-    trace_ring[i].t = t;
-    trace_ring[i].what = what;
-    trace_ring[i].grid = (int)(gridDim.x * gridDim.y * gridDim.z);
-    trace_ring[i].block = (int)blockIdx.x;
-  }
-}
-#define PKV_TRACE_NOTE(what) pkv::trace_note(what)
-#ifdef PKV_TRACE_BLOCKS
-#define PKV_TRACE_NOTE_BLOCK(what) pkv::trace_note_block(what)
-#else
-#define PKV_TRACE_NOTE_BLOCK(what)
-#endif
-#else
-#define PKV_TRACE_NOTE(what)
-#define PKV_TRACE_NOTE_BLOCK(what)
-#endif
-
 __device__ __forceinline__ void dependents_may_launch() {
-  PKV_TRACE_NOTE(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ void wait_for_prior_kernels() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  PKV_TRACE_NOTE(1);
 }
 
 // Launches `kernel`; `chained` as above, `cluster_x` > 0 groups that many blocks along x into a
@@ -162,12 +114,3 @@ inline int launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t sme
 }
 
 }  // namespace pkv
-
-#ifdef PKV_TRACE
-// Copies the library's trace ring (8192 records of 24 bytes) and its count to the host.
-PKV_EXPORT int pkv_trace_read(void* records, unsigned int* count) {
-  cudaError_t e = cudaMemcpyFromSymbol(records, pkv::trace_ring, sizeof(pkv::trace_ring));
-  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(count, pkv::trace_count, sizeof(unsigned int));
-  return (int)e;
-}
-#endif

@@ -188,7 +188,6 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, PER_SM) gemm_small_m_kernel(
   __shared__ int is_last;
   __shared__ float inv_root_s[32];
   __shared__ float squares[EPI == EPI_RESIDUAL ? SLOTS * 32 : 1];
-  PKV_TRACE_NOTE(2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   // units of work (tile-major) [range_begin, range_end) of this block; fewer than 2^31 in all
@@ -344,7 +343,6 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, PER_SM) gemm_small_m_kernel(
       // places that free up and request its own first weights. (Earlier would be no gain: its
       // blocks would sit beside blocks of this kernel that still wait for a place.)
       pkv::dependents_may_launch();
-      PKV_TRACE_NOTE_BLOCK(16);
     }
 
 #pragma unroll
@@ -434,7 +432,6 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, PER_SM) gemm_small_m_kernel(
     }
     __syncthreads();  // `red`, `is_last` and `squares` are written again in the next round
   }
-  PKV_TRACE_NOTE_BLOCK(17);
 }
 
 int sm_count() {

@@ -14,7 +14,9 @@
 // output does not depend on the batch it was sampled in.
 //
 // `probs` is scratch memory of n_rows * vocab floats: the kernel writes the (filtered)
-// probabilities there and reads them back in later passes.
+// probabilities there and reads them back in later passes. With `status_word` (a device int, may
+// be null) `out` has n_rows + 1 elements and the last one receives the word's value, so that the
+// host learns of a fault that a kernel of the step recorded in the copy that brings the ids.
 #include "common.cuh"
 
 namespace pkv {
@@ -80,15 +82,19 @@ __device__ double block_scan_d(double v, double* scratch, double* total) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const double* __restrict__ uniform, float* __restrict__ probs,
-              int32_t* __restrict__ out, int vocab, float greedy_below) {
+              int32_t* __restrict__ out, int vocab, float greedy_below, const int* __restrict__ status_word) {
   __shared__ double scratch_d[33];
   __shared__ ArgMax scratch_a[32];
   __shared__ float shared_f;
   __shared__ int shared_i;
+  __shared__ int shared_last;
   dependents_may_launch();
   wait_for_prior_kernels();
   const int r = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // every kernel of the step has finished (the wait above): what they recorded in the device's
+  // status word travels to the host behind the ids, in the same copy
+  if (status_word != nullptr && r == 0 && tid == 0) out[gridDim.x] = *status_word;
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature[r];
 
@@ -192,23 +198,35 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, const floa
 
   // ---- inverse CDF in id order ----
   double mine = 0.0;
-  for (int i = c0; i < c1; ++i) mine += (double)p[i];
+  int last_kept = -1;   // the highest id of this thread's share with a probability above zero
+  for (int i = c0; i < c1; ++i) {
+    mine += (double)p[i];
+    if (p[i] > 0.0f) last_kept = i;
+  }
   double total;
   const double before = block_scan_d(mine, scratch_d, &total);
   const double draw = uniform[r] * total;
-  if (tid == 0) shared_i = vocab - 1;
+  if (tid == 0) {
+    shared_i = -1;
+    shared_last = 0;
+  }
   __syncthreads();
-  if (c1 > c0 && before <= draw && before + mine > draw) {
+  if (last_kept >= 0) atomicMax(&shared_last, last_kept);
+  if (last_kept >= 0 && before <= draw && before + mine > draw) {
+    // `before` comes from the block's scan and `mine` from this loop: their roundings differ by an
+    // ulp, so the loop may end without crossing the draw; the share's last kept id then takes it
     double c = before;
-    int token = c1 - 1;
+    int token = last_kept;
     for (int i = c0; i < c1; ++i) {
       c += (double)p[i];
-      if (c > draw) { token = i; break; }
+      if (c > draw && p[i] > 0.0f) { token = i; break; }
     }
     shared_i = token;
   }
   __syncthreads();
-  if (tid == 0) out[r] = shared_i;
+  // a draw at the very top of the distribution (u * total rounding up to the total) is claimed by
+  // no share: it belongs to the last id that the filter kept, never to a zeroed one
+  if (tid == 0) out[r] = shared_i >= 0 ? shared_i : shared_last;
 }
 
 }  // namespace pkv
@@ -217,11 +235,11 @@ using namespace pkv;
 
 PKV_EXPORT int pkv_sample(const float* logits, long long row_stride, const float* temperature, const float* top_p,
                           const double* uniform, float* probs, int32_t* out, int n_rows, int vocab,
-                          float greedy_below, void* stream) {
+                          float greedy_below, const int* status_word, void* stream) {
   if (n_rows <= 0) return 0;
   if (vocab <= 0 || row_stride < vocab) return PKV_ERR_SIZE;
   return launch_kernel(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, true, 0, logits, row_stride,
-                       temperature, top_p, uniform, probs, out, vocab, greedy_below);
+                       temperature, top_p, uniform, probs, out, vocab, greedy_below, status_word);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -248,7 +266,7 @@ PKV_EXPORT int pkv_sample_static_scratch(const float* logits, long long row_stri
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
-  if (device < 0 || device >= kMaxDevices) return PKV_ERR_LIMIT;
+  if (device < 0 || device >= kMaxDevices) return PKV_SAMPLE_STATIC_DEVICE_INDEX;
   if (!static_area_of_device[device]) {
     // set-up, once per device, with that device current
     float* address = nullptr;
@@ -258,6 +276,6 @@ PKV_EXPORT int pkv_sample_static_scratch(const float* logits, long long row_stri
   }
   sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, temperature, top_p, uniform,
                                                                     static_area_of_device[device], out, vocab,
-                                                                    greedy_below);
+                                                                    greedy_below, nullptr);
   return launch_status();
 }

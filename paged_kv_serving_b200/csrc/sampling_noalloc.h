@@ -20,6 +20,8 @@
  * Limits and rules.
  *  - n_rows * vocab must not exceed PKV_SAMPLE_STATIC_FLOATS; a larger request is refused with
  *    PKV_SAMPLE_STATIC_TOO_LARGE (-5) and nothing is launched.
+ *  - The addresses are kept for device indices 0 to 63; on a device with a higher index the
+ *    call is refused with PKV_SAMPLE_STATIC_DEVICE_INDEX (-6).
  *  - The first call on each device looks up the device address of the work area
  *    (cudaGetSymbolAddress, with that device current) and keeps it. Make that first call
  *    outside of any stream capture.
@@ -38,6 +40,7 @@
 
 #define PKV_SAMPLE_STATIC_FLOATS (1 << 20)
 #define PKV_SAMPLE_STATIC_TOO_LARGE (-5)
+#define PKV_SAMPLE_STATIC_DEVICE_INDEX (-6)
 
 #ifdef __cplusplus
 extern "C" {

@@ -28,14 +28,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
   return done != 0;
 }
-// Bounded wait: false when the block gave up (its own limit ran out, or another role did).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait: false when the block gave up (its own limit of `limit_cycles` clock cycles ran
+// out, or another role of the block did). The kernels wait for about a second.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit_cycles = GM_WAIT_CYCLES) {
   const long long start = clock64();
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 0xff) == 0xff) {
       if (*abort_flag) return false;
-      if (clock64() - start > GM_WAIT_CYCLES) {
+      if (clock64() - start > limit_cycles) {
         *abort_flag = 1;
         return false;
       }

@@ -357,11 +357,18 @@ class Engine:
 
                 logits = device_logits.index_select(0, torch.tensor(index, device=device_logits.device))
             self.h2d_bytes_last_step += 32 * len(samplers)
-            self.d2h_bytes_last_step = 4 * len(samplers)
-            ids = self.sampler.sample_on_device(logits, params, generators)
+            ids = self.sampler.sample_on_device(logits, params, generators, status=self.runner.status)
             # the GPU is busy with this step: the host gets the arrays of the next one ready
             self.runner.prepare_next()
-            return [int(t) for t in ids.cpu().tolist()]
+            # one copy brings the ids and, behind them, the device's status word: a kernel that
+            # recorded a fault (a wait it gave up, an id outside the table) stops generation here
+            # instead of letting wrong tokens through
+            values = ids.cpu().tolist()
+            self.d2h_bytes_last_step = 4 * len(values)
+            from paged_kv_serving_b200 import ops
+
+            ops.raise_for_status(values.pop(), self.runner.model.device)
+            return [int(t) for t in values]
         # rows of a stand-in executor (tests without a GPU): the caller's sampler, else the argmax
         if self.host_sampler is not None:
             return [int(self.host_sampler(np.asarray(host_rows[row]), p, g))

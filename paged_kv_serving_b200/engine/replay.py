@@ -24,7 +24,9 @@ import sys
 from pathlib import Path
 
 import numpy as np
+import torch
 
+from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.cache.manager import KVCacheManager
 from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
 from paged_kv_serving_b200.engine.sequence import Request, SamplingParams, Sequence
@@ -92,9 +94,17 @@ class ReplaySession:
             sequence = self.live.pop(str(name), None)
             if sequence is not None:
                 self.cache.free(sequence)
-        if result.logits is None:
-            return None
-        return result.logits.cpu().numpy()
+        # the wanted logits and the device's status word cross to the host behind one
+        # synchronisation; a fault that a kernel recorded raises instead of writing wrong logits
+        status = torch.empty((1,), dtype=torch.int32, pin_memory=True)
+        status.copy_(self.runner.status, non_blocking=True)
+        host = None
+        if result.logits is not None:
+            host = torch.empty(result.logits.shape, dtype=torch.float32, pin_memory=True)
+            host.copy_(result.logits, non_blocking=True)
+        torch.cuda.current_stream(self.model.device).synchronize()
+        ops.raise_for_status(int(status[0]), self.model.device)
+        return None if host is None else host.numpy().copy()
 
     def check_invariants(self) -> None:
         self.cache.check_invariants()

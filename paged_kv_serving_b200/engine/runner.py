@@ -378,13 +378,16 @@ class ModelRunner:
                 return False
         return True
 
+    @property
+    def status(self) -> torch.Tensor:
+        """The device's status word (int32 [1]): zero unless a kernel recorded a fault. Callers
+        that copy results to the host anyway read it in the same copy and hand the value to
+        ``ops.raise_for_status``; ``check_status`` is the stand-alone form."""
+        return self._status
+
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault since the last check (this synchronises)."""
-        code = int(self._status.item())
-        if code:
-            self._status.zero_()
-            what = {1: "a token id outside the embedding table", 2: "a tensor-core product gave up a wait"}
-            raise RuntimeError(f"a kernel recorded a fault: {what.get(code, f'code {code}')}")
+        ops.raise_for_status(int(self._status.item()), self.model.device)
 
     def execute(self, batch: ExecutionBatch) -> dict[str, np.ndarray]:
         """The reference's executor interface (src/paged_kv_serving/engine/engine.py:64-73):

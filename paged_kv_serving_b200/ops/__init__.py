@@ -3,6 +3,10 @@
 Every wrapper takes torch tensors that live on the GPU, checks what the kernel relies on
 (dtype, contiguity, sizes), launches on torch's current stream and raises on a refused argument
 or a failed launch. Nothing here falls back to a library or to the CPU.
+
+Three kernels keep a workspace per device from launch to launch (partial tiles, arrival counters,
+flags: ``gemm_small_m``, the two-SM ``gemm_tcgen05``, ``attention_decode_flat``). They are shared by
+every caller in the process and serve one stream per device; see ``_one_stream``.
 """
 
 from __future__ import annotations
@@ -22,13 +26,14 @@ __all__ = [
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
     "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
     "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
-    "launch_count", "library", "library_names", "paged_attention_generic", "rope_kv_store", "sample", "silu_mul", "status_word",
+    "launch_count", "library", "library_names", "paged_attention_generic", "raise_for_status", "reset_workspaces",
+    "rope_kv_store", "sample", "silu_mul", "status_word", "wait_probe",
 ]
 
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
 _ERRORS = {
     -2: "unsupported element type", -3: "refused size", -4: "refused alignment",
-    -5: "size beyond the kernel's limit",
+    -5: "size beyond the kernel's limit", -6: "device index beyond the kernel's table",
 }
 
 
@@ -149,11 +154,66 @@ _STATUS: dict[str, torch.Tensor] = {}
 
 def status_word(device: torch.device | str) -> torch.Tensor:
     """The int32 status word of a device: kernels record a code there instead of trapping
-    (1: a token id outside the embedding table, 2: a tensor-core product gave up a wait)."""
+    (1: a token id outside the embedding table, 2: a kernel gave up a bounded wait)."""
     key = str(torch.device(device))
     if key not in _STATUS:
         _STATUS[key] = torch.zeros((1,), dtype=torch.int32, device=device)
     return _STATUS[key]
+
+
+STATUS_MEANINGS = {1: "a token id outside the embedding table", 2: "a kernel gave up a bounded wait"}
+
+
+def raise_for_status(code: int, device: torch.device | str) -> None:
+    """What the host does with a status word it has read: nothing for 0; otherwise the word and
+    the workspaces that kernels share from launch to launch are cleared (a kernel that gave up
+    may have left counters or flags set, which would spoil every later launch) and the fault is
+    raised. The results of the step that recorded the code are not to be used."""
+    if not code:
+        return
+    torch.cuda.synchronize(device)
+    status_word(device).zero_()
+    reset_workspaces(device)
+    raise RuntimeError(f"a kernel recorded a fault: {STATUS_MEANINGS.get(int(code), f'code {int(code)}')}")
+
+
+def reset_workspaces(device: torch.device | str) -> None:
+    """Zero the counters, flags and partial sums that kernels of this module keep on a device
+    between launches (they are left zero by every launch that ends in order)."""
+    key = str(torch.device(device))
+    for kept in _DECODE_FLAT_SCRATCH.get(key, []):
+        kept[1].zero_()
+    for table in (_GEMM_WORKSPACE, _SMALL_M_WORKSPACE):
+        if key in table:
+            table[key].zero_()
+
+
+_WORKSPACE_STREAM: dict[str, int] = {}
+
+
+def _one_stream(device: torch.device | str) -> None:
+    """The shared workspaces serve the launches of ONE stream per device: two launches that
+    overlap would count each other's tiles. The first stream that uses them is remembered; a
+    launch from another stream is refused unless it is being captured into a graph (a capture
+    runs on a stream of its own and records launches, it runs none)."""
+    key = str(torch.device(device))
+    stream = torch.cuda.current_stream(device).cuda_stream
+    known = _WORKSPACE_STREAM.setdefault(key, stream)
+    if known != stream and not torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("the kernels' shared workspaces of this device belong to the stream that used them "
+                           "first; launches from a second stream would race on their counters")
+
+
+def wait_probe(status: torch.Tensor, limit_cycles: int) -> torch.Tensor:
+    """Run one bounded wait that nothing will ever satisfy, with a limit of ``limit_cycles`` SM
+    clock cycles: the wait gives up by itself and the kernel records code 2 in ``status`` as the
+    tensor-core and TMA kernels do. Returns a device int that is 1 when the wait gave up. This is
+    how the give-up path is exercised without faulting, trapping or hanging anything."""
+    _need(status, torch.int32, "status")
+    gave_up = torch.zeros((1,), dtype=torch.int32, device=status.device)
+    fn = _fn("wait_probe", "pkv_wait_probe", [c_void_p, c_longlong, c_void_p, c_void_p])
+    _check(fn(_ptr(status), int(limit_cycles), _ptr(gave_up), _stream()), "wait_probe")
+    return gave_up
 
 
 def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None,
@@ -343,6 +403,7 @@ def _decode_flat_scratch(device: torch.device, floats: int, pairs: int) -> tuple
     """Workspace and arrival counters of ``attention_decode_flat`` on a device. Counters are zeroed
     once and left zero by every launch. A buffer that has become too small is replaced but kept
     alive, since captured graphs may still point at it."""
+    _one_stream(device)
     key = str(torch.device(device))
     kept = _DECODE_FLAT_SCRATCH.setdefault(key, [])
     if not kept or kept[-1][0].numel() < floats or kept[-1][1].numel() < pairs:
@@ -465,6 +526,7 @@ _GEMM_WORKSPACE: dict[str, torch.Tensor] = {}
 def gemm_workspace(device: torch.device | str) -> torch.Tensor:
     """The workspace of the two-SM tcgen05 product on a device (partial accumulators and flags of
     its stream-K hand-over), allocated and zeroed once. Launches on one stream share it."""
+    _one_stream(device)
     key = str(torch.device(device))
     if key not in _GEMM_WORKSPACE:
         lib = library("gemm_tcgen05")
@@ -528,6 +590,7 @@ _SMALL_M_WORKSPACE: dict[str, torch.Tensor] = {}
 def _small_m_workspace(device: torch.device) -> torch.Tensor:
     """Partial sums and tile counters of ``gemm_small_m`` on a device: allocated and zeroed once,
     left zero by every launch, shared by the launches of a stream."""
+    _one_stream(device)
     key = str(torch.device(device))
     if key not in _SMALL_M_WORKSPACE:
         lib = library("gemm_small_m")
@@ -627,8 +690,10 @@ def finish_norm(xw: torch.Tensor, sumsq: torch.Tensor, eps: float) -> torch.Tens
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
-           greedy_below: float, probs: torch.Tensor | None = None) -> torch.Tensor:
-    """One token id per row of ``logits [R, V]`` (float32); ``uniform`` is float64, one per row."""
+           greedy_below: float, probs: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """One token id per row of ``logits [R, V]`` (float32); ``uniform`` is float64, one per row.
+    With ``status`` (the device's status word) the result has ``R + 1`` elements and the last is
+    the word's value after every earlier kernel on the stream has finished."""
     _need(logits, torch.float32, "logits"); _need(temperature, torch.float32, "temperature")
     _need(top_p, torch.float32, "top_p"); _need(uniform, torch.float64, "uniform")
     rows, vocab = logits.shape
@@ -638,9 +703,12 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
         _need(probs, torch.float32, "probs")
         if probs.numel() < rows * vocab:
             raise ValueError("probs scratch is smaller than the logits")
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if status is not None:
+        _need(status, torch.int32, "status")
+    out = torch.empty((rows + (status is not None),), dtype=torch.int32, device=logits.device)
     fn = _fn("sampling", "pkv_sample",
-             [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
+              c_void_p])
     _check(fn(_ptr(logits), logits.stride(0), _ptr(temperature), _ptr(top_p), _ptr(uniform), _ptr(probs), _ptr(out),
-              rows, vocab, float(greedy_below), _stream()), "sample")
+              rows, vocab, float(greedy_below), _ptr(status), _stream()), "sample")
     return out

@@ -126,6 +126,14 @@ def library(name: str) -> ctypes.CDLL:
         return lib
 
 
-def build_all() -> list[Path]:
-    """Compile every library (used by the build check); returns their paths."""
-    return [_locate_or_build(name) for name in library_names()]
+def build_all(prune: bool = True) -> list[Path]:
+    """Compile every library (used by the build check); returns their paths. ``prune`` removes
+    libraries of earlier source versions from the folders the new ones went to."""
+    built = [_locate_or_build(name) for name in library_names()]
+    if prune:
+        current = {path.name for path in built}
+        for directory in {path.parent for path in built}:
+            for stale in directory.glob("*-????????????????.so"):
+                if stale.name not in current:
+                    stale.unlink(missing_ok=True)
+    return built

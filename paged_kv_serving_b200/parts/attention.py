@@ -143,7 +143,11 @@ class PagedAttention(Part):
         return pairs > places and 1.0 - rounds / math.ceil(rounds) > self.FLAT_DECODE_IDLE_SHARE
 
     def _fast_key(self, page_size: int) -> str:
-        return f"attention/fast/g{self.group_size}/{'t' if self._tcgen05(page_size) else 'm'}"
+        """Name of this mixer's plan among a step's plans. Everything the plan depends on is part
+        of it (head counts and size decide splits and grids, the window the tiles of an entry,
+        the page size which kernels serve), so that layers share a plan only when it is the same."""
+        return (f"attention/fast/h{self.n_heads}k{self.n_kv_heads}d{self.head_dim}w{self.window or 0}p{page_size}/"
+                f"{'t' if self._tcgen05(page_size) else 'm'}")
 
     def _plan_fast(self, ctx: StepContext, page_size: int) -> None:
         """Work lists of the bfloat16 kernels: entries of at most 16 rows per key/value head go

@@ -82,3 +82,22 @@ def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what: str) -> No
         first_bad = int(np.argmax(gap.max(axis=-1) > atol))
         raise AssertionError(f"{what}: max |gap| {worst:.3e} > {atol:.3e} at row {row}, column {col}; "
                              f"first row beyond the bound: {first_bad}")
+
+
+def assert_greedy_tokens(config: dict, tensors: dict[str, np.ndarray], prompt, got, dtype: str, what: str) -> None:
+    """Greedy tokens of the engine against the plain implementation. In float32 they are equal. In
+    bfloat16 a token may differ from the plain choice only at a near tie: the plain logits are
+    computed on the engine's own tokens (one whole-sequence pass), and at every place the logit of
+    the engine's token must lie within the rounding bound of the plain maximum (twice the bound of
+    one logit, since both may be off). A wrong cache or kernel moves logits by far more."""
+    got = [int(t) for t in got]
+    if dtype == "float32":
+        want = plain_model.generate(config, tensors, prompt, len(got))
+        assert got == want, f"{what}: float32 tokens {got} differ from the plain implementation's {want}"
+        return
+    rows = plain_model.forward(config, tensors, list(prompt) + got[:-1])[len(prompt) - 1:]
+    for place, (token, row) in enumerate(zip(got, rows)):
+        slack = 2 * bf16_atol(row)
+        assert row[token] >= row.max() - slack, (
+            f"{what}: token {place} is {token} (plain logit {row[token]:.4f}) but the plain maximum is "
+            f"{row.max():.4f} at {int(row.argmax())}; allowed gap {slack:.4f}")

@@ -90,8 +90,7 @@ def test_mixed_requests_with_page_reuse(name, dtype):
     progress = [0] * len(prompts)
     waiting = list(range(len(prompts)))
     live: list[int] = []
-    pages_seen: set[int] = set()
-    reused = False
+    owners: dict[int, set[str]] = {}      # page -> the requests that have held it
     step = 0
     while waiting or live:
         while waiting and len(live) < 4 and sum(-(-lengths[i] // 64) * 64 for i in live) + 64 <= 256:
@@ -112,9 +111,9 @@ def test_mixed_requests_with_page_reuse(name, dtype):
         for row, (i, position) in enumerate(checks):
             helpers.assert_close(got[row:row + 1], wants[i][position:position + 1], dtype,
                                  f"{name} mixed step {step} request {i} position {position}")
-        for sequence in session.live.values():
+        for request, sequence in session.live.items():
             for page in sequence.block_table:
-                pages_seen.add(page)
+                owners.setdefault(page, set()).add(request)
         for i in finished:
             live.remove(i)
         session.check_invariants()
@@ -122,6 +121,8 @@ def test_mixed_requests_with_page_reuse(name, dtype):
     total_pages_needed = sum(-(-n // helpers.PAGE_SIZE[name]) for n in lengths)
     assert total_pages_needed > session.num_blocks, "the scenario must need more pages than the pool has"
     assert session.cache.num_free_blocks == session.num_blocks
+    assert sum(len(requests) > 1 for requests in owners.values()) >= session.num_blocks // 2, \
+        "pages must have passed from finished requests to later ones"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
