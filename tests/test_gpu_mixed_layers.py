@@ -38,7 +38,8 @@ def _register():
 
     @registry.register_architecture("ToyMixedWindowDecoder")
     class ToyMixedWindowDecoder:
-        """Even layers attend to every key, odd layers to the last ``WINDOW`` positions."""
+        """Even layers attend to the last ``WINDOW`` positions, odd layers to every key (the windowed
+        kind comes first, so a plan wrongly shared would be the one with fewer keys)."""
 
         @staticmethod
         def layout(config):
@@ -46,7 +47,7 @@ def _register():
             for i in range(config.n_layers):
                 mixer = PagedAttention(config.d_model, config.n_heads, config.n_kv_heads, config.head_dim,
                                        RotaryEncoding(config.head_dim, config.rope_theta, config.max_seq_len),
-                                       window=WINDOW if i % 2 else None)
+                                       window=None if i % 2 else WINDOW)
                 block = PreNormBlock(RMSNorm(config.d_model, config.norm_eps), mixer,
                                      RMSNorm(config.d_model, config.norm_eps), SwiGLU(config.d_model, config.d_ff))
                 blocks.append(block)
@@ -70,9 +71,9 @@ def _tensors(dtype: str) -> dict[str, np.ndarray]:
             continue
         values = rng.standard_normal(spec.shape) * 0.05
         if name.endswith("qkv_proj"):
-            values[:, :(MIXED["n_heads"] + MIXED["n_kv_heads"]) * MIXED["head_dim"]] *= 3.0   # peaked softmax rows
+            values[:, :(MIXED["n_heads"] + MIXED["n_kv_heads"]) * MIXED["head_dim"]] *= 1.5   # peaked softmax rows
         if name == "embed":
-            values *= 4.0
+            values *= 2.0
         values = values.astype(np.float32)
         tensors[name] = plain_model.round_to_bfloat16(values) if dtype == "bfloat16" else values
     return tensors
@@ -90,7 +91,7 @@ def _plain(tensors, tokens):
         normed = plain_model.rms_norm(x, tensors[p + "mixer_norm.weight"], eps)
         q, k, v = plain_model.project_qkv(normed, tensors[p + "mixer.qkv_proj"], h, kv, hd)
         q, k = plain_model.apply_rope(q, pos, cos, sin), plain_model.apply_rope(k, pos, cos, sin)
-        attended = plain_model.causal_attention(q, k, v, 1 / math.sqrt(hd), window=WINDOW if i % 2 else None)
+        attended = plain_model.causal_attention(q, k, v, 1 / math.sqrt(hd), window=None if i % 2 else WINDOW)
         x = (x + attended.reshape(len(tokens), h * hd) @ tensors[p + "mixer.out_proj"]).astype(np.float32)
         normed = plain_model.rms_norm(x, tensors[p + "ff_norm.weight"], eps)
         x = (x + plain_model.swiglu(normed, tensors[p + "feed_forward.gate_proj"], tensors[p + "feed_forward.up_proj"],
@@ -122,7 +123,7 @@ def _wrong_window_gap(tensors, tokens) -> float:
 
 @pytest.mark.parametrize("flat", ["never", "always"])
 @pytest.mark.parametrize("graphs", [True, False])
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_global_and_windowed_layers_in_one_model(dtype, graphs, flat):
     from paged_kv_serving_b200.config import ModelConfig
     from paged_kv_serving_b200.engine.replay import ReplaySession
