@@ -28,3 +28,13 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    try:
+        import helpers
+    except Exception:  # pragma: no cover
+        return
+    if helpers.WORST_SHARE:
+        shares = ", ".join(f"{dtype} {share:.2f}" for dtype, share in sorted(helpers.WORST_SHARE.items()))
+        terminalreporter.write_line(f"largest logit gap as a share of its bound: {shares}")

@@ -73,15 +73,25 @@ def random_tokens(config: dict, count: int, seed: int) -> list[int]:
     return [int(t) for t in np.random.default_rng(seed).integers(0, config["vocab_size"], size=count)]
 
 
-def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what: str) -> None:
-    atol = F32_ATOL if dtype == "float32" else bf16_atol(want)
+#: The largest gap met so far as a share of its bound, per type (printed at the end of a run: it
+#: shows how much room the bounds leave).
+WORST_SHARE: dict[str, float] = {}
+
+
+def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what: str, atol: float | None = None) -> float:
+    """Raises when ``got`` misses ``want`` by more than the bound of ``dtype`` (or ``atol``);
+    returns the largest gap."""
+    if atol is None:
+        atol = F32_ATOL if dtype == "float32" else bf16_atol(want)
     gap = np.abs(got.astype(np.float64) - want.astype(np.float64))
     worst = float(gap.max())
+    WORST_SHARE[dtype] = max(WORST_SHARE.get(dtype, 0.0), worst / atol if atol > 0 else 0.0)
     if not worst <= atol:
         row, col = np.unravel_index(int(gap.argmax()), gap.shape)
         first_bad = int(np.argmax(gap.max(axis=-1) > atol))
         raise AssertionError(f"{what}: max |gap| {worst:.3e} > {atol:.3e} at row {row}, column {col}; "
                              f"first row beyond the bound: {first_bad}")
+    return worst
 
 
 def assert_greedy_tokens(config: dict, tensors: dict[str, np.ndarray], prompt, got, dtype: str, what: str) -> None:

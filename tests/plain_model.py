@@ -171,8 +171,10 @@ def config_sizes(config: dict) -> dict:
     return out
 
 
-def forward(config: dict, tensors: dict[str, np.ndarray], token_ids) -> np.ndarray:
-    """Logits ``(T, vocab)`` at every position of one whole sequence, recomputed from scratch.
+def forward(config: dict, tensors: dict[str, np.ndarray], token_ids, rows=None) -> np.ndarray:
+    """Logits ``(T, vocab)`` at every position of one whole sequence, recomputed from scratch
+    (with ``rows``, a list of positions, only those rows of the logits: the whole sequence still
+    runs through the layers, the head is applied where asked).
 
     Reference: src/paged_kv_serving/engine/model.py:269-288 (embed; per layer: pre-norm,
     fused QKV, RoPE on q and k, causal attention with scale ``1/sqrt(head_dim)``, output
@@ -201,6 +203,8 @@ def forward(config: dict, tensors: dict[str, np.ndarray], token_ids) -> np.ndarr
         normed = rms_norm(hidden, tensors[p + "ffn_norm"], eps)
         hidden = (hidden + swiglu(normed, tensors[p + "gate_proj"], tensors[p + "up_proj"], tensors[p + "down_proj"])).astype(F32)
     head = tensors["token_embedding"] if c["tie_embeddings"] else tensors["lm_head"]
+    if rows is not None:
+        hidden = hidden[np.asarray(rows, dtype=np.int64)]
     return lm_head(hidden, tensors["final_norm"], eps, head)
 
 
