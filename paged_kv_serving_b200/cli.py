@@ -18,11 +18,13 @@ __all__ = ["main"]
 
 
 def _model_config(args):
-    from paged_kv_serving_b200.config.model_config import ModelConfig
+    """The typed configuration of whatever architecture the file names (its own config class
+    where it has one), or a preset."""
+    from paged_kv_serving_b200.config import load_config
     from paged_kv_serving_b200.config.presets import preset
 
     if args.config is not None:
-        return ModelConfig.from_json_file(args.config)
+        return load_config(args.config)
     return preset(args.preset)
 
 
@@ -32,7 +34,7 @@ def _build_checkpoint(args) -> int:
 
     config = _model_config(args)
     manifest = write_random_model_folder(args.out, config, seed=args.seed, dtype=args.dtype, std=args.std)
-    print(json.dumps({"directory": str(args.out), "parameters": config.parameter_count,
+    print(json.dumps({"directory": str(args.out), "parameters": manifest["parameter_count"],
                       "vocab_size": config.vocab_size, "manifest_sha256": manifest_digest(manifest)}, indent=2))
     return 0
 

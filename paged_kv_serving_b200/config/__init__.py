@@ -27,8 +27,19 @@ def load_config(path):
     return config_class.from_dict(data)
 
 
+def write_config(config, path) -> None:
+    """Write a configuration (of any architecture: it offers ``to_dict``) as ``config.json``."""
+    import json
+    from pathlib import Path
+
+    path = Path(path)
+    if path.is_dir():
+        path = path / CONFIG_FILE
+    path.write_text(json.dumps(config.to_dict(), indent=2, sort_keys=True) + "\n", encoding="utf-8")
+
+
 __all__ = [
-    "load_config",
+    "load_config", "write_config",
     "CONFIG_FILE", "DTYPES", "EngineConfig", "ModelConfig", "architecture", "known_architectures",
     "known_parts", "part", "register_architecture", "register_part",
 ]

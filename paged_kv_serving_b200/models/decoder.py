@@ -45,6 +45,7 @@ class DecoderModel:
         specs = layout.tensor_specs()
         loader.check_tensors(specs, tensors)
         placed = {name: loader.place(tensors[name], spec, model.dtype, model.device) for name, spec in specs.items()}
+        loader.check_finite(placed)      # one pass on the device, after the cast to the compute type
         model.embedding = placed[layout.embedding_name].contiguous()
         model.head = placed[layout.head_name].contiguous() if layout.head_name else model.embedding
         per_part: dict[int, tuple[object, dict[str, torch.Tensor]]] = {}

@@ -48,6 +48,16 @@ class ModelLayout:
             specs[name] = part.param_specs()[local]
         return specs
 
+    def parameter_count(self) -> int:
+        """Number of parameters in the tensors of a model folder (a tied head counts once)."""
+        total = 0
+        for spec in self.tensor_specs().values():
+            count = 1
+            for size in spec.shape:
+                count *= int(size)
+            total += count
+        return total
+
     def cache_entries(self) -> list[tuple[int, object]]:
         """``(entry number, request)`` of every distinct cache entry of the run order."""
         seen: dict[int, object] = {}

@@ -18,7 +18,8 @@ from paged_kv_serving_b200.config.model_config import CONFIG_FILE, ModelConfig
 from paged_kv_serving_b200.parts.base import ParamSpec
 from paged_kv_serving_b200.weights import manifest as manifest_module
 
-__all__ = ["WEIGHTS_FILE", "WeightsError", "check_tensors", "place", "read_model_folder", "read_safetensors"]
+__all__ = ["WEIGHTS_FILE", "WeightsError", "check_finite", "check_tensors", "cross_check_manifest", "non_finite_tensors",
+           "place", "read_model_folder", "read_safetensors"]
 
 WEIGHTS_FILE = "model.safetensors"
 _FLOAT_TYPES = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
@@ -79,12 +80,58 @@ def read_model_folder(folder: str | Path, expect_manifest_sha256: str | None = N
     folder = Path(folder)
     if not folder.is_dir():
         raise FileNotFoundError(f"model folder {folder} does not exist")
+    manifest = None
     if (folder / manifest_module.MANIFEST_FILE).is_file() or expect_manifest_sha256 is not None:
-        manifest_module.verify_manifest(folder, (CONFIG_FILE, WEIGHTS_FILE), expect_manifest_sha256)
+        manifest = manifest_module.verify_manifest(folder, (CONFIG_FILE, WEIGHTS_FILE), expect_manifest_sha256)
     for name in (CONFIG_FILE, WEIGHTS_FILE):
         if not (folder / name).is_file():
             raise FileNotFoundError(f"model folder {folder} has no {name}")
     from paged_kv_serving_b200.config import load_config
 
     config = load_config(folder / CONFIG_FILE)
-    return config, read_safetensors(folder / WEIGHTS_FILE)
+    tensors = read_safetensors(folder / WEIGHTS_FILE)
+    if manifest is not None:
+        cross_check_manifest(manifest, config, tensors)
+    return config, tensors
+
+
+def cross_check_manifest(manifest: dict, config, tensors: dict[str, torch.Tensor]) -> None:
+    """What the manifest says about the model against what the folder holds: its
+    ``architecture`` must be the configuration that ``config.json`` gives (read through the same
+    typed class, so defaults compare equal), and its ``parameter_count`` must be both the number
+    of elements in the tensors found and the number the architecture's layout declares
+    (reference: src/paged_kv_serving/engine/weights.py:191-200)."""
+    from paged_kv_serving_b200.config import registry
+
+    recorded = manifest.get("architecture")
+    try:
+        same = isinstance(recorded, dict) and type(config).from_dict(recorded).to_dict() == config.to_dict()
+    except (TypeError, ValueError):
+        same = False
+    if not same:
+        raise manifest_module.ModelIntegrityError("the manifest's architecture is not the configuration in config.json")
+    found = sum(int(t.numel()) for t in tensors.values())
+    declared = registry.architecture(config.architecture).layout(config).parameter_count()
+    count = manifest.get("parameter_count")
+    if count != found or count != declared:
+        raise manifest_module.ModelIntegrityError(
+            f"parameter count mismatch: the manifest records {count}, the tensors hold {found}, "
+            f"the configuration declares {declared}")
+
+
+def non_finite_tensors(tensors: dict[str, torch.Tensor]) -> list[str]:
+    """Names of the floating-point tensors that hold a NaN or an infinite value. The flags are
+    gathered where the tensors live and read in one transfer."""
+    names = [name for name, t in tensors.items() if t.is_floating_point()]
+    if not names:
+        return []
+    flags = torch.stack([torch.isfinite(tensors[name]).all() for name in names])
+    return sorted(name for name, ok in zip(names, flags.cpu().tolist()) if not ok)
+
+
+def check_finite(tensors: dict[str, torch.Tensor]) -> None:
+    """Refuse weights with NaN or infinite values (reference: src/paged_kv_serving/engine/model.py:
+    103-128 validates every tensor as finite), in the same error form as the other tensor faults."""
+    bad = non_finite_tensors(tensors)
+    if bad:
+        raise WeightsError([], [], [f"{name}: holds NaN or infinite values" for name in bad])

@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from paged_kv_serving_b200.config import registry
-from paged_kv_serving_b200.config.model_config import CONFIG_FILE, ModelConfig
+from paged_kv_serving_b200.config.model_config import CONFIG_FILE
 from paged_kv_serving_b200.parts.base import ParamSpec
 from paged_kv_serving_b200.weights import manifest as manifest_module
 from paged_kv_serving_b200.weights.loader import WEIGHTS_FILE
@@ -70,20 +70,26 @@ def random_tensors_on_device(specs: dict[str, ParamSpec], seed: int, std: float,
     return out
 
 
-def write_model_folder(folder: str | Path, config: ModelConfig, tensors: dict[str, torch.Tensor]) -> dict:
-    """Write ``config.json``, ``model.safetensors`` and ``manifest.json``; returns the manifest."""
+def write_model_folder(folder: str | Path, config, tensors: dict[str, torch.Tensor]) -> dict:
+    """Write ``config.json``, ``model.safetensors`` and ``manifest.json``; returns the manifest.
+    ``config`` is the typed configuration of any registered architecture (it names its
+    architecture and offers ``to_dict``); the parameter count comes from the architecture's
+    layout, not from a formula of one model."""
     from safetensors.torch import save_file
+
+    from paged_kv_serving_b200.config import write_config
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    config.write_json(folder / CONFIG_FILE)
+    write_config(config, folder / CONFIG_FILE)
     save_file({name: tensor.detach().cpu().contiguous() for name, tensor in tensors.items()},
               str(folder / WEIGHTS_FILE))
-    return manifest_module.write_manifest(folder, config.to_dict(), config.parameter_count,
+    layout = registry.architecture(config.architecture).layout(config)
+    return manifest_module.write_manifest(folder, config.to_dict(), layout.parameter_count(),
                                           (CONFIG_FILE, WEIGHTS_FILE))
 
 
-def write_random_model_folder(folder: str | Path, config: ModelConfig, seed: int = 0, dtype: str = "bfloat16",
+def write_random_model_folder(folder: str | Path, config, seed: int = 0, dtype: str = "bfloat16",
                               std: float = 0.02, norm_jitter: float = 0.0) -> dict:
     """The random-weights mode: a model folder from a configuration and a seed."""
     torch_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]

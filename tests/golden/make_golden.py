@@ -16,7 +16,12 @@ logits of the reference's cache-free forward pass next to this script:
   public parts (``embed``, ``project_qkv``, ``dense_causal_attention``, ``feed_forward``), and
   only the last matrix product uses the separate head.
 
-``tests/test_plain_model.py`` recomputes both with the plain implementation and compares.
+* ``sampling.npy``: token ids that the reference's ``sample_token``
+  (src/paged_kv_serving/engine/sampling.py:56-74) returns for 2,000 seeded cases (vocabularies of
+  5 to 700, greedy and temperatures up to 2, nucleus masses of 0.05 to 1, ties in the logits),
+  each with a generator seeded by the case's number, so that the draw can be repeated.
+
+``tests/test_plain_model.py`` recomputes all three with the plain implementation and compares.
 The files are small (tens of kilobytes) and are committed with this script.
 """
 
@@ -53,8 +58,31 @@ def golden_inputs(name: str):
     return config, tensors, tokens
 
 
+SAMPLING_CASES = 2000
+
+
+def sampling_case(number: int):
+    """Logits, temperature, nucleus mass and the generator of one sampling case."""
+    rng = np.random.default_rng(10_000 + number)
+    vocab = int(rng.integers(5, 701))
+    logits = (rng.standard_normal(vocab) * rng.uniform(0.5, 4.0)).astype(np.float32)
+    if number % 5 == 0:                      # ties, also among the most probable tokens
+        logits = np.round(logits)
+    temperature = 0.0 if number % 7 == 0 else float(rng.uniform(0.05, 2.0))
+    top_p = 1.0 if number % 3 == 0 else float(rng.uniform(0.05, 1.0))
+    return logits, temperature, top_p, np.random.default_rng(number)
+
+
 def main(reference_src: str) -> None:
     sys.path.insert(0, reference_src)
+    from paged_kv_serving.engine.sampling import sample_token as reference_sample_token
+    from paged_kv_serving.engine.sequence import SamplingParams
+
+    ids = np.zeros(SAMPLING_CASES, dtype=np.int32)
+    for number in range(SAMPLING_CASES):
+        logits, temperature, top_p, generator = sampling_case(number)
+        ids[number] = reference_sample_token(logits, SamplingParams(temperature=temperature, top_p=top_p), generator)
+    np.save(HERE / "sampling.npy", ids)
     from paged_kv_serving.engine.config import ModelConfig
     from paged_kv_serving.engine.model import (
         LanguageModel, LayerWeights, TransformerWeights, dense_causal_attention, rms_norm,

@@ -167,3 +167,120 @@ def test_folder_written_from_given_tensors_round_trips(tmp_path):
     assert set(back) == set(tensors)
     assert all(torch.equal(back[k], tensors[k]) for k in tensors)
     assert np.isfinite(back["token_embedding"].numpy()).all()
+
+
+def test_weights_with_nan_or_infinite_values_are_refused():
+    """Reference: src/paged_kv_serving/engine/model.py:103-128 refuses non-finite tensors."""
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+    from paged_kv_serving_b200.weights import non_finite_tensors
+
+    c = _config("A")
+    specs = architecture("LlamaToyDecoder").layout(c).tensor_specs()
+    tensors = random_tensors(specs, 3)
+    assert non_finite_tensors(tensors) == []
+    DecoderModel.from_tensors(c, tensors, "float32", "cpu")           # finite weights load
+    tensors["layers.1.down_proj"][5, 7] = float("nan")
+    tensors["final_norm"][0] = float("inf")
+    assert non_finite_tensors(tensors) == ["final_norm", "layers.1.down_proj"]
+    with pytest.raises(WeightsError) as error:
+        DecoderModel.from_tensors(c, tensors, "float32", "cpu")
+    assert "final_norm: holds NaN or infinite values" in str(error.value)
+    assert "layers.1.down_proj: holds NaN or infinite values" in str(error.value)
+    # a value that is finite in float32 and overflows the compute type is caught after the cast
+    tensors = random_tensors(specs, 3)
+    tensors["layers.0.up_proj"][0, 0] = 3.4e38
+    DecoderModel.from_tensors(c, tensors, "float32", "cpu")
+    with pytest.raises(WeightsError, match="layers.0.up_proj"):
+        DecoderModel.from_tensors(c, tensors, "bfloat16", "cpu")
+
+
+def test_manifest_must_agree_with_the_configuration_and_the_tensors(tmp_path):
+    """Reference: src/paged_kv_serving/engine/weights.py:191-200 (parameter count and architecture
+    of the manifest against the model that was read)."""
+    from safetensors.torch import save_file
+
+    from paged_kv_serving_b200.weights.manifest import sha256_file
+
+    c = _config("B")
+    write_random_model_folder(tmp_path, c, seed=1, dtype="float32")
+    path = tmp_path / "manifest.json"
+    good = json.loads(path.read_text())
+    assert good["parameter_count"] == c.parameter_count and good["architecture"] == c.to_dict()
+    read_model_folder(tmp_path)
+    lying = json.loads(json.dumps(good))
+    lying["parameter_count"] += 1
+    path.write_text(json.dumps(lying))
+    with pytest.raises(ModelIntegrityError, match="parameter count mismatch"):
+        read_model_folder(tmp_path)
+    lying = json.loads(json.dumps(good))
+    lying["architecture"]["n_layers"] = 4
+    path.write_text(json.dumps(lying))
+    with pytest.raises(ModelIntegrityError, match="not the configuration"):
+        read_model_folder(tmp_path)
+    # defaults written out or left out describe the same configuration
+    same = json.loads(json.dumps(good))
+    del same["architecture"]["rope_theta"]
+    same["architecture"]["rope_theta"] = c.rope_theta
+    path.write_text(json.dumps(same))
+    read_model_folder(tmp_path)
+    # tensors that hold another number of parameters than the manifest records (digests in order)
+    _, tensors = read_model_folder(tmp_path)
+    tensors["stowaway"] = torch.zeros(3)
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    forged = json.loads(json.dumps(good))
+    for artifact in forged["artifacts"]:
+        artifact["sha256"] = sha256_file(tmp_path / artifact["name"])
+        artifact["size_bytes"] = (tmp_path / artifact["name"]).stat().st_size
+    path.write_text(json.dumps(forged))
+    with pytest.raises(ModelIntegrityError, match="parameter count mismatch"):
+        read_model_folder(tmp_path)
+
+
+def test_build_checkpoint_takes_an_architecture_with_a_configuration_class_of_its_own(tmp_path):
+    """The command line and the random-weights mode go through the architecture's own typed
+    configuration: a toy architecture registered here, whose config.json has a key the shared
+    class does not know, builds a model folder and reads back."""
+    from dataclasses import dataclass, fields
+
+    from paged_kv_serving_b200 import cli
+    from paged_kv_serving_b200.config import load_config, registry
+
+    if "ToyOwnConfigDecoder" not in known_architectures():
+        @dataclass(frozen=True)
+        class ToyConfig:
+            vocab_size: int
+            d_model: int
+            n_layers: int
+            n_heads: int
+            d_ff: int
+            max_seq_len: int
+            ff_widening: int = 1          # a key of this architecture alone
+            architecture: str = "ToyOwnConfigDecoder"
+
+            def to_dict(self):
+                return {f.name: getattr(self, f.name) for f in fields(self)}
+
+            @classmethod
+            def from_dict(cls, data):
+                return cls(**data)
+
+        @registry.register_architecture("ToyOwnConfigDecoder")
+        class ToyOwnConfigDecoder:
+            config_class = ToyConfig
+
+            @staticmethod
+            def layout(config):
+                shared = ModelConfig(vocab_size=config.vocab_size, d_model=config.d_model, n_layers=config.n_layers,
+                                     n_heads=config.n_heads, d_ff=config.d_ff * config.ff_widening,
+                                     max_seq_len=config.max_seq_len)
+                return architecture("LlamaToyDecoder").layout(shared)
+
+    source = tmp_path / "toy.json"
+    source.write_text(json.dumps({"architecture": "ToyOwnConfigDecoder", "vocab_size": 50, "d_model": 32, "n_layers": 1,
+                                  "n_heads": 2, "d_ff": 24, "max_seq_len": 64, "ff_widening": 2}))
+    out = tmp_path / "folder"
+    assert cli.main(["build-checkpoint", "--out", str(out), "--config", str(source), "--seed", "3", "--dtype", "float32"]) == 0
+    config, tensors = read_model_folder(out)
+    assert type(config).__name__ == "ToyConfig" and config.ff_widening == 2 and load_config(out) == config
+    assert tensors["layers.0.gate_proj"].shape == (32, 48)
+    assert json.loads((out / "manifest.json").read_text())["parameter_count"] == sum(t.numel() for t in tensors.values())

@@ -23,6 +23,23 @@ def test_plain_forward_matches_reference_golden(name):
     assert np.abs(got - want).max() <= 1e-5
 
 
+def test_plain_sampler_matches_reference_golden():
+    """2,000 seeded cases whose token ids the reference's own ``sample_token`` produced
+    (src/paged_kv_serving/engine/sampling.py:56-74): greedy, temperature, nucleus, ties."""
+    want = np.load(GOLDEN / "sampling.npy")
+    assert want.shape == (make_golden.SAMPLING_CASES,)
+    sampled = 0
+    for number in range(make_golden.SAMPLING_CASES):
+        logits, temperature, top_p, generator = make_golden.sampling_case(number)
+        if temperature < plain_model.GREEDY_TEMPERATURE:
+            got = plain_model.greedy_token(logits)          # a greedy token draws no number
+        else:
+            got = plain_model.sample_token(logits, temperature, top_p, float(generator.random()))
+            sampled += 1
+        assert got == int(want[number]), f"case {number}"
+    assert sampled > 1500
+
+
 def test_forward_is_causal():
     config, tensors, tokens = make_golden.golden_inputs("gqa_untied")
     full = plain_model.forward(config, tensors, tokens)
