@@ -8,19 +8,20 @@ in the cache, decode one token per step. A "step" is one decode step of the whol
 line is printed with
 
 * ``value``      decoded tokens a second, timed on the device with CUDA events over K steps;
-                 each step runs the model and samples, the ids stay on the device and the host
-                 prepares step k + 1 while the GPU runs step k (synchronised before and after the K steps)
+                 each step runs the model and samples, the sampled ids enter the next step on the
+                 device, and the host prepares step k + 1 while the GPU runs step k (synchronised
+                 before and after the K steps)
 * ``e2e``        the same through the Python entry point (``Engine.step``): host token ids in,
                  sampled ids read back every step, with the host-to-device and device-to-host
-                 bytes of a step
+                 bytes of a step and the roofline fraction that its time amounts to
 * ``prefill``    one 2,048-token prompt in one step: tokens a second, milliseconds and the
                  fraction of the bfloat16 matrix peak its flops reach
 * ``roofline``   the bytes a decode step must read (every weight once, the cache of the live
                  requests) over its time, against the measured copy bandwidth
 * ``points``     decode tokens a second at batch 1 and 64
 
-Peaks come from ``MEASURED_PEAKS.json`` beside this file when it exists, else from the fallback
-figures of this pool. Weights of a step (16 GB) are far larger than L2, so nothing is flushed
+Peaks come from ``MEASURED_PEAKS.json`` beside this file when it exists, else from fallback
+figures (6.65 TB/s, 1.59 PFLOP/s). Weights of a step (16 GB) are far larger than L2, so nothing is flushed
 between steps. With ``--gpus`` above 1 the program says that it measures one GPU only and exits 2.
 """
 
@@ -38,7 +39,7 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-METRIC = "decode tok/s at batch 8, Llama-3-8B shape, 1024-token prompts"
+METRIC = "decode tok/s at batch {batch}, {model} shape, {prompt}-token prompts"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -183,15 +184,21 @@ def run(args) -> dict:
 
     def decode(num_seqs: int, warmup: int, steps: int, offset: int):
         """``steps`` decode steps of the first ``num_seqs`` sequences; returns (ms, launches)."""
+        feedback = {f"s{i}": i for i in range(num_seqs)}
+        fed = [None]        # the first step of a run takes its tokens from the host, the others feed back
+
         def one(k):
             position = prompt_len + offset + k
             entries = tuple(BatchEntry(f"s{i}", (int(prompts[i, position]),), position, (tables[i],), (0,))
                             for i in range(num_seqs))
-            result = runner.step(ExecutionBatch(entries))
-            # sampled on the device and left there: between the synchronisations around the timed
-            # steps the host prepares step k + 1 while the GPU runs step k (the end-to-end number
-            # below reads every step's tokens back)
-            sampler.sample_on_device(result.logits, [greedy] * num_seqs, [None] * num_seqs)
+            result = runner.step(ExecutionBatch(entries), feedback=fed[0])
+            # sampled on the device into the buffer that the next step's embedding lookup reads:
+            # every step runs the tokens the step before it sampled, and between the
+            # synchronisations around the timed steps the host prepares step k + 1 while the GPU
+            # runs step k (the end-to-end number below also reads every step's tokens back)
+            sampler.sample_on_device(result.logits, [greedy] * num_seqs, [None] * num_seqs, out=runner.sampled_ids)
+            runner.prepare_next()
+            fed[0] = feedback
         for k in range(warmup):
             one(k)
         before = ops.launch_count()
@@ -244,11 +251,13 @@ def run(args) -> dict:
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - started
     clocks.stop()
+    e2e_ms = 1e3 * elapsed / args.steps
     e2e = {"value": produced / elapsed, "unit": "tok/s", "h2d_bytes_per_step": h2d // args.steps,
-           "d2h_bytes_per_step": d2h // args.steps, "ms_per_step": 1e3 * elapsed / args.steps}
+           "d2h_bytes_per_step": d2h // args.steps, "ms_per_step": e2e_ms,
+           "roofline_frac": step_bytes / (e2e_ms / 1e3) / 1e9 / peaks["hbm_gbs"]}
 
     return {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC.format(batch=batch, model=args.model, prompt=prompt_len), "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, random N(0, 0.02) weights", "impl": "ours",
         "config": {
@@ -257,7 +266,7 @@ def run(args) -> dict:
             "d_ff": config.d_ff, "vocab_size": config.vocab_size, "global_batch": batch, "seq_len": prompt_len,
             "kv_block_size": block, "prefill_tokens": args.prefill_tokens, "parallelism": "single-gpu",
             "l2": "weights read each step (GBs) exceed L2; no flush", "peaks": peaks["source"],
-            "value_timing": "K steps back to back between two synchronisations; e2e reads tokens back every step",
+            "value_timing": "K steps back to back, sampled ids fed to the next step on the device; e2e also reads them back",
         },
         "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
         "clocks": clocks.summary(),

@@ -165,7 +165,10 @@ class KVCacheManager:
         """Offer every page that the computed tokens now fill completely to the prefix cache."""
         if not self.prefix_cache.enabled:
             return 0
-        complete = sequence.num_computed_tokens // self.block_size
+        # only pages whose tokens are all final: ids sampled on the device and not read back yet
+        # stand at the end of the sequence's tokens and cannot be hashed
+        known = sequence.num_tokens - getattr(sequence, "num_unsettled_tokens", 0)
+        complete = min(sequence.num_computed_tokens, known) // self.block_size
         scope = self.prefix_cache.scope_bytes(sequence.request.key_id)
         accepted = 0
         while len(sequence.block_hashes) < complete:

@@ -13,14 +13,22 @@ namespace pkv {
 
 // ---------------------------------------------------------------------------------------------
 // embedding gather: out[t, :] = table[ids[t], :] widened to float32
+// With `fed_back` and `fed_back_at`, token t whose fed_back_at[t] >= 0 takes its id from
+// fed_back[fed_back_at[t]] instead: the id that the sampler of the step before left on the device,
+// so that a decoded token can enter the next step without passing through the host.
 // ---------------------------------------------------------------------------------------------
 template <typename W>
 __global__ void embedding_gather_kernel(const W* __restrict__ table, const int32_t* __restrict__ ids,
-                                        float* __restrict__ out, int d, int vocab, int* __restrict__ status) {
+                                        float* __restrict__ out, int d, int vocab, int* __restrict__ status,
+                                        const int32_t* __restrict__ fed_back, const int32_t* __restrict__ fed_back_at) {
   dependents_may_launch();
   wait_for_prior_kernels();
   const int t = blockIdx.x;
   int id = ids[t];
+  if (fed_back_at != nullptr) {
+    const int at = fed_back_at[t];
+    if (at >= 0) id = fed_back[at];
+  }
   if (id < 0 || id >= vocab) {  // never read outside the table: record and use row 0
     if (threadIdx.x == 0) atomicExch(status, 1);
     id = 0;
@@ -326,7 +334,8 @@ __global__ void rope_kv_store_vec_kernel(A* __restrict__ qkv, const int32_t* __r
 using namespace pkv;
 
 PKV_EXPORT int pkv_embedding_gather(const void* table, int table_dtype, const int32_t* ids, float* out,
-                                    int n_tokens, int d, int vocab, int* status, void* stream) {
+                                    int n_tokens, int d, int vocab, int* status, const int32_t* fed_back,
+                                    const int32_t* fed_back_at, void* stream) {
   if (n_tokens <= 0) return 0;
   if (d <= 0 || vocab <= 0) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
@@ -334,10 +343,10 @@ PKV_EXPORT int pkv_embedding_gather(const void* table, int table_dtype, const in
   // the first kernel of a step follows a copy from the host, not a kernel: an ordinary launch
   if (table_dtype == PKV_F32)
     return launch_kernel(embedding_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, false, 0,
-                         (const float*)table, ids, out, d, vocab, status);
+                         (const float*)table, ids, out, d, vocab, status, fed_back, fed_back_at);
   if (table_dtype == PKV_BF16)
     return launch_kernel(embedding_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, false, 0,
-                         (const bf16*)table, ids, out, d, vocab, status);
+                         (const bf16*)table, ids, out, d, vocab, status, fed_back, fed_back_at);
   return PKV_ERR_DTYPE;
 }
 

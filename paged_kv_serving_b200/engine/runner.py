@@ -13,6 +13,7 @@ copy-on-write and state-slot copies act on (reference: src/paged_kv_serving/engi
 
 from __future__ import annotations
 
+import gc
 import hashlib
 from dataclasses import dataclass
 
@@ -137,6 +138,10 @@ class ModelRunner:
             else:
                 self.bindings.append(CacheBinding(call.cache, state=self.storage.state_index[call.cache], write=call.write))
         self._status = ops.status_word(model.device)
+        # Where a sampler leaves the ids of a step (and, behind them, the status word) so that the
+        # next step's embedding lookup can read a decoded token without a trip through the host.
+        # Its address is fixed: captured graphs read it.
+        self.sampled_ids = torch.zeros((max(1, max_running_seqs) + 1,), dtype=torch.int32, device=model.device)
         self.steps_run = 0
         self.use_graphs = use_graphs
         self._graph_safe = all(block.graph_safe for block in model.layout.blocks) and model.layout.final_norm.graph_safe
@@ -192,11 +197,26 @@ class ModelRunner:
             if self.state_entries and entry.state_slot is None:
                 raise ValueError(f"sequence {entry.seq_id}: the model keeps per-request state but no slot was given")
 
-    def _context(self, batch: ExecutionBatch, table_width: int | None = None,
-                 pad_to: int | None = None) -> tuple[StepContext, list[tuple[str, int]]]:
+    def _feedback_array(self, entries, feedback: dict[str, int] | None, starts) -> np.ndarray:
+        """Per token -1, or (for a one-token entry named in ``feedback``) the place of its id in
+        ``sampled_ids``."""
+        array = np.full(int(starts[-1]), -1, dtype=np.int32)
+        if feedback:
+            for e, start in zip(entries, starts[:-1]):
+                place = feedback.get(e.seq_id) if e.num_tokens == 1 else None
+                if place is not None:
+                    if not 0 <= place < self.sampled_ids.numel() - 1:
+                        raise ValueError(f"sequence {e.seq_id}: fed-back id outside the sampler's buffer")
+                    array[int(start)] = place
+        return array
+
+    def _context(self, batch: ExecutionBatch, table_width: int | None = None, pad_to: int | None = None,
+                 feedback: dict[str, int] | None = None) -> tuple[StepContext, list[tuple[str, int]]]:
         """Flatten a batch into the step's integer arrays. ``pad_to`` appends stand-in entries of
         one token (no page, no store, token 0) up to that many entries and ``table_width`` fixes
-        the width of the block tables, so that a captured graph keeps its shapes."""
+        the width of the block tables, so that a captured graph keeps its shapes. ``feedback``
+        maps sequence ids of one-token entries to the place in ``sampled_ids`` where the token's
+        id lies (the entry's own ``token_ids`` is then a stand-in)."""
         entries = batch.entries
         if pad_to is not None and len(entries) < pad_to:
             filler = BatchEntry("", (0,), 0, tuple((NULL_PAGE,) for _ in self.groups), (0,), 0)
@@ -211,6 +231,7 @@ class ModelRunner:
         seq_of_token = np.repeat(np.arange(len(entries)), lens)
         positions = np.arange(total, dtype=np.int64) - starts[seq_of_token] + first[seq_of_token]
         arena.add(StepContext.TOKEN_IDS, tokens)
+        arena.add(StepContext.TOKEN_FEEDBACK, self._feedback_array(entries, feedback, starts))
         arena.add(StepContext.POSITIONS, positions)
         arena.add(StepContext.SEQ_STARTS, starts)
         arena.add(StepContext.FIRST_POS, first)
@@ -253,7 +274,8 @@ class ModelRunner:
         """The kernels of one step, launched on the current stream; nothing here reads device
         data on the host, so the whole sequence can be captured in a CUDA graph."""
         model = self.model
-        hidden = ops.embedding_gather(model.embedding, ctx.ints(StepContext.TOKEN_IDS), self._status)
+        hidden = ops.embedding_gather(model.embedding, ctx.ints(StepContext.TOKEN_IDS), self._status,
+                                      self.sampled_ids, ctx.ints(StepContext.TOKEN_FEEDBACK))
         blocks = model.layout.blocks
         delta = None
         for i, (call, binding) in enumerate(zip(self.order, self.bindings)):
@@ -269,12 +291,17 @@ class ModelRunner:
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
         return gemm.linear(normed, model.head, out_dtype=torch.float32, chain=True)
 
-    def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None) -> StepResult:
+    def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None,
+             feedback: dict[str, int] | None = None) -> StepResult:
         """Run one batch: writes the cache for every token given, returns logits where wanted.
 
         A batch of single decoded tokens (every entry one token whose logits are wanted) replays
         a CUDA graph captured for its size class; the logits tensor of such a step is reused by
         the next one, so the caller reads it before stepping again.
+
+        ``feedback``: sequence id -> place in ``sampled_ids``, for one-token entries whose token
+        was sampled by the step before and has not left the device: the embedding lookup reads
+        the id there (the entry's ``token_ids`` is a stand-in and is not looked at).
         """
         if not batch.entries:
             return StepResult(None, [], 0, 0)
@@ -283,8 +310,8 @@ class ModelRunner:
         self._last_graph_step = None
         if self.use_graphs and self._graph_safe and not clear_state_slots and \
                 all(e.num_tokens == 1 and e.logits_at == (0,) for e in batch.entries):
-            return self._step_graph(batch)
-        ctx, rows = self._context(batch)
+            return self._step_graph(batch, feedback)
+        ctx, rows = self._context(batch, feedback=feedback)
         self._plan(ctx)
         ctx.arena.upload(self.model.device)
         if clear_state_slots:
@@ -297,7 +324,7 @@ class ModelRunner:
     GRAPH_BATCH_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     GRAPH_TABLE_STEP = 32     # block tables of a graph are this many pages wide, or a multiple
 
-    def _step_graph(self, batch: ExecutionBatch) -> StepResult:
+    def _step_graph(self, batch: ExecutionBatch, feedback: dict[str, int] | None = None) -> StepResult:
         count = len(batch.entries)
         size = next((b for b in self.GRAPH_BATCH_SIZES if b >= count), None)
         if size is None:
@@ -311,8 +338,10 @@ class ModelRunner:
             ctx, rows = ahead["ctx"], ahead["rows"]
             tokens = [e.token_ids[0] for e in batch.entries] + [0] * (size - count)
             ctx.arena.patch(StepContext.TOKEN_IDS, tokens)
+            places = [(feedback or {}).get(e.seq_id, -1) for e in batch.entries] + [-1] * (size - count)
+            ctx.arena.patch(StepContext.TOKEN_FEEDBACK, places)
         else:
-            ctx, rows = self._context(batch, table_width=width, pad_to=size)
+            ctx, rows = self._context(batch, table_width=width, pad_to=size, feedback=feedback)
             ctx.planning_context_len = width * self.block_size
             self._plan(ctx)
         self._last_graph_step = (batch, key)
@@ -332,8 +361,18 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         ctx.scratch = {k: v for k, v in ctx.scratch.items() if not isinstance(v, torch.Tensor)}
         before = ops.launch_count()
-        with torch.cuda.graph(graph, pool=self._graph_pool):
-            captured = self._forward(ctx, True)
+        # The cyclic garbage collector stays off while the capture runs: were it to free, in the
+        # middle of it, an object that owns CUDA resources (the graphs and memory pool of a runner
+        # that died in a reference cycle), the driver would refuse the call during capture and the
+        # capture would be void. (Entering the capture collects garbage first.)
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                captured = self._forward(ctx, True)
+        finally:
+            if collecting:
+                gc.enable()
         launches = ops.launch_count() - before
         ops.LAUNCHES["count"] = before                     # a capture records launches, it runs none
         self._graphs[key] = {"graph": graph, "ints": ints, "logits": captured, "signature": ctx.arena.signature(),

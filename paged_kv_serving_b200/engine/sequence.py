@@ -12,6 +12,7 @@ Names and defaults of ``SamplingParams`` and ``Request`` are the reference's
 from __future__ import annotations
 
 import itertools
+import math
 from dataclasses import dataclass, field
 from enum import Enum
 
@@ -65,6 +66,9 @@ class FinishReason(Enum):
 
 @dataclass(frozen=True, slots=True)
 class SamplingParams:
+    """How a request's tokens are chosen; the field names and defaults are the reference's
+    (src/paged_kv_serving/engine/sequence.py:64-87)."""
+
     max_new_tokens: int = 32
     temperature: float = 0.0
     top_p: float = 1.0
@@ -72,14 +76,17 @@ class SamplingParams:
     ignore_eos: bool = False
 
     def __post_init__(self) -> None:
+        problems = []
         if self.max_new_tokens < 1:
-            raise ValueError("max_new_tokens must be >= 1")
+            problems.append(f"max_new_tokens is {self.max_new_tokens}: a request generates one token or more")
         if self.temperature < 0.0:
-            raise ValueError("temperature must be >= 0")
+            problems.append(f"temperature is {self.temperature}: it cannot be negative (0 decodes greedily)")
         if not 0.0 < self.top_p <= 1.0:
-            raise ValueError("top_p must be in (0, 1]")
+            problems.append(f"top_p is {self.top_p}: the nucleus mass lies in (0, 1]")
         if self.seed < 0:
-            raise ValueError("seed must be >= 0")
+            problems.append(f"seed is {self.seed}: seeds are non-negative integers")
+        if problems:
+            raise ValueError("; ".join(problems))
 
     @property
     def greedy(self) -> bool:
@@ -88,7 +95,8 @@ class SamplingParams:
 
 @dataclass(frozen=True, slots=True)
 class Request:
-    """A submitted request; its ``n`` samples share the prompt's pages."""
+    """A submitted request; its ``n`` samples share the prompt's pages
+    (fields as in the reference, src/paged_kv_serving/engine/sequence.py:90-126)."""
 
     request_id: str
     prompt_token_ids: tuple[int, ...]
@@ -100,12 +108,12 @@ class Request:
     arrival_time: float = 0.0
 
     def __post_init__(self) -> None:
-        if not self.prompt_token_ids:
-            raise ValueError("the prompt must contain at least one token")
+        if len(self.prompt_token_ids) == 0:
+            raise ValueError(f"request {self.request_id}: an empty prompt has no position to predict from")
         if self.n < 1:
-            raise ValueError("n must be >= 1")
-        if self.deadline_seconds is not None and self.deadline_seconds <= 0:
-            raise ValueError("deadline_seconds must be > 0")
+            raise ValueError(f"request {self.request_id}: n is {self.n}, at least one sample is generated")
+        if self.deadline_seconds is not None and not self.deadline_seconds > 0:
+            raise ValueError(f"request {self.request_id}: a deadline lies after the arrival (deadline_seconds > 0)")
 
     @property
     def prompt_len(self) -> int:
@@ -141,21 +149,19 @@ class Sequence:
     finish_time: float | None = None
     admission_order: int = field(default_factory=lambda: next(_ORDER))
     rng: np.random.Generator | None = None
+    #: Tokens at the end of ``token_ids`` that stand in for ids sampled on the device and not
+    #: read back yet (the engine's overlapped steps); their values mean nothing until settled.
+    num_unsettled_tokens: int = 0
 
     @classmethod
     def from_request(cls, request: Request, sample_index: int, num_groups: int = 1) -> "Sequence":
-        sequence = cls(
-            seq_id=new_sequence_id(request.request_id, sample_index),
-            request=request,
-            sample_index=sample_index,
-            token_ids=list(request.prompt_token_ids),
-            block_tables=[[] for _ in range(max(1, num_groups))],
-        )
-        # One generator per sample: output depends on (seed, sample index) only
-        # (reference: src/paged_kv_serving/engine/sequence.py:165-170).
-        sequence.rng = np.random.default_rng(
-            np.random.SeedSequence(entropy=request.sampling.seed, spawn_key=(sample_index,)))
-        return sequence
+        """Sample ``sample_index`` of ``request``, with nothing computed and nothing held. Its
+        generator is seeded by (the request's seed, the sample's index) alone, so what it draws
+        depends on nothing else (reference: src/paged_kv_serving/engine/sequence.py:165-170)."""
+        seed = np.random.SeedSequence(entropy=request.sampling.seed, spawn_key=(sample_index,))
+        return cls(seq_id=new_sequence_id(request.request_id, sample_index), request=request,
+                   sample_index=sample_index, token_ids=[int(t) for t in request.prompt_token_ids],
+                   block_tables=[[] for _ in range(max(1, num_groups))], rng=np.random.default_rng(seed))
 
     # --- lengths -------------------------------------------------------------------------
 
@@ -167,6 +173,11 @@ class Sequence:
     @property
     def num_tokens(self) -> int:
         return len(self.token_ids)
+
+    @property
+    def num_settled_tokens(self) -> int:
+        """Leading tokens whose ids are final."""
+        return len(self.token_ids) - self.num_unsettled_tokens
 
     @property
     def num_output_tokens(self) -> int:
@@ -198,38 +209,41 @@ class Sequence:
         self.token_ids.append(int(token_id))
 
     def reset_for_recompute(self) -> None:
-        """Forget what is cached; sampled tokens stay and are recomputed with the prompt
-        (reference: src/paged_kv_serving/engine/sequence.py:210-221)."""
-        self.num_computed_tokens = 0
-        for table in self.block_tables:
-            table.clear()
-        self.block_hashes.clear()
-        self.cached_prefix_blocks = 0
+        """After preemption: the cache holds nothing of this sequence any more. Its tokens, the
+        sampled ones included, all stay and will be run again like a prompt, which draws no random
+        number (reference: src/paged_kv_serving/engine/sequence.py:210-221)."""
         self.status = SequenceStatus.PREEMPTED
         self.preemption_count += 1
+        self.num_computed_tokens = self.cached_prefix_blocks = 0
+        self.block_hashes = []
+        self.block_tables = [[] for _ in self.block_tables]
 
     def finish(self, reason: FinishReason, now: float) -> None:
-        self.status = SequenceStatus.ABORTED if reason is FinishReason.ABORTED else SequenceStatus.FINISHED
-        self.finish_reason = reason
-        self.finish_time = now
+        aborted = reason is FinishReason.ABORTED
+        self.finish_reason, self.finish_time = reason, now
+        self.status = SequenceStatus.ABORTED if aborted else SequenceStatus.FINISHED
 
     def priority_key(self) -> tuple[int, float, int]:
-        """Class, then earliest deadline, then arrival
-        (reference: src/paged_kv_serving/engine/sequence.py:230-241)."""
-        deadline = self.request.deadline
-        return (self.request.slo_class.rank, float("inf") if deadline is None else deadline, self.admission_order)
+        """Sort key of the scheduler: service class first, then the earlier deadline (none sorts
+        last), then the order of admission (reference: src/paged_kv_serving/engine/sequence.py:230-241)."""
+        request = self.request
+        return (request.slo_class.rank, math.inf if request.deadline is None else request.deadline, self.admission_order)
 
 
-def finish_reason_for(sequence: Sequence, token: int, *, eos_token_id: int | None,
-                      max_context_tokens: int) -> FinishReason | None:
-    """Why a sequence is done after sampling ``token``, or ``None``
-    (reference: src/paged_kv_serving/engine/sequence.py:244-262; a stop token wins over the
-    length cap, the context cap is checked last)."""
+def finish_reason_for(sequence: Sequence, token: int | None, *, eos_token_id: int | None, max_context_tokens: int,
+                      num_output_tokens: int | None = None) -> FinishReason | None:
+    """Why a sequence is done once it has ``num_output_tokens`` sampled tokens (default: all it
+    holds now), the newest being ``token``; ``None`` if it goes on. A stop token counts before the
+    caps, the cap on new tokens before the cap on the context
+    (reference: src/paged_kv_serving/engine/sequence.py:244-262). With ``token=None`` only the
+    caps are looked at: whether the sequence is complete whatever its newest token is."""
     sampling = sequence.request.sampling
-    if eos_token_id is not None and token == eos_token_id and not sampling.ignore_eos:
+    produced = sequence.num_output_tokens if num_output_tokens is None else num_output_tokens
+    stops = token is not None and eos_token_id is not None and not sampling.ignore_eos and token == eos_token_id
+    if stops:
         return FinishReason.STOP
-    if sequence.num_output_tokens >= sampling.max_new_tokens:
+    if produced >= sampling.max_new_tokens:
         return FinishReason.LENGTH
-    if sequence.num_tokens >= max_context_tokens:
+    if sequence.request.prompt_len + produced >= max_context_tokens:
         return FinishReason.CONTEXT_LIMIT
     return None

@@ -94,15 +94,24 @@ def _fn(lib_name: str, fn_name: str, argtypes: list):
 # ---------------------------------------------------------------------------------------------
 
 
-def embedding_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
-    """``table[ids]`` widened to float32. An id outside the table sets ``status[0]`` to 1."""
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
+                     fed_back: torch.Tensor | None = None, fed_back_at: torch.Tensor | None = None) -> torch.Tensor:
+    """``table[ids]`` widened to float32. An id outside the table sets ``status[0]`` to 1.
+    With ``fed_back`` (int32 ids on the device) and ``fed_back_at`` (one int32 per token), a token
+    whose ``fed_back_at`` is not negative takes ``fed_back[fed_back_at]`` as its id."""
     _need(table, None, "table"); _need(ids, torch.int32, "ids"); _need(status, torch.int32, "status")
+    if (fed_back is None) != (fed_back_at is None):
+        raise ValueError("fed_back and fed_back_at go together")
+    if fed_back is not None:
+        _need(fed_back, torch.int32, "fed_back"); _need(fed_back_at, torch.int32, "fed_back_at")
+        if fed_back_at.numel() != ids.numel():
+            raise ValueError("fed_back_at needs one element per token")
     vocab, d = table.shape
     out = torch.empty((ids.numel(), d), dtype=torch.float32, device=table.device)
     fn = _fn("elementwise", "pkv_embedding_gather",
-             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), ids.numel(), d, vocab,
-              _ptr(status), _stream()), "embedding_gather")
+              _ptr(status), _ptr(fed_back), _ptr(fed_back_at), _stream()), "embedding_gather")
     return out
 
 
@@ -690,10 +699,12 @@ def finish_norm(xw: torch.Tensor, sumsq: torch.Tensor, eps: float) -> torch.Tens
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
-           greedy_below: float, probs: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+           greedy_below: float, probs: torch.Tensor | None = None, status: torch.Tensor | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
     """One token id per row of ``logits [R, V]`` (float32); ``uniform`` is float64, one per row.
     With ``status`` (the device's status word) the result has ``R + 1`` elements and the last is
-    the word's value after every earlier kernel on the stream has finished."""
+    the word's value after every earlier kernel on the stream has finished. ``out`` (int32, at
+    least that many elements) receives the result in place of a fresh tensor."""
     _need(logits, torch.float32, "logits"); _need(temperature, torch.float32, "temperature")
     _need(top_p, torch.float32, "top_p"); _need(uniform, torch.float64, "uniform")
     rows, vocab = logits.shape
@@ -705,7 +716,14 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
             raise ValueError("probs scratch is smaller than the logits")
     if status is not None:
         _need(status, torch.int32, "status")
-    out = torch.empty((rows + (status is not None),), dtype=torch.int32, device=logits.device)
+    count = rows + (status is not None)
+    if out is None:
+        out = torch.empty((count,), dtype=torch.int32, device=logits.device)
+    else:
+        _need(out, torch.int32, "out")
+        if out.numel() < count:
+            raise ValueError("the output buffer is smaller than the rows to sample")
+        out = out[:count]
     fn = _fn("sampling", "pkv_sample",
              [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
               c_void_p])

@@ -241,6 +241,7 @@ class StepContext:
     CONTEXT_LENS = "context_lens"
     STATE_SLOTS = "state_slots"
     LOGITS_ROWS = "logits_rows"
+    TOKEN_FEEDBACK = "token_feedback"   # per token: -1, or the place of its id in the sampler's output buffer
 
     def ints(self, name: str) -> torch.Tensor:
         return self.arena[name]

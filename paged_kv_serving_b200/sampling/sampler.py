@@ -32,10 +32,12 @@ class Sampler:
         return [int(t) for t in self.sample_on_device(logits, params, generators).cpu().tolist()]
 
     def sample_on_device(self, logits: torch.Tensor, params: list[SamplingParams],
-                         generators: list[np.random.Generator], status: torch.Tensor | None = None) -> torch.Tensor:
+                         generators: list[np.random.Generator], status: torch.Tensor | None = None,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
         """The same ids as an int32 tensor on the device: nothing waits for the GPU. With
         ``status`` (the device's status word) one more element follows the ids: the word's value
-        once the step's kernels have finished, so that one copy brings back ids and faults."""
+        once the step's kernels have finished, so that one copy brings back ids and faults. ``out``
+        (an int32 device buffer) receives the ids where the next step's embedding lookup can read them."""
         rows, vocab = logits.shape
         if rows != len(params) or rows != len(generators):
             raise ValueError("one SamplingParams and one generator per logits row are required")
@@ -62,4 +64,4 @@ class Sampler:
             top_p = dev[rows * 12:].view(torch.float32)
         if self._probs is None or self._probs.numel() < rows * vocab:
             self._probs = torch.empty((rows * vocab,), dtype=torch.float32, device=self.device)
-        return ops.sample(logits, temperature, top_p, uniform, GREEDY_TEMPERATURE, self._probs, status)
+        return ops.sample(logits, temperature, top_p, uniform, GREEDY_TEMPERATURE, self._probs, status, out)

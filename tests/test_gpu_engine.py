@@ -126,6 +126,52 @@ def test_generation_is_the_same_cramped_and_roomy_and_hits_the_prefix_cache(tmp_
         assert roomy_tokens[i] == want, f"request {i}"
 
 
+def test_overlapped_steps_give_the_tokens_of_steps_in_order():
+    """Launching step k before step k-1 is settled changes when the host learns a token, not the
+    token: the same requests (greedy and sampled, 1 to 3 samples each, a stop token that ends
+    some of them early, a pool so small that sequences are preempted, shared prefixes) give the
+    same outputs, finish reasons and counts both ways, and the pool is whole afterwards. In
+    float32, where a recomputed sequence's logits do not depend on which kernels recomputed them
+    beyond 1e-6 (the two ways preempt at different moments); the bfloat16 logits of overlapped
+    steps are compared row by row in test_gpu_engine_equivalence.py."""
+    dtype = "float32"
+    from paged_kv_serving_b200.config import EngineConfig
+    from paged_kv_serving_b200.engine.engine import Engine
+    from paged_kv_serving_b200.engine.sequence import FinishReason, Request, SamplingParams
+
+    config = helpers.TINY_D
+    model = helpers.build_model(config, helpers.tensors_for("D", dtype), dtype)
+    rng = np.random.default_rng(12)
+    shared = [int(t) for t in rng.integers(0, config["vocab_size"], size=32)]
+    prompts = [shared + [int(t) for t in rng.integers(0, config["vocab_size"], size=n)] for n in (3, 40, 9, 70, 1, 25)]
+
+    def run(overlap, eos):
+        engine = Engine(model, EngineConfig(block_size=16, num_blocks=10, max_batched_tokens=48, max_running_seqs=6,
+                                            max_prompt_tokens=104, max_new_tokens=24, max_context_tokens=128,
+                                            dtype=dtype, watermark=0.0), eos_token_id=eos, overlap=overlap)
+        requests = [Request(f"r{i}", tuple(p), SamplingParams(max_new_tokens=10 + 2 * i, temperature=0.0 if i % 2 else 0.9,
+                                                              top_p=0.95, seed=70 + i), n=1 + i % 3)
+                    for i, p in enumerate(prompts)]
+        outputs = {o.request_id: o for o in engine.generate(requests)}
+        engine.check_invariants()
+        engine.flush_prefix_cache()
+        assert engine.cache.num_free_blocks == 10 and not engine.has_work
+        return engine, {name: [(s.sample_index, s.token_ids, s.finish_reason) for s in o.samples]
+                        for name, o in outputs.items()}
+
+    _, free_running = run(False, None)
+    # a stop token that some samples meet early: the most frequent token of the free-running outputs
+    counts = np.bincount([t for samples in free_running.values() for _, tokens, _ in samples for t in tokens[2:]])
+    eos = int(counts.argmax())
+    in_order_engine, in_order = run(False, eos)
+    overlapped_engine, overlapped = run(True, eos)
+    assert overlapped == in_order
+    reasons = [reason for samples in in_order.values() for _, _, reason in samples]
+    assert FinishReason.STOP in reasons and FinishReason.LENGTH in reasons
+    assert in_order_engine.scheduler.stats.preemptions > 0 and overlapped_engine.scheduler.stats.preemptions > 0
+    assert overlapped_engine.prefix_cache.stats.hit_blocks > 0
+
+
 def test_n_way_sampling_shares_the_prompt_and_reproduces(tmp_path):
     from paged_kv_serving_b200.api import generate
 
