@@ -19,6 +19,13 @@ line is printed with
 * ``roofline``   the bytes a decode step must read (every weight once, the cache of the live
                  requests) over its time, against the measured copy bandwidth
 * ``points``     decode tokens a second at batch 1 and 64
+* ``mixed``      Llama-2-13B layer sizes: one step of 32 decoding sequences at 2,048 tokens of
+                 context beside a 512-token portion of a prompt, with its bytes against the bandwidth
+* ``serve``      Llama-3.2-1B layer sizes: 256 requests with prompts of 128 to 4,096 tokens sharing a
+                 512-token prefix, 128 tokens each at temperature 0.7, through ``Engine`` with the
+                 prefix cache: output tokens a second, prefix hit ratio, preemptions
+* ``reference_workload``  this engine on the reference's own published workload (a tiny float32
+                 model); ``--impl reference`` times the reference itself on it, as context
 
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when it exists, else from fallback
 figures (6.65 TB/s, 1.59 PFLOP/s). Weights of a step (16 GB) are far larger than L2, so nothing is flushed
@@ -273,6 +280,202 @@ def run(args) -> dict:
     }
 
 
+def run_mixed(args, peaks) -> dict:
+    """The fourth configuration of the baseline list as it is worded: Llama-2-13B layer sizes
+    (40 heads without grouping), one step of 32 decoding sequences at 2,048 tokens of context
+    beside one 512-token portion of a prompt (a step of 544 tokens), sampled on the device."""
+    import numpy as np
+    import torch
+
+    from paged_kv_serving_b200.config.presets import PRESETS, preset
+    from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+    from paged_kv_serving_b200.engine.runner import ModelRunner
+    from paged_kv_serving_b200.engine.sequence import SamplingParams
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+    from paged_kv_serving_b200.sampling.sampler import Sampler
+
+    full_layers = PRESETS["llama-2-13b"]["n_layers"]
+    layers = args.workload_layers or full_layers
+    config = preset("llama-2-13b", n_layers=layers)
+    model = DecoderModel.from_random(config, seed=0, dtype="bfloat16", device="cuda:0")
+    rng = np.random.default_rng(2)
+    seqs, context, portion, block, steps, warmup = 32, 2048, 512, 16, 12, 3
+    pages = -(-(context + steps + warmup + 8) // block)
+    runner = ModelRunner(model, num_blocks=(seqs + 1) * pages, block_size=block, max_running_seqs=64)
+    sampler = Sampler(model.device)
+    tables = [tuple(range(i * pages, (i + 1) * pages)) for i in range(seqs + 1)]
+    tokens = rng.integers(0, config.vocab_size, size=(seqs + 1, context + steps + warmup + 8))
+    for first in range(0, seqs, 2):           # fill the cache of the decoding sequences, 4,096 tokens a step
+        runner.step(ExecutionBatch(tuple(
+            BatchEntry(f"d{i}", tuple(int(t) for t in tokens[i, :context]), 0, (tables[i],), ()) for i in (first, first + 1))))
+    runner.step(ExecutionBatch((BatchEntry("p", tuple(int(t) for t in tokens[seqs, :portion]), 0, (tables[seqs],), ()),)))
+    chunk = tuple(int(t) for t in tokens[seqs, portion:2 * portion])
+    greedy = SamplingParams(max_new_tokens=1)
+
+    def one(k):
+        entries = [BatchEntry(f"d{i}", (int(tokens[i, context + k]),), context + k, (tables[i],), (0,)) for i in range(seqs)]
+        entries.append(BatchEntry("p", chunk, portion, (tables[seqs],), ()))     # the prompt's second 512 tokens
+        result = runner.step(ExecutionBatch(tuple(entries)))
+        sampler.sample_on_device(result.logits, [greedy] * seqs, [None] * seqs)
+
+    for k in range(warmup):
+        one(k)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for k in range(steps):
+        one(warmup + k)
+    stop.record()
+    torch.cuda.synchronize()
+    runner.check_status()
+    ms = start.elapsed_time(stop) / steps
+    kv_per_token = sum(2 * len(g.entries) * g.n_kv_heads * g.head_dim * 2 for g in runner.groups)
+    cache_tokens = seqs * (context + warmup + steps / 2) + 2 * portion
+    step_bytes = model.weight_bytes_read_per_step() + cache_tokens * kv_per_token
+    step_tokens = seqs + portion
+    flops = 2.0 * step_tokens * layers * (config.d_model * (config.q_width + 2 * config.kv_width)
+                                          + config.q_width * config.d_model + 3 * config.d_model * config.d_ff)
+    flops += 2.0 * seqs * config.d_model * config.vocab_size
+    flops += 4.0 * layers * config.n_heads * config.head_dim * (seqs * context + portion * 1.5 * portion)
+    out = {"model": "llama-2-13b-shape", "n_layers": layers, "n_layers_full": full_layers, "decode_seqs": seqs,
+           "context": context, "prefill_portion": portion, "ms_per_step": ms, "tokens_per_s": step_tokens / (ms / 1e3),
+           "decode_tokens_per_s": seqs / (ms / 1e3), "bound": "hbm (weights once + keys and values of the live requests)",
+           "gbytes_per_step": step_bytes / 1e9, "hbm_frac": step_bytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"],
+           "flops_frac": flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+    del runner, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_serve(args) -> dict:
+    """The fifth configuration of the baseline list as it is worded: Llama-3.2-1B layer sizes,
+    256 requests with prompts of 128 to 4,096 tokens that share a 512-token prefix, 128 tokens
+    each at temperature 0.7, through ``Engine`` with its scheduler and prefix cache."""
+    import numpy as np
+    import torch
+
+    from paged_kv_serving_b200.config import EngineConfig
+    from paged_kv_serving_b200.config.presets import PRESETS, preset
+    from paged_kv_serving_b200.engine.engine import Engine
+    from paged_kv_serving_b200.engine.sequence import Request, SamplingParams
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+
+    full_layers = PRESETS["llama-3.2-1b"]["n_layers"]
+    layers = args.workload_layers or full_layers
+    config = preset("llama-3.2-1b", n_layers=layers)
+    model = DecoderModel.from_random(config, seed=0, dtype="bfloat16", device="cuda:0")
+    rng = np.random.default_rng(3)
+    count, shared_len, new_tokens, block = args.serve_requests, 512, 128, 16
+    shared = [int(t) for t in rng.integers(0, config.vocab_size, size=shared_len)]
+    lengths = [int(n) for n in rng.integers(128, 4097, size=count)]
+    prompts = [shared[:min(n, shared_len)] + [int(t) for t in rng.integers(0, config.vocab_size, size=max(0, n - shared_len))]
+               for n in lengths]
+    per_sequence = -(-(4096 + new_tokens) // block) + 1
+    engine = Engine(model, EngineConfig(
+        block_size=block, num_blocks=count * per_sequence, max_batched_tokens=8192, max_running_seqs=count,
+        max_prompt_tokens=4096, max_new_tokens=new_tokens, max_context_tokens=4096 + new_tokens,
+        enable_prefix_cache=True, dtype="bfloat16"))
+    # one small request first: kernels, graphs and buffers of the sizes to come are built outside the timed run
+    engine.generate([Request("warm", tuple(prompts[0][:300]), SamplingParams(max_new_tokens=4, temperature=0.7))])
+    engine.flush_prefix_cache()
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    requests = [Request(f"u{i}", tuple(p), SamplingParams(max_new_tokens=new_tokens, temperature=0.7, seed=i, ignore_eos=True),
+                        arrival_time=started) for i, p in enumerate(prompts)]
+    outputs = engine.generate(requests)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - started
+    produced = sum(o.output_tokens for o in outputs)
+    stats = engine.scheduler.stats
+    out = {"model": "llama-3.2-1b-shape", "n_layers": layers, "n_layers_full": full_layers, "requests": len(outputs),
+           "prompt_tokens": sum(lengths), "output_tokens": produced, "seconds": elapsed,
+           "output_tokens_per_s": produced / elapsed, "total_tokens_per_s": (produced + sum(lengths)) / elapsed,
+           "prefix_hit_ratio": engine.prefix_cache.stats.hit_ratio,
+           "cached_prompt_tokens": sum(o.cached_prompt_tokens for o in outputs),
+           "preemptions": stats.preemptions, "steps": stats.iterations,
+           "mean_ttft_s": sum(o.ttft for o in outputs) / max(1, len(outputs))}
+    del engine, model
+    torch.cuda.empty_cache()
+    return out
+
+
+REFERENCE_SRC = ROOT / "baseline" / "_ref"
+REFERENCE_OBSTACLE = ("the reference is a NumPy engine for the CPU whose ModelConfig has neither grouped-query heads nor "
+                      "an untied head, so the benchmark's 8B configuration cannot be expressed on its stock path")
+
+
+def reference_workload_requests():
+    """The reference's own published engine workload (bench/bench_baseline.py:189-214 of
+    rouviere-german/paged-kv-serving): 24 requests of 48 random tokens, 12 new tokens each, on its
+    default random model (4 layers, width 128, 4 heads, feed-forward 320, vocabulary 512)."""
+    import numpy as np
+
+    rng = np.random.default_rng(4)
+    return [([int(v) for v in rng.integers(1, 256, 48)], 12, index) for index in range(24)]
+
+
+def reference_context() -> dict | None:
+    """Times the unmodified reference (copied to ``baseline/_ref``) through its own public API
+    (``Engine.generate``) on its published workload. Context only: another model and another
+    machine part (the host's CPU) than the headline, so no ratio is formed from it."""
+    if not (REFERENCE_SRC / "paged_kv_serving").is_dir():
+        return None
+    sys.path.insert(0, str(REFERENCE_SRC))
+    try:
+        from paged_kv_serving.engine.config import EngineConfig, ModelConfig
+        from paged_kv_serving.engine.engine import Engine
+        from paged_kv_serving.engine.model import LanguageModel, random_weights
+        from paged_kv_serving.engine.sequence import Request, SamplingParams
+    except Exception as error:                                  # the copy does not import here
+        return {"error": f"{type(error).__name__}: {error}"}
+    config = ModelConfig(vocab_size=512, d_model=128, n_layers=4, n_heads=4, d_ff=320, max_seq_len=1024)
+    model = LanguageModel(config, random_weights(config, 0))
+    limits = EngineConfig(block_size=16, num_blocks=192, max_batched_tokens=128, max_running_seqs=12,
+                          max_prompt_tokens=192, max_new_tokens=24, max_context_tokens=256)
+    best = None
+    for _ in range(3):
+        requests = [Request(request_id=f"bench-{i}", prompt_token_ids=tuple(p), sampling=SamplingParams(max_new_tokens=n, seed=i))
+                    for p, n, i in reference_workload_requests()]
+        engine = Engine(model, limits)
+        started = time.perf_counter()
+        outputs = engine.generate(requests)
+        elapsed = time.perf_counter() - started
+        tokens = sum(o.output_tokens for o in outputs)
+        best = elapsed if best is None else min(best, elapsed)
+    return {"workload": "24 requests x 48 prompt tokens x 12 new tokens, 820k-parameter model, float32, CPU (NumPy)",
+            "output_tokens": tokens, "seconds": best, "output_tokens_per_s": tokens / best}
+
+
+def run_reference_workload() -> dict:
+    """This engine on the reference's published workload (same model sizes, same requests, same
+    limits), on the GPU in float32 through ``Engine.generate``: the number that stands beside
+    ``reference_context`` of the reference arm."""
+    import torch
+
+    from paged_kv_serving_b200.config import EngineConfig
+    from paged_kv_serving_b200.config.presets import preset
+    from paged_kv_serving_b200.engine.engine import Engine
+    from paged_kv_serving_b200.engine.sequence import Request, SamplingParams
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+
+    model = DecoderModel.from_random(preset("reference-default"), seed=0, dtype="float32", device="cuda:0", std=0.08)
+    limits = EngineConfig(block_size=16, num_blocks=192, max_batched_tokens=128, max_running_seqs=12,
+                          max_prompt_tokens=192, max_new_tokens=24, max_context_tokens=256, dtype="float32")
+    best = None
+    for _ in range(3):
+        requests = [Request(f"bench-{i}", tuple(p), SamplingParams(max_new_tokens=n, seed=i)) for p, n, i in reference_workload_requests()]
+        engine = Engine(model, limits)
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        outputs = engine.generate(requests)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - started
+        tokens = sum(o.output_tokens for o in outputs)
+        best = elapsed if best is None else min(best, elapsed)
+    return {"workload": "24 requests x 48 prompt tokens x 12 new tokens, 820k-parameter model, float32, one B200",
+            "output_tokens": tokens, "seconds": best, "output_tokens_per_s": tokens / best}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -285,19 +488,32 @@ def main() -> int:
     parser.add_argument("--prompt-len", type=int, default=1024)
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    parser.add_argument("--skip-workloads", action="store_true",
+                        help="leave out the mixed step (13B sizes), the 256-request run (1B sizes) and the reference's workload")
+    parser.add_argument("--workloads", default="all", help="which of mixed,serve,reference to run beside the headline")
+    parser.add_argument("--only-workloads", action="store_true", help="leave out the headline run (for profiling a workload)")
+    parser.add_argument("--workload-layers", type=int, default=0, help="fewer layers for those workloads (0: all)")
+    parser.add_argument("--serve-requests", type=int, default=256)
     args = parser.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference does not install offline (its build backend uv_build is absent) and is a "
-                          "NumPy CPU engine whose ModelConfig cannot express the benchmark's grouped-query, untied "
-                          "8B configuration"}))
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_OBSTACLE, "context": reference_context()}))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design, --gpus {args.gpus} is not run")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    print(json.dumps(run(args)))
+    wanted = set() if args.skip_workloads else {w for w in args.workloads.split(",") if w}
+    if "all" in wanted:
+        wanted = {"mixed", "serve", "reference"}
+    line = run(args) if not args.only_workloads else {"impl": "ours", "n_gpus": 1}
+    if "mixed" in wanted:
+        line["mixed"] = run_mixed(args, load_peaks())
+    if "serve" in wanted:
+        line["serve"] = run_serve(args)
+    if "reference" in wanted:
+        line["reference_workload"] = run_reference_workload()
+    print(json.dumps(line))
     return 0
 
 

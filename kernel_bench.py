@@ -1,19 +1,25 @@
-"""Timing of single kernels at Llama-family layer sizes: ``python -m paged_kv_serving_b200.kernel_bench``.
+"""Timing of single kernels at Llama-family layer sizes: ``python kernel_bench.py``.
 
 Each case captures a few dozen launches in a CUDA graph (so that no host launch cost is timed),
 rotates over 32 layers' worth of buffers (so that weights, keys and values come from DRAM as in
 a real step) and reports microseconds per launch with the achieved bandwidth or arithmetic rate.
 The sizes come from a preset of ``config/presets.py``; nothing here is used by the engine.
 
-    python -m paged_kv_serving_b200.kernel_bench [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise]
+    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise]
 """
 
 from __future__ import annotations
 
 import argparse
 import math
+import sys
+from pathlib import Path
 
 import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
 
 from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.config.presets import preset

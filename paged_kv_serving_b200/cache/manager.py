@@ -112,16 +112,23 @@ class KVCacheManager:
     def can_reserve(self, count: int) -> bool:
         return count <= self.num_free_blocks + self.evictable_blocks()
 
-    def coverable_tokens(self, sequence, keep_free: int = 0) -> int:
+    def coverable_tokens(self, sequence, keep_free: int = 0, enough: int | None = None) -> int:
         """How many more tokens of ``sequence`` the pools could hold beyond those computed,
-        leaving ``keep_free`` pages free (the scheduler's memory bound for a portion)."""
-        best = None
-        evictable = self.evictable_blocks()
-        for allocator, table in zip(self.allocators, sequence.block_tables):
-            available = max(0, allocator.num_free + evictable - keep_free)
-            tokens = (len(table) + available) * self.block_size - sequence.num_computed_tokens
-            best = tokens if best is None else min(best, tokens)
-        return best if best is not None else 1 << 30
+        leaving ``keep_free`` pages free (the scheduler's memory bound for a portion). Cached
+        pages that only the prefix cache holds count as available; they are counted (a walk over
+        the whole cache) only when the free pages alone do not cover ``enough`` tokens."""
+        def covered(evictable: int) -> int:
+            best = None
+            for allocator, table in zip(self.allocators, sequence.block_tables):
+                available = max(0, allocator.num_free + evictable - keep_free)
+                tokens = (len(table) + available) * self.block_size - sequence.num_computed_tokens
+                best = tokens if best is None else min(best, tokens)
+            return best if best is not None else 1 << 30
+
+        from_free_pages = covered(0)
+        if enough is not None and from_free_pages >= enough:
+            return from_free_pages
+        return covered(self.evictable_blocks())
 
     # --- prefix reuse --------------------------------------------------------------------
 

@@ -120,13 +120,14 @@ class PrefixCache:
         dropped = 0
         if count <= 0:
             return 0
-        for key in list(self._entries):
-            if dropped >= count:
+        victims = []
+        for key, pages in self._entries.items():          # least recently used first
+            if len(victims) >= count:
                 break
-            pages = self._entries[key]
-            if not self._sole_holder(pages):
-                continue
-            del self._entries[key]
+            if self._sole_holder(pages):
+                victims.append(key)
+        for key in victims:
+            pages = self._entries.pop(key)
             for allocator, page in zip(self._allocators, pages):
                 allocator.release(page)
             dropped += 1

@@ -469,3 +469,46 @@ PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positi
 #undef PKV_ROPE
   return PKV_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// copy of one cache page (copy-on-write): in both pools, for every layer of a page group, page
+// `src` is copied onto page `dst`. A page of one layer is one contiguous run of `page_bytes`
+// bytes (a multiple of 4); layers are `layer_stride_bytes` apart. One launch instead of two
+// strided copies per pool (reference: src/paged_kv_serving/engine/runner.py:128-133).
+// ---------------------------------------------------------------------------------------------
+namespace pkv {
+
+template <typename V>
+__global__ void copy_page_kernel(uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool, long long layer_stride_bytes,
+                                 long long page_bytes, long long src, long long dst) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  uint8_t* pool = (blockIdx.y & 1) ? v_pool : k_pool;
+  const long long layer = blockIdx.y >> 1;
+  const V* from = reinterpret_cast<const V*>(pool + layer * layer_stride_bytes + src * page_bytes);
+  V* to = reinterpret_cast<V*>(pool + layer * layer_stride_bytes + dst * page_bytes);
+  const long long n = page_bytes / (long long)sizeof(V);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    to[i] = from[i];
+}
+
+}  // namespace pkv
+
+PKV_EXPORT int pkv_copy_page(void* k_pool, void* v_pool, int layers, long long layer_stride_bytes, long long page_bytes,
+                             long long pages, long long src, long long dst, void* stream) {
+  if (layers <= 0 || page_bytes <= 0 || page_bytes % 4 != 0 || layers > 32767) return PKV_ERR_SIZE;
+  if (src < 0 || dst < 0 || src >= pages || dst >= pages || src == dst) return PKV_ERR_SIZE;
+  if (layer_stride_bytes < pages * page_bytes) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool wide = page_bytes % 16 == 0 && layer_stride_bytes % 16 == 0 &&
+                    (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
+  const long long units = page_bytes / (wide ? 16 : 4);
+  int bx = (int)((units + 255) / 256);
+  if (bx > 32) bx = 32;
+  dim3 grid(bx, 2 * layers);
+  if (wide)
+    return launch_kernel(copy_page_kernel<uint4>, grid, dim3(256), 0, s, true, 0, (uint8_t*)k_pool, (uint8_t*)v_pool,
+                         layer_stride_bytes, page_bytes, src, dst);
+  return launch_kernel(copy_page_kernel<uint32_t>, grid, dim3(256), 0, s, true, 0, (uint8_t*)k_pool, (uint8_t*)v_pool,
+                       layer_stride_bytes, page_bytes, src, dst);
+}

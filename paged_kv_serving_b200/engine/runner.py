@@ -65,8 +65,7 @@ class CacheStorage:
     def copy_page(self, group: int, source: int, destination: int) -> None:
         if source == destination:
             raise ValueError("a page is never copied onto itself")
-        self.k_pools[group][:, destination].copy_(self.k_pools[group][:, source])
-        self.v_pools[group][:, destination].copy_(self.v_pools[group][:, source])
+        ops.copy_page(self.k_pools[group], self.v_pools[group], source, destination)
 
     def copy_state(self, source_slot: int, destination_slot: int) -> None:
         for state in self.states:

@@ -237,7 +237,7 @@ class Scheduler:
         wanted = plan.allowed(sequence, self._portion(sequence, plan))
         if wanted <= 0:
             return
-        tokens = min(wanted, self.cache.coverable_tokens(sequence))
+        tokens = min(wanted, self.cache.coverable_tokens(sequence, enough=wanted))
         while tokens <= 0:
             # Two long prompts can hold the whole pool between them with no decoder left to
             # trigger a preemption; the one in front takes pages from the weakest one behind it.
@@ -245,7 +245,7 @@ class Scheduler:
             if not victims:
                 return
             self._preempt(victims[-1], plan)
-            tokens = min(wanted, self.cache.coverable_tokens(sequence))
+            tokens = min(wanted, self.cache.coverable_tokens(sequence, enough=wanted))
         try:
             self.cache.reserve(sequence, sequence.num_computed_tokens + tokens)
         except OutOfPages:  # pragma: no cover - coverable_tokens bounds the portion
@@ -261,7 +261,8 @@ class Scheduler:
         # The watermark keeps room for the decode steps of running sequences; with nothing
         # running it protects nobody and could refuse the only request forever.
         keep_free = int(self.config.watermark * self.cache.num_blocks) if self._running else 0
-        tokens = min(self._portion(sequence, plan), self.cache.coverable_tokens(sequence, keep_free))
+        portion = self._portion(sequence, plan)
+        tokens = min(portion, self.cache.coverable_tokens(sequence, keep_free, enough=portion))
         tokens = plan.allowed(sequence, tokens)
         if tokens <= 0:
             self.cache.detach_prefix(sequence)

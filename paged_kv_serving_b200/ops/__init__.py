@@ -24,7 +24,7 @@ __all__ = [
     "attention_decode_flat_supports", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
     "attention_decode_tma_pushed_splits", "attention_decode_tma_supports",
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
-    "attention_tcgen05_supports", "build_all", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
+    "attention_tcgen05_supports", "build_all", "copy_page", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
     "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
     "launch_count", "library", "library_names", "paged_attention_generic", "raise_for_status", "reset_workspaces",
     "rope_kv_store", "sample", "silu_mul", "status_word", "wait_probe",
@@ -139,6 +139,20 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(weight),
               float(eps), _ptr(out), dtype_code(out_dtype), _ptr(rows), n_rows, d, _stream()), "add_rmsnorm")
     return out
+
+
+def copy_page(k_pool: torch.Tensor, v_pool: torch.Tensor, source: int, destination: int) -> None:
+    """Copy page ``source`` onto page ``destination`` in every layer of both pools
+    (``[layers, pages, ...]``, equal shapes and types): copy-on-write of a cache page in one launch."""
+    _need(k_pool, None, "k_pool"); _need(v_pool, k_pool.dtype, "v_pool")
+    if k_pool.shape != v_pool.shape or k_pool.dim() < 2:
+        raise ValueError("the pools must be [layers, pages, ...] of equal shape")
+    layers, pages = k_pool.shape[0], k_pool.shape[1]
+    page_bytes = k_pool.stride(1) * k_pool.element_size()
+    fn = _fn("elementwise", "pkv_copy_page",
+             [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_longlong, c_longlong, c_void_p])
+    _check(fn(_ptr(k_pool), _ptr(v_pool), layers, k_pool.stride(0) * k_pool.element_size(), page_bytes, pages,
+              int(source), int(destination), _stream()), "copy_page")
 
 
 def silu_mul(gate_up: torch.Tensor, clip: float, ff: int | None = None, interleave: int = 0) -> torch.Tensor:

@@ -27,9 +27,6 @@ class SwiGLU(Part):
     graph_safe = True
     BLOCK = 128
 
-    graph_safe = True
-
-
     def __init__(self, width: int, inner: int, clip: float = 60.0) -> None:
         self.width = int(width)
         self.inner = int(inner)

@@ -39,15 +39,18 @@ PAGE_SIZE = {"A": 4, "B": 8, "C": 16, "D": 16}
 CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 WEIGHT_SEED = {"A": 0, "B": 2, "C": 5, "D": 7}
 
-# Tolerances, fixed before any GPU run. float32: the reference's own bound for paged against
-# dense logits (tests/property/test_equivalence.py:33-34 of the reference). bfloat16: activations
-# carry 8 bits of mantissa (relative 2^-8 per rounding); with a few roundings per layer on logits
-# of magnitude ~1 the bound is 3% of the largest logit of the compared rows plus a small floor.
+# Tolerances. float32: the reference's own bound for paged against dense logits
+# (tests/property/test_equivalence.py:33-34 of the reference). bfloat16: activations carry 8 bits
+# of mantissa (relative 2^-8 per rounding); with a few roundings per layer the bound was first set
+# to 3 % of the largest logit of the compared rows plus a small floor, before any GPU run. Every
+# comparison of the suite (tiny models, two layers at the widths of 1-, 8- and 13-billion-parameter
+# models, every way of cutting and batching) then stayed below 1.9 %, and the bound was tightened
+# to 2.4 %: room for a quarter more than the worst case seen, none for a wrong key or page.
 F32_ATOL = 1e-4
 
 
 def bf16_atol(reference: np.ndarray) -> float:
-    return 0.03 * float(np.abs(reference).max()) + 2e-3
+    return 0.024 * float(np.abs(reference).max()) + 2e-3
 
 
 def tensors_for(name: str, dtype: str, std: float | None = None, norm_jitter: float = 0.1) -> dict[str, np.ndarray]:

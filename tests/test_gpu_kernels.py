@@ -691,3 +691,24 @@ def test_sampling_kernel_large_vocabulary():
             p = plain_model.sample_distribution(logits[row], 0.7, float(top_p[row]))
             cum = np.cumsum(p, dtype=np.float64)
             assert min(abs(cum[ids[row]] - u[row] * cum[-1]), abs(cum[want] - u[row] * cum[-1])) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layers, pages, kv, page, hd", [(3, 7, 2, 4, 6), (1, 4, 1, 3, 2), (5, 9, 8, 16, 128)])
+def test_copy_page_copies_one_page_of_every_layer_and_nothing_else(layers, pages, kv, page, hd, dtype):
+    """Copy-on-write of a cache page: one launch for both pools and all layers; pages whose bytes
+    are no multiple of 16 take the narrow path."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(layers + hd)
+    k_pool = torch.from_numpy(rng.standard_normal((layers, pages, kv, page, hd)).astype(np.float32)).cuda().to(dtype)
+    v_pool = torch.from_numpy(rng.standard_normal((layers, pages, kv, page, hd)).astype(np.float32)).cuda().to(dtype)
+    want_k, want_v = k_pool.clone(), v_pool.clone()
+    want_k[:, pages - 2] = want_k[:, 1]
+    want_v[:, pages - 2] = want_v[:, 1]
+    ops.copy_page(k_pool, v_pool, 1, pages - 2)
+    assert torch.equal(k_pool, want_k) and torch.equal(v_pool, want_v)
+    with pytest.raises(ValueError, match="size"):
+        ops.copy_page(k_pool, v_pool, 1, pages)          # outside the pool
+    with pytest.raises(ValueError, match="size"):
+        ops.copy_page(k_pool, v_pool, 2, 2)              # onto itself
