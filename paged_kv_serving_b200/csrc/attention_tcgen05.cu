@@ -54,12 +54,18 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int HD, int KT>
+// WIDE: a page of keys or values arrives as ONE copy that covers every 64-column panel (the pool
+// seen through make_panel_group_map), and a tile lies in shared memory as groups of 8 keys, each
+// group panel after panel; otherwise one copy per page and panel, and a tile lies panel after
+// panel. With pages of 16 keys the number of copies per tile is what holds this kernel back, and
+// the wide form halves it for head size 128.
+template <int HD, int KT, bool WIDE>
 __global__ void __launch_bounds__(FA_THREADS, KT == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const FaParams p) {
   constexpr int FA_BN = KT;                               // keys per tile
   constexpr int PANELS = HD / 64;                         // 64-column panels of a row of Q, K or V
+  constexpr uint32_t GROUP_BYTES = PANELS * 1024;         // WIDE: 8 keys, every panel
   constexpr uint32_t PANEL_BYTES = 128 * 128;             // a panel of Q or P: 128 rows of 128 bytes
   constexpr uint32_t Q_BYTES = PANELS * PANEL_BYTES;      // the query tile
   constexpr uint32_t KV_PANEL_BYTES = KT * 128;           // a panel of K or V: KT rows of 128 bytes
@@ -129,7 +135,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         tma_load_2d(q_s + pn * PANEL_BYTES, &map_q, &q_full, head * HD + 64 * pn, tok0 + q0);
     }
     const int pages_per_tile = FA_BN / p.page_size;
-    const int boxes = pages_per_tile * PANELS;
+    const int boxes = WIDE ? pages_per_tile : pages_per_tile * PANELS;
     bool ok = true;
     int loaded_k = 0, loaded_v = 0;
     // one tile of keys (which = 0) or values (1): wait for its slot, announce the bytes, one box a lane
@@ -147,7 +153,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!ok) return;
       uint8_t* dst = (which ? v_s : k_s) + stage * TILE_BYTES;
       for (int b = lane; b < boxes; b += 32) {
-        const int i = b / PANELS, pn = b - i * PANELS;
+        const int i = WIDE ? b : b / PANELS, pn = WIDE ? 0 : b - i * PANELS;
         const int pos = tile_base + i * p.page_size;
         int row = p.pool_rows;                               // outside the pool: zeros
         if (pos < key_hi && pos + p.page_size > key_lo) {
@@ -155,7 +161,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
           if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
         }
-        tma_load_2d(dst + pn * KV_PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
+        if (WIDE)
+          tma_load_4d(dst + (i * p.page_size >> 3) * GROUP_BYTES, which ? &map_v : &map_k, full, 0, 0, 0, row >> 3);
+        else
+          tma_load_2d(dst + pn * KV_PANEL_BYTES + i * p.page_size * 128, which ? &map_v : &map_k, full, 64 * pn, row);
       }
       __syncwarp();
       if (which) loaded_v = j + 1; else loaded_k = j + 1;
@@ -187,8 +196,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s + stage * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t k_desc = WIDE ? umma_desc_sbo(k_addr + (ks >> 2) * 1024, GROUP_BYTES)
+                                       : umma_desc(k_addr + (ks >> 2) * KV_PANEL_BYTES);
           umma_bf16(tmem_base + S_COL + stage * FA_BN, umma_desc(q_addr + (ks >> 2) * PANEL_BYTES) + 2 * (ks & 3),
-                    umma_desc(k_addr + (ks >> 2) * KV_PANEL_BYTES) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
+                    k_desc + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(&k_empty[stage]);
         umma_commit(&s_full[stage]);
@@ -213,8 +224,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t p_addr = smem_addr(p_s), v_addr = smem_addr(v_s + (j % VSTAGES) * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FA_BN / 16; ++ks) {
-          umma_bf16(tmem_base + O_COL, umma_desc(p_addr + (ks >> 2) * PANEL_BYTES) + 2 * (ks & 3),
-                    umma_desc_mn(v_addr + ks * 16 * 128, KV_PANEL_BYTES, 1024), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          // 16 keys a step: the next 64 columns of the values KV_PANEL_BYTES (WIDE: 1024) on,
+          // the next 8 keys 1024 (WIDE: GROUP_BYTES) on
+          const uint64_t v_desc = WIDE ? umma_desc_mn(v_addr + ks * 2 * GROUP_BYTES, 1024, GROUP_BYTES)
+                                       : umma_desc_mn(v_addr + ks * 16 * 128, KV_PANEL_BYTES, 1024);
+          umma_bf16(tmem_base + O_COL, umma_desc(p_addr + (ks >> 2) * PANEL_BYTES) + 2 * (ks & 3), v_desc, idesc_o,
+                    (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[j % VSTAGES]);
         umma_commit(&pv_done);
@@ -321,7 +336,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int r = key_hi - tile_base + (int)threadIdx.x - 64;     // threads 64..191 take one row each
         if (r < FA_BN)
           for (int pn = 0; pn < PANELS; ++pn) {
-            uint4* dst = reinterpret_cast<uint4*>(v_s + (j % VSTAGES) * TILE_BYTES + pn * KV_PANEL_BYTES + r * 128);
+            const uint32_t at = WIDE ? (r >> 3) * GROUP_BYTES + pn * 1024 + (r & 7) * 128 : pn * KV_PANEL_BYTES + r * 128;
+            uint4* dst = reinterpret_cast<uint4*>(v_s + (j % VSTAGES) * TILE_BYTES + at);
 #pragma unroll
             for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
           }
@@ -369,23 +385,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 struct PoolMapKey {
   const void* base;
   long long rows;
-  int hd, box;
+  int hd, box, wide;
   CUtensorMap map;
 };
 
-static const CUtensorMap* pool_map(const void* base, long long rows, int hd, int box_rows) {
+// The tensor map of a key or value pool, kept per (pool, sizes, form); null when the driver
+// refuses to encode it.
+static const CUtensorMap* pool_map(const void* base, long long rows, int hd, int box_rows, int wide) {
   static PoolMapKey cache[512];
   static int used = 0;
   for (int i = 0; i < used; ++i)
-    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) return &cache[i].map;
+    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows &&
+        cache[i].wide == wide)
+      return &cache[i].map;
   PoolMapKey& slot = cache[used < 512 ? used : 511];
-  if (make_tile_map(&slot.map, base, rows, hd, hd, box_rows)) return nullptr;
-  slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows;
+  const int rc = wide ? make_panel_group_map(&slot.map, base, rows, hd / 64, box_rows)
+                      : make_tile_map(&slot.map, base, rows, hd, hd, box_rows);
+  if (rc) return nullptr;
+  slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows; slot.wide = wide;
   if (used < 512) ++used;
   return &slot.map;
 }
 
-template <int HD, int KT>
+template <int HD, int KT, bool WIDE>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
                      cudaStream_t s) {
   // the query tile, two key tiles, one or two value tiles, the probabilities, and room to align
@@ -393,17 +415,19 @@ static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
   const size_t smem = panels * 128 * 128 + (2 + (KT == 64 ? 1 : 2)) * panels * KT * 128 + (size_t)(KT / 64) * 128 * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_tcgen05_kernel<HD, KT><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
+  attention_tcgen05_kernel<HD, KT, WIDE><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
   return launch_status();
 }
 
 }  // namespace pkv
 
 using namespace pkv;
+
+static int g_narrow_boxes = 0;
 
 // 1 when this kernel takes the sizes, 0 when another attention kernel must be used.
 PKV_EXPORT int pkv_attention_tcgen05_supports(int hd, int page_size, int q_row_stride) {
@@ -428,8 +452,15 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   alignas(64) CUtensorMap map_q;
   int r = make_tile_map(&map_q, qkv, n_tokens, q_row_stride, q_row_stride, FA_BM);
   if (r) return r;
-  const CUtensorMap* map_k = pool_map(k_pool, pool_rows, hd, page_size);
-  const CUtensorMap* map_v = pool_map(v_pool, pool_rows, hd, page_size);
+  // head size 128: a page in one copy (both 64-column panels) where the driver encodes that map
+  int wide = hd == 128 && pool_rows % 8 == 0 && !g_narrow_boxes;
+  const CUtensorMap* map_k = pool_map(k_pool, pool_rows, hd, page_size, wide);
+  const CUtensorMap* map_v = pool_map(v_pool, pool_rows, hd, page_size, wide);
+  if (wide && (!map_k || !map_v)) {
+    wide = 0;
+    map_k = pool_map(k_pool, pool_rows, hd, page_size, 0);
+    map_v = pool_map(v_pool, pool_rows, hd, page_size, 0);
+  }
   if (!map_k || !map_v) return PKV_ERR_SIZE;
   int shift = -1;
   for (int i = 0; i < 31; ++i)
@@ -439,9 +470,19 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   cudaStream_t s = (cudaStream_t)stream;
   // tiles of 64 keys (two blocks to an SM) wherever a page fits one
   if (page_size <= 64) {
-    if (hd == 128) return launch_fa<128, 64>(map_q, *map_k, *map_v, p, n_work, s);
-    return launch_fa<64, 64>(map_q, *map_k, *map_v, p, n_work, s);
+    if (hd == 128 && wide) return launch_fa<128, 64, true>(map_q, *map_k, *map_v, p, n_work, s);
+    if (hd == 128) return launch_fa<128, 64, false>(map_q, *map_k, *map_v, p, n_work, s);
+    return launch_fa<64, 64, false>(map_q, *map_k, *map_v, p, n_work, s);
   }
-  if (hd == 128) return launch_fa<128, 128>(map_q, *map_k, *map_v, p, n_work, s);
-  return launch_fa<64, 128>(map_q, *map_k, *map_v, p, n_work, s);
+  if (hd == 128 && wide) return launch_fa<128, 128, true>(map_q, *map_k, *map_v, p, n_work, s);
+  if (hd == 128) return launch_fa<128, 128, false>(map_q, *map_k, *map_v, p, n_work, s);
+  return launch_fa<64, 128, false>(map_q, *map_k, *map_v, p, n_work, s);
+}
+
+// For comparisons and tests: non-zero makes the kernel fetch one copy per page and panel even
+// where one copy per page is possible. Returns the previous setting.
+PKV_EXPORT int pkv_attention_tcgen05_narrow_boxes(int on) {
+  const int before = g_narrow_boxes;
+  g_narrow_boxes = on != 0;
+  return before;
 }

@@ -52,6 +52,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(columns));
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -71,6 +78,17 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
   d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset: 8 rows x 128 bytes
   d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
   d |= (uint64_t)2 << 61;                            // 128-byte swizzle
+  return d;
+}
+
+// The same with groups of 8 rows `sbo_bytes` apart (a multiple of 1024).
+__device__ __forceinline__ uint64_t umma_desc_sbo(uint32_t saddr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffff) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
   return d;
 }
 
@@ -219,6 +237,26 @@ inline EncodeTiledFn encode_tiled() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   }
   return fn;
+}
+
+// A [rows, 64 * panels] bfloat16 matrix (rows a multiple of 8, contiguous) seen as
+// [rows / 8][panels][8][64]: a box of `box_rows` rows brings, for every group of 8 rows, panel after
+// panel, the 8 rows of 128 bytes of that panel, swizzled by 128 bytes. In shared memory that is
+// the canonical K-major layout of each panel with groups of 8 rows panels * 1024 bytes apart, so
+// one copy fetches whole rows of several panels (a page of keys) instead of one copy per panel.
+inline int make_panel_group_map(CUtensorMap* map, const void* base, long long rows, int panels, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return PKV_ERR_LIMIT;
+  if (rows % 8 || box_rows % 8 || panels < 1) return PKV_ERR_SIZE;
+  const cuuint64_t row_bytes = (cuuint64_t)panels * 128;
+  cuuint64_t dims[4] = {64, 8, (cuuint64_t)panels, (cuuint64_t)(rows / 8)};
+  cuuint64_t strides[3] = {row_bytes, 128, 8 * row_bytes};
+  cuuint32_t box[4] = {64u, 8u, (cuuint32_t)panels, (cuuint32_t)(box_rows / 8)};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : PKV_ERR_SIZE;
 }
 
 // A [rows, cols] bfloat16 matrix with `ld` elements between rows, fetched in boxes of

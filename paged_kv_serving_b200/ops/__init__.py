@@ -23,7 +23,8 @@ __all__ = [
     "attention_decode_blocks_per_sm", "attention_decode_flat", "attention_decode_flat_blocks_per_sm",
     "attention_decode_flat_supports", "attention_decode_tma", "attention_decode_tma_blocks_per_sm",
     "attention_decode_tma_pushed_splits", "attention_decode_tma_supports",
-    "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_rows",
+    "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_narrow_boxes",
+    "attention_tcgen05_rows",
     "attention_tcgen05_supports", "build_all", "copy_page", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
     "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
     "launch_count", "library", "library_names", "paged_attention_generic", "raise_for_status", "reset_workspaces",
@@ -314,6 +315,16 @@ def attention_tcgen05_supports(head_dim: int, page_size: int, q_row_stride: int)
     lib.pkv_attention_tcgen05_supports.restype = c_int
     lib.pkv_attention_tcgen05_supports.argtypes = [c_int, c_int, c_int]
     return bool(lib.pkv_attention_tcgen05_supports(int(head_dim), int(page_size), int(q_row_stride)))
+
+
+def attention_tcgen05_narrow_boxes(on: bool) -> bool:
+    """For comparisons and tests: make the tcgen05 prefill attention fetch one copy per page and
+    64-column panel even where it can fetch a page in one copy (head size 128). Returns the
+    previous setting."""
+    lib = library("attention_tcgen05")
+    lib.pkv_attention_tcgen05_narrow_boxes.restype = c_int
+    lib.pkv_attention_tcgen05_narrow_boxes.argtypes = [c_int]
+    return bool(lib.pkv_attention_tcgen05_narrow_boxes(int(bool(on))))
 
 
 def attention_tcgen05_rows() -> int:

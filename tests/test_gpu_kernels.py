@@ -284,20 +284,29 @@ def test_attention_bf16_tensor_core_kernels(heads, kv, hd, page, splits):
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 
 
+@pytest.mark.parametrize("narrow", [False, True])
 @pytest.mark.parametrize("heads, kv, hd, page", [(32, 8, 128, 16), (3, 3, 128, 8), (16, 2, 64, 8), (4, 4, 64, 32),
-                                                   (6, 1, 128, 128)])
-def test_attention_tcgen05_prefill(heads, kv, hd, page):
+                                                   (6, 1, 128, 128), (5, 5, 128, 64), (4, 2, 128, 32)])
+def test_attention_tcgen05_prefill(heads, kv, hd, page, narrow):
     """The tcgen05/TMA prefill kernel: runs of 17 to 513 queries, block edges at 128 and 129
     queries, a run deep inside its context, partial last pages filled with NaN, one far key that
-    dominates the last query; short entries go to the decode kernel in the same batch."""
+    dominates the last query; short entries go to the decode kernel in the same batch. With head
+    size 128 a page arrives as one copy over both 64-column panels, or (``narrow``) as one copy
+    per panel."""
     from paged_kv_serving_b200 import ops
 
     assert ops.attention_tcgen05_supports(hd, page, (heads + 2 * kv) * hd)
     assert not ops.attention_tcgen05_supports(48, 16, 144) and not ops.attention_tcgen05_supports(128, 4, 384)
+    if narrow and hd != 128:
+        pytest.skip("head size 64 has one panel: the two forms are the same")
     rng = np.random.default_rng(hd + page)
-    got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
-                                contexts=[300, 1, 129, 33, 128, 700, 513, 1000], queries=[100, 1, 129, 17, 128, 150, 513, 2],
-                                dtype="bfloat16", fast=True, splits=2, tcgen05=True)
+    before = ops.attention_tcgen05_narrow_boxes(narrow)
+    try:
+        got, want = _attention_case(rng, heads=heads, kv=kv, hd=hd, page=page, window=None,
+                                    contexts=[300, 1, 129, 33, 128, 700, 513, 1000], queries=[100, 1, 129, 17, 128, 150, 513, 2],
+                                    dtype="bfloat16", fast=True, splits=2, tcgen05=True)
+    finally:
+        ops.attention_tcgen05_narrow_boxes(before)
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 
@@ -362,10 +371,11 @@ def test_attention_decode_tma_window_edges(window):
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("window", [1, 63, 128, 129, 300])
-def test_attention_tcgen05_prefill_window_edges(window):
+def test_attention_tcgen05_prefill_window_edges(window, hd):
     rng = np.random.default_rng(window)
-    got, want = _attention_case(rng, heads=4, kv=2, hd=64, page=8, window=window,
+    got, want = _attention_case(rng, heads=4, kv=2, hd=hd, page=8, window=window,
                                 contexts=[400, 128, 31, 640], queries=[200, 128, 31, 300],
                                 dtype="bfloat16", fast=True, splits=2, tcgen05=True)
     assert np.isfinite(got).all()
