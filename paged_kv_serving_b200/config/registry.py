@@ -16,7 +16,7 @@ __all__ = [
     "register_architecture", "register_part",
 ]
 
-PART_KINDS = ("mixer", "feed_forward", "norm", "position", "block")
+PART_KINDS = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
 
 _ARCHITECTURES: dict[str, Any] = {}
 _PARTS: dict[str, dict[str, Any]] = {kind: {} for kind in PART_KINDS}

@@ -143,7 +143,8 @@ class ModelRunner:
         self.sampled_ids = torch.zeros((max(1, max_running_seqs) + 1,), dtype=torch.int32, device=model.device)
         self.steps_run = 0
         self.use_graphs = use_graphs
-        self._graph_safe = all(block.graph_safe for block in model.layout.blocks) and model.layout.final_norm.graph_safe
+        layout = model.layout
+        self._graph_safe = all(part.graph_safe for part in (*layout.blocks, layout.final_norm, layout.embedding, layout.head))
         self._graphs: dict[tuple[int, int], dict] = {}
         self._last_graph_step: tuple[ExecutionBatch, tuple[int, int]] | None = None
         self._ahead: dict | None = None
@@ -262,7 +263,7 @@ class ModelRunner:
                                    self.groups[g].window, table_name, slots_name))
         ctx = StepContext(dtype=self.model.dtype, device=self.model.device, num_tokens=total, num_seqs=len(entries),
                           seq_lens=lens, first_positions=[e.first_position for e in entries], arena=arena,
-                          groups=views, states=self.storage.states)
+                          groups=views, states=self.storage.states, status=self._status, fed_back_ids=self.sampled_ids)
         return ctx, rows
 
     def _plan(self, ctx: StepContext) -> None:
@@ -273,8 +274,7 @@ class ModelRunner:
         """The kernels of one step, launched on the current stream; nothing here reads device
         data on the host, so the whole sequence can be captured in a CUDA graph."""
         model = self.model
-        hidden = ops.embedding_gather(model.embedding, ctx.ints(StepContext.TOKEN_IDS), self._status,
-                                      self.sampled_ids, ctx.ints(StepContext.TOKEN_FEEDBACK))
+        hidden = model.layout.embedding.forward(ctx)
         blocks = model.layout.blocks
         delta = None
         for i, (call, binding) in enumerate(zip(self.order, self.bindings)):
@@ -288,7 +288,7 @@ class ModelRunner:
         if not want_logits:
             return None
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
-        return gemm.linear(normed, model.head, out_dtype=torch.float32, chain=True)
+        return model.layout.head.forward(normed, ctx)
 
     def step(self, batch: ExecutionBatch, clear_state_slots: list[int] | None = None,
              feedback: dict[str, int] | None = None) -> StepResult:

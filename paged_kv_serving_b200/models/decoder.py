@@ -31,8 +31,6 @@ class DecoderModel:
         self.dtype_name = dtype
         self.dtype = TORCH_DTYPES[dtype]
         self.device = torch.device(device)
-        self.embedding: torch.Tensor | None = None
-        self.head: torch.Tensor | None = None      # [vocab, width]; the embedding when tied
 
     # --- construction --------------------------------------------------------------------
 
@@ -46,8 +44,6 @@ class DecoderModel:
         loader.check_tensors(specs, tensors)
         placed = {name: loader.place(tensors[name], spec, model.dtype, model.device) for name, spec in specs.items()}
         loader.check_finite(placed)      # one pass on the device, after the cast to the compute type
-        model.embedding = placed[layout.embedding_name].contiguous()
-        model.head = placed[layout.head_name].contiguous() if layout.head_name else model.embedding
         per_part: dict[int, tuple[object, dict[str, torch.Tensor]]] = {}
         for name, (part, local) in layout.names.items():
             per_part.setdefault(id(part), (part, {}))[1][local] = placed[name]
@@ -77,9 +73,13 @@ class DecoderModel:
     def weight_bytes_read_per_step(self) -> int:
         """Bytes of weights one decode step has to read: every matrix once (the embedding table
         only by row, so it counts only as the head when tied or not at all when untied)."""
-        total = self.head.numel() * self.head.element_size()
+        element = torch.empty((), dtype=self.dtype).element_size()
+        head = getattr(self.layout.head, "weight", None)
+        total = head.numel() * head.element_size() if head is not None else 0
         seen = set()
         for name, (part, local) in self.layout.names.items():
+            if part is self.layout.embedding or part is self.layout.head:
+                continue                    # the table is read by row; the head is counted above
             spec = part.param_specs()[local]
             count = 1
             for s in spec.shape:
@@ -88,5 +88,5 @@ class DecoderModel:
             if key in seen:
                 continue
             seen.add(key)
-            total += count * (self.head.element_size() if spec.kind == "matrix" else 4)
+            total += count * (element if spec.kind == "matrix" else 4)
         return total

@@ -39,14 +39,30 @@ class ModelLayout:
     embedding_name: str = "token_embedding"
     head_name: str | None = None          # None: the head is the embedding table (tied)
     notes: dict[str, str] = field(default_factory=dict)
+    #: The part that turns the step's token ids into the residual stream (``forward(ctx)``) and
+    #: the part that turns the final norm's rows into float32 logits (``forward(normed, ctx)``).
+    #: Left ``None`` they are a plain table lookup named ``embedding_name`` and a linear head
+    #: named ``head_name`` (tied to the table when that is ``None``). An architecture with
+    #: another kind of embedding or head passes its own parts and names their tensors in ``names``.
+    embedding: Part | None = None
+    head: Part | None = None
+
+    def __post_init__(self) -> None:
+        from paged_kv_serving_b200.parts.io import LinearHead, TokenEmbedding
+
+        if self.embedding is None:
+            self.embedding = TokenEmbedding(self.vocab_size, self.width)
+            self.names[self.embedding_name] = (self.embedding, "table")
+        if self.head is None:
+            tied = self.embedding if self.head_name is None and isinstance(self.embedding, TokenEmbedding) else None
+            if self.head_name is None and tied is None:
+                raise ValueError("a head tied to the embedding needs the plain embedding part, or a head of its own")
+            self.head = LinearHead(self.vocab_size, self.width, tied=tied)
+            if self.head_name is not None:
+                self.names[self.head_name] = (self.head, "weight")
 
     def tensor_specs(self) -> dict[str, ParamSpec]:
-        specs = {self.embedding_name: ParamSpec((self.vocab_size, self.width))}
-        if self.head_name is not None:
-            specs[self.head_name] = ParamSpec((self.vocab_size, self.width))
-        for name, (part, local) in self.names.items():
-            specs[name] = part.param_specs()[local]
-        return specs
+        return {name: part.param_specs()[local] for name, (part, local) in self.names.items()}
 
     def parameter_count(self) -> int:
         """Number of parameters in the tensors of a model folder (a tied head counts once)."""

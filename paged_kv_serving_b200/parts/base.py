@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 __all__ = [
-    "CacheBinding", "GroupView", "IntArena", "Normed", "PagedKVRequest", "ParamSpec", "Part", "StateRequest",
+    "Block", "CacheBinding", "GroupView", "IntArena", "Normed", "PagedKVRequest", "ParamSpec", "Part", "StateRequest",
     "StepContext",
 ]
 
@@ -106,6 +106,39 @@ class Normed:
 
     values: torch.Tensor
     norm: object
+
+
+class Block(Part):
+    """The arrangement of the parts of one layer, and the interface the step function runs.
+
+    The residual stream ``hidden`` is a float32 tensor ``[tokens, width]`` that blocks update in
+    place. A residual add is never a kernel of its own: whoever produces an update hands it on as
+    *pending*, and the norm that follows adds it while it normalises. Between blocks that means:
+
+    * ``forward(hidden, pending, ctx, binding, next_norm=None)`` receives what the block before
+      handed on: ``None`` (the first block: the stream holds the embeddings), a tensor (that
+      block's last update, not yet added to ``hidden``), or a ``Normed`` (that block already added
+      its update and applied ``first_norm`` of this block; ``Normed.norm`` says which norm it was,
+      and a block that is handed a ``Normed`` made for another norm must refuse it).
+    * It returns its own last update as a tensor, or, when ``next_norm`` was given (the
+      ``first_norm`` of the block that runs next) and it could apply it in the tail of its last
+      kernel, a ``Normed(values, next_norm)``. A block may always ignore ``next_norm`` and
+      return a tensor.
+    * ``first_norm`` is the norm the block applies to the stream it is given, or ``None`` when it
+      has none that a predecessor could apply for it (the step function then never passes
+      ``next_norm`` to the block before).
+
+    The last block's update is added by the model's final norm. ``plan_step`` and
+    ``cache_request`` are those of ``Part``; a block usually passes them on to its mixer.
+    """
+
+    @property
+    def first_norm(self) -> "Part | None":
+        return None
+
+    def forward(self, hidden: torch.Tensor, pending: "torch.Tensor | Normed | None", ctx: "StepContext",
+                binding: "CacheBinding | None", next_norm: "Part | None" = None) -> "torch.Tensor | Normed":
+        raise NotImplementedError
 
 
 class IntArena:
@@ -232,6 +265,11 @@ class StepContext:
     #: When set, parts plan launch shapes from this context length instead of the batch's own
     #: (a captured graph must keep its launch shapes from step to step).
     planning_context_len: int | None = None
+    #: The device's status word (int32 [1]): kernels record a fault code there instead of trapping.
+    status: torch.Tensor | None = None
+    #: Where the sampler of the step before left its ids; a token whose ``TOKEN_FEEDBACK`` entry
+    #: is not negative takes its id from there (see ``ModelRunner.sampled_ids``).
+    fed_back_ids: torch.Tensor | None = None
 
     # the arrays every step has (names in the arena)
     TOKEN_IDS = "token_ids"

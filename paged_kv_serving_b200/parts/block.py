@@ -6,19 +6,19 @@ import torch
 
 from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
-from paged_kv_serving_b200.parts.base import CacheBinding, Normed, Part, StepContext
+from paged_kv_serving_b200.parts.base import Block, CacheBinding, Normed, Part, StepContext
 
 __all__ = ["PreNormBlock"]
 
 
 @register_part("block", "prenorm_residual")
-class PreNormBlock(Part):
+class PreNormBlock(Block):
     """Pre-norm residual arrangement: ``h += mixer(norm(h)); h += feed_forward(norm(h))``
     (reference: src/paged_kv_serving/engine/model.py:283-287, src/paged_kv_serving/engine/runner.py:213-214).
 
-    The residual stream ``hidden`` is float32 and is updated in place. Each residual add is
-    fused with the norm that follows it: a block receives the previous block's output as a
-    pending ``delta`` and returns its own feed-forward output as the next pending delta.
+    The hand-over between blocks (pending updates, ``Normed``) is the one ``parts.base.Block``
+    describes: a block receives the previous block's output as a pending update and returns its
+    own feed-forward output as the next one, or the stream already normalised for the next block.
     """
 
     @property

@@ -421,3 +421,63 @@ def test_layer_order_may_repeat_a_layer_and_read_another_layers_cache():
     got = [session.step([{"id": "s", "tokens": tokens[:23], "want": [22]}])]
     got += [session.step([{"id": "s", "tokens": [t], "want": [0]}]) for t in tokens[23:]]
     helpers.assert_close(np.concatenate(got), want[22:], "float32", "shared cache order")
+
+
+def test_an_architecture_brings_its_own_embedding_and_head():
+    """An embedding scaled by sqrt(width) and a head with a soft cap on its logits, both defined in
+    this file, in an architecture registered from this file: the step function asks the layout for
+    its two ends and knows nothing of what they do."""
+    from paged_kv_serving_b200.config import ModelConfig, registry
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+    from paged_kv_serving_b200.parts import LinearHead, TokenEmbedding
+
+    cap = 3.0
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, ctx):
+            return super().forward(ctx) * math.sqrt(self.width)
+
+    class CappedHead(LinearHead):
+        def forward(self, normed, ctx):
+            return cap * torch.tanh(super().forward(normed, ctx) / cap)
+
+    if "ToyCappedDecoder" not in registry.known_architectures():
+        @registry.register_architecture("ToyCappedDecoder")
+        class ToyCappedDecoder:
+            @staticmethod
+            def layout(config):
+                base = registry.architecture("LlamaToyDecoder").layout(config)
+                names = {name: target for name, target in base.names.items()
+                         if target[0] is not base.embedding and target[0] is not base.head}
+                embedding = ScaledEmbedding(config.vocab_size, config.d_model)
+                head = CappedHead(config.vocab_size, config.d_model)           # a head of its own, not tied
+                names["tokens.table"] = (embedding, "table")
+                names["capped_head.weight"] = (head, "weight")
+                from paged_kv_serving_b200.models.layout import ModelLayout
+
+                return ModelLayout(width=base.width, vocab_size=base.vocab_size, max_positions=base.max_positions,
+                                   blocks=base.blocks, order=base.order, final_norm=base.final_norm, names=names,
+                                   embedding=embedding, head=head)
+
+    config = dict(helpers.TINY_B, architecture="ToyCappedDecoder")
+    tensors = helpers.tensors_for("B", "float32")
+    rng = np.random.default_rng(4)
+    head_weight = (rng.standard_normal(tensors["token_embedding"].shape) * 0.3).astype(np.float32)
+    mine = {("tokens.table" if k == "token_embedding" else k): v for k, v in tensors.items()}
+    mine["capped_head.weight"] = head_weight
+    model = DecoderModel.from_tensors(ModelConfig.from_dict(config), {k: torch.from_numpy(v) for k, v in mine.items()},
+                                      "float32", "cuda")
+    tokens = helpers.random_tokens(config, 50, seed=9)
+
+    # the plain forward with the scaled embedding and the capped, untied head
+    plain_tensors = dict(tensors, token_embedding=tensors["token_embedding"] * np.float32(math.sqrt(config["d_model"])),
+                         lm_head=head_weight)
+    raw = plain_model.forward(dict(helpers.TINY_B, tie_embeddings=False), plain_tensors, tokens)
+    want = cap * np.tanh(raw / cap)
+    assert np.abs(raw).max() > cap, "the cap must bite for the test to mean anything"
+
+    session = ReplaySession(model, max_tokens=64, block_size=8)
+    got = [session.step([{"id": "s", "tokens": tokens[:31], "want": [0, 30]}])]
+    got += [session.step([{"id": "s", "tokens": [t], "want": [0]}]) for t in tokens[31:]]
+    helpers.assert_close(np.concatenate(got), want[[0] + list(range(30, 50))], "float32", "own embedding and head")
