@@ -1,9 +1,12 @@
 // What the decode attention kernels share: the fragment helpers, a warp's running softmax state
 // and the step that folds 16 keys of a 64-key stage into it.
 //
-// A stage holds 64 keys and 64 values of one key/value head as TMA left them: per 64-column panel
-// 64 rows of 128 bytes, the 16-byte chunks of a row swizzled by the row number (128-byte swizzle);
-// the keys' panels first, then the values'. Consumer warp w takes rows 16 w .. 16 w + 15.
+// A stage holds 64 keys and 64 values of one key/value head as TMA left them, the keys first, then
+// the values; rows of 128 bytes whose 16-byte chunks are swizzled by the row number (128-byte
+// swizzle). Head size 64 (one 64-column panel): 64 rows, one copy per page. Head size 128 (two
+// panels): groups of 8 rows, each group panel after panel (8 rows of panel 0, then of panel 1), so
+// that one copy brings a whole page (see make_panel_group_map); half as many copies per tile as
+// one per page and panel. Consumer warp w takes rows 16 w .. 16 w + 15.
 #pragma once
 
 #include "tcgen05.cuh"
@@ -59,6 +62,12 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
   constexpr uint32_t HALF_BYTES = PANELS * PANEL_BYTES;
   constexpr int KSTEPS = HD / 16;
   constexpr int DTILES = HD / 8;
+  // byte offset of 16-byte chunk `chunk` (unswizzled number, 8 per panel) of row `row` in the keys or values
+  auto chunk_at = [](int row, int chunk, int swizzled) -> uint32_t {
+    const uint32_t in_row = (uint32_t)((swizzled ? ((chunk & 7) ^ (row & 7)) : (chunk & 7)) << 4);
+    if (PANELS == 1) return (uint32_t)row * 128 + in_row;
+    return (uint32_t)(row >> 3) * (PANELS * 1024) + (uint32_t)(chunk >> 3) * 1024 + (uint32_t)(row & 7) * 128 + in_row;
+  };
   const int t4 = lane & 3;
   const uint32_t k_base = smem_addr(stage_smem);
   const uint32_t v_base = k_base + HALF_BYTES;
@@ -71,8 +80,7 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
       for (int idx = lane; idx < 16 * PANELS * 8; idx += 32) {
         const int r = idx / (PANELS * 8), c = idx - r * (PANELS * 8);
         if (wbase + r >= key_hi)
-          *reinterpret_cast<uint4*>(stage_smem + HALF_BYTES + (c >> 3) * PANEL_BYTES +
-                                    (warp * 16 + r) * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(stage_smem + HALF_BYTES + chunk_at(warp * 16 + r, c, 0)) = make_uint4(0u, 0u, 0u, 0u);
       }
       __syncwarp();
     }
@@ -83,7 +91,7 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
       const int krow = warp * 16 + (lane & 7) + 8 * (lane >> 4);
       const int chunk = kk * 2 + ((lane >> 3) & 1);
       uint32_t b[4];
-      ldsm_x4(b, k_base + (chunk >> 3) * PANEL_BYTES + krow * 128 + (((chunk & 7) ^ (krow & 7)) << 4));
+      ldsm_x4(b, k_base + chunk_at(krow, chunk, 1));
       mma16816(sc[0], qa[kk], b[0], b[1]);
       mma16816(sc[1], qa[kk], b[2], b[3]);
     }
@@ -127,7 +135,7 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
       const int vrow = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
       const int chunk = dd * 2 + (lane >> 4);
       uint32_t b[4];
-      ldsm_x4_trans(b, v_base + (chunk >> 3) * PANEL_BYTES + vrow * 128 + (((chunk & 7) ^ (vrow & 7)) << 4));
+      ldsm_x4_trans(b, v_base + chunk_at(vrow, chunk, 1));
       o[2 * dd][0] *= resc_a; o[2 * dd][1] *= resc_a; o[2 * dd][2] *= resc_b; o[2 * dd][3] *= resc_b;
       o[2 * dd + 1][0] *= resc_a; o[2 * dd + 1][1] *= resc_a; o[2 * dd + 1][2] *= resc_b; o[2 * dd + 1][3] *= resc_b;
       mma16816(o[2 * dd], a, b[0], b[1]);
@@ -137,8 +145,9 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
 }
 
 // Tensor maps over the page pools, one per (pool, size): [rows = pages x kv heads x page size,
-// head size], boxes of one page of one 64-column panel. Kept for the life of the library, since a
-// captured graph holds them by value and a step asks for the same few again and again.
+// head size], boxes of one page: of its one 64-column panel (head size 64) or of both, group of 8
+// rows by group (head size 128). Kept for the life of the library, since a captured graph holds
+// them by value and a step asks for the same few again and again.
 struct DecMapKey {
   const void* base;
   long long rows;
@@ -152,7 +161,9 @@ static const CUtensorMap* decode_pool_map(const void* base, long long rows, int 
   for (int i = 0; i < used; ++i)
     if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) return &cache[i].map;
   DecMapKey& slot = cache[used < 512 ? used : 511];
-  if (make_tile_map(&slot.map, base, rows, hd, hd, box_rows)) return nullptr;
+  const int rc = hd == 128 ? make_panel_group_map(&slot.map, base, rows, 2, box_rows)
+                           : make_tile_map(&slot.map, base, rows, hd, hd, box_rows);
+  if (rc) return nullptr;
   slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows;
   if (used < 512) ++used;
   return &slot.map;

@@ -133,17 +133,20 @@ attention_decode_flat_kernel(const __grid_constant__ CUtensorMap map_k, const __
       wait_for_prior_kernels();     // the newest keys and values come from the kernel before this one
       const int pw = warp - 4;
       const int pages_per_tile = DT_BN / p.page_size;
-      const int boxes = pages_per_tile * PANELS * 2;      // keys and values
+      // one box per page and panel, or (two panels) one box per page over both panels
+      constexpr int BOX_PANELS = PANELS == 2 ? 2 : 1, BOXES_PER_PAGE = PANELS / BOX_PANELS;
+      const int boxes = pages_per_tile * BOXES_PER_PAGE * 2;      // keys and values
       const int my_boxes = (boxes - pw + DF_PRODUCERS - 1) / DF_PRODUCERS;
-      const uint32_t my_bytes = (uint32_t)my_boxes * p.page_size * 128;
+      const uint32_t my_bytes = (uint32_t)my_boxes * p.page_size * 128 * BOX_PANELS;
       // at most 32 boxes a tile: one a lane; what does not change from tile to tile is worked out once
       const int box = pw + lane * DF_PRODUCERS;
       const bool has_box = box < boxes;
-      const int which = box / (pages_per_tile * PANELS);  // 0: keys, 1: values
-      const int rest = box - which * pages_per_tile * PANELS;
-      const int page_in_tile = rest / PANELS, pn = rest - page_in_tile * PANELS;
+      const int which = box / (pages_per_tile * BOXES_PER_PAGE);  // 0: keys, 1: values
+      const int rest = box - which * pages_per_tile * BOXES_PER_PAGE;
+      const int page_in_tile = rest / BOXES_PER_PAGE, pn = rest - page_in_tile * BOXES_PER_PAGE;
       const int key_in_tile = page_in_tile * p.page_size;
-      const uint32_t dst_offset = which * HALF_BYTES + pn * PANEL_BYTES + key_in_tile * 128;
+      const uint32_t dst_offset = which * HALF_BYTES +
+                                  (PANELS == 2 ? (uint32_t)(key_in_tile >> 3) * 2048 : pn * PANEL_BYTES + key_in_tile * 128);
       const CUtensorMap* map = which ? &map_v : &map_k;
       bool ok = true;
       while (left > 0 && ok) {
@@ -177,7 +180,10 @@ attention_decode_flat_kernel(const __grid_constant__ CUtensorMap map_k, const __
               }
               ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
               if (ok) {
-                if (has_box) tma_load_2d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 64 * pn, row);
+                if (has_box) {
+                  if (PANELS == 2) tma_load_4d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 0, 0, 0, row >> 3);
+                  else tma_load_2d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 64 * pn, row);
+                }
                 __syncwarp();
                 ++j;
               }

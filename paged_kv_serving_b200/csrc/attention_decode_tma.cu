@@ -151,18 +151,21 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // consumers need for the tile: the producer warps share the boxes.
     const int pw = warp - 4;
     const int pages_per_tile = DT_BN / p.page_size;
-    const int boxes = pages_per_tile * PANELS * 2;      // keys and values
+    // one box per page and panel, or (two panels) one box per page over both panels
+    constexpr int BOX_PANELS = PANELS == 2 ? 2 : 1, BOXES_PER_PAGE = PANELS / BOX_PANELS;
+    const int boxes = pages_per_tile * BOXES_PER_PAGE * 2;      // keys and values
     const int my_boxes = (boxes - pw + DT_PRODUCERS - 1) / DT_PRODUCERS;
-    const uint32_t my_bytes = (uint32_t)my_boxes * p.page_size * 128;
+    const uint32_t my_bytes = (uint32_t)my_boxes * p.page_size * 128 * BOX_PANELS;
     // at most 32 boxes a tile (pages of 8 keys, two panels, keys and values): one box a lane,
     // and what does not change from tile to tile is worked out once
     const int b = pw + lane * DT_PRODUCERS;
     const bool has_box = b < boxes;
-    const int which = b / (pages_per_tile * PANELS);              // 0: keys, 1: values
-    const int rest = b - which * pages_per_tile * PANELS;
-    const int page_in_tile = rest / PANELS, pn = rest - page_in_tile * PANELS;
+    const int which = b / (pages_per_tile * BOXES_PER_PAGE);              // 0: keys, 1: values
+    const int rest = b - which * pages_per_tile * BOXES_PER_PAGE;
+    const int page_in_tile = rest / BOXES_PER_PAGE, pn = rest - page_in_tile * BOXES_PER_PAGE;
     const int key_in_tile = page_in_tile * p.page_size;
-    const uint32_t dst_offset = which * HALF_BYTES + pn * PANEL_BYTES + key_in_tile * 128;
+    const uint32_t dst_offset = which * HALF_BYTES +
+                                (PANELS == 2 ? (uint32_t)(key_in_tile >> 3) * 2048 : pn * PANEL_BYTES + key_in_tile * 128);
     const CUtensorMap* map = which ? &map_v : &map_k;
     bool ok = true;
     int issued = 0;
@@ -182,7 +185,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
           if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
         }
-        tma_load_2d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 64 * pn, row);
+        if (PANELS == 2) tma_load_4d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 0, 0, 0, row >> 3);
+        else tma_load_2d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 64 * pn, row);
       }
       __syncwarp();
       issued = j + 1;
