@@ -152,18 +152,19 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const D* __re
   }
 }
 
-// Completes an RMS norm that a matrix-product kernel left in two pieces (csrc/gemm_small_m.cu,
-// residual epilogue): `xw` is the stream times the norm's weight, `sumsq[part][row]` the sums of
-// squares of the stream per 16-column tile. out = xw / sqrt(sum / d + eps). One block per row.
-__global__ void finish_norm_kernel(const bf16* __restrict__ xw, const float* __restrict__ sumsq, int parts, float eps,
-                                   bf16* __restrict__ out, int d) {
+// Completes an RMS norm that a matrix-product kernel left in two pieces (the residual epilogues
+// of csrc/gemm_small_m.cu and csrc/gemm_stream.cu): `xw` is the stream times the norm's weight,
+// `sumsq[part * stride + row]` the sums of squares of the stream per tile of columns.
+// out = xw / sqrt(sum / d + eps). One block per row.
+__global__ void finish_norm_kernel(const bf16* __restrict__ xw, const float* __restrict__ sumsq, int parts, int stride,
+                                   float eps, bf16* __restrict__ out, int d) {
   dependents_may_launch();
   wait_for_prior_kernels();
   __shared__ float inv_root;
   const int row = blockIdx.x;
   if (threadIdx.x < 32) {   // the same order of additions as the product kernel that reads these sums
     float q = 0.0f;
-    for (int part = threadIdx.x; part < parts; part += 32) q += sumsq[part * 32 + row];
+    for (int part = threadIdx.x; part < parts; part += 32) q += sumsq[(size_t)part * stride + row];
     q = warp_sum(q);
     if (threadIdx.x == 0) inv_root = 1.0f / sqrtf(q / (float)d + eps);
   }
@@ -389,12 +390,12 @@ PKV_EXPORT int pkv_add_rmsnorm(float* hidden, const void* delta, int delta_dtype
   return PKV_ERR_DTYPE;
 }
 
-PKV_EXPORT int pkv_finish_norm(const void* xw, const float* sumsq, int parts, float eps, void* out, int n_rows, int d,
-                               void* stream) {
+PKV_EXPORT int pkv_finish_norm(const void* xw, const float* sumsq, int parts, int stride, float eps, void* out, int n_rows,
+                               int d, void* stream) {
   if (n_rows <= 0) return 0;
-  if (d <= 0 || parts <= 0 || n_rows > 32) return PKV_ERR_SIZE;
+  if (d <= 0 || parts <= 0 || n_rows > stride) return PKV_ERR_SIZE;
   return launch_kernel(finish_norm_kernel, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, true, 0, (const bf16*)xw, sumsq,
-                       parts, eps, (bf16*)out, d);
+                       parts, stride, eps, (bf16*)out, d);
 }
 
 PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, int ff, int in_stride,

@@ -26,7 +26,7 @@ __all__ = [
     "attention_prefill_bf16", "attention_prefill_tcgen05", "attention_rows_per_block", "attention_tcgen05_narrow_boxes",
     "attention_tcgen05_rows",
     "attention_tcgen05_supports", "build_all", "copy_page", "dtype_code", "embedding_gather", "finish_norm", "gemm_small_m", "gemm_small_m_supports",
-    "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
+    "gemm_stream", "gemm_stream_supports", "gemm_tcgen05", "gemm_tcgen05_supports", "gemm_workspace",
     "launch_count", "library", "library_names", "paged_attention_generic", "raise_for_status", "reset_workspaces",
     "rope_kv_store", "sample", "silu_mul", "status_word", "wait_probe",
 ]
@@ -207,7 +207,7 @@ def reset_workspaces(device: torch.device | str) -> None:
     key = str(torch.device(device))
     for kept in _DECODE_FLAT_SCRATCH.get(key, []):
         kept[1].zero_()
-    for table in (_GEMM_WORKSPACE, _SMALL_M_WORKSPACE):
+    for table in (_GEMM_WORKSPACE, _SMALL_M_WORKSPACE, _STREAM_WORKSPACE):
         if key in table:
             table[key].zero_()
 
@@ -712,14 +712,100 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
     return (out, sumsq_out) if residual is not None else out
 
 
+STREAM_MAX_ROWS = 128
+_STREAM_WORKSPACE: dict[str, torch.Tensor] = {}
+
+
+def gemm_stream_supports(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16") -> bool:
+    """Whether the tcgen05 weight-streaming product takes these operands: bfloat16, 1 to 128 rows, an
+    inner size that is a multiple of 64, contiguous weights, 16-byte aligned rows (and, for the fused
+    activation, gate and up rows interleaved in blocks of 128)."""
+    return (a.dtype == torch.bfloat16 and b_nk.dtype == torch.bfloat16 and a.dim() == 2 and b_nk.dim() == 2
+            and 0 < a.shape[0] <= STREAM_MAX_ROWS and a.shape[1] % 64 == 0 and a.stride(1) == 1 and a.stride(0) % 8 == 0
+            and b_nk.is_contiguous() and a.data_ptr() % 16 == 0 and b_nk.data_ptr() % 16 == 0
+            and (epilogue != "silu_mul" or b_nk.shape[0] % 256 == 0))
+
+
+def _stream_workspace(device: torch.device) -> torch.Tensor:
+    """Partial accumulators and tile counters of ``gemm_stream`` on a device: allocated and zeroed
+    once, left zero by every launch, shared by the launches of a stream."""
+    _one_stream(device)
+    key = str(torch.device(device))
+    if key not in _STREAM_WORKSPACE:
+        lib = library("gemm_stream")
+        lib.pkv_gemm_stream_workspace_bytes.restype = c_longlong
+        lib.pkv_gemm_stream_workspace_bytes.argtypes = [c_int]
+        size = int(lib.pkv_gemm_stream_workspace_bytes(STREAM_MAX_ROWS))
+        _STREAM_WORKSPACE[key] = torch.zeros((size,), dtype=torch.uint8, device=device)
+    return _STREAM_WORKSPACE[key]
+
+
+def gemm_stream(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epilogue: str = "bf16", n_out: int = 0,
+                clip: float = 60.0, chained: bool = True, residual: tuple[torch.Tensor, torch.Tensor] | None = None,
+                row_norm: tuple[torch.Tensor, float] | None = None):
+    """``a [M, K] @ b_nk [N, K]^T`` for 1 to 128 rows on the tcgen05 tensor cores with the operands
+    swapped: tiles of 128 weight rows are the tall side of the MMA, the weights stream through a
+    TMA ring, every weight is read once. Epilogues ``"bf16"``, ``"f32"``, ``"silu_mul"`` as in
+    ``gemm_tcgen05``.
+
+    ``residual = (hidden, norm_weight)``: the product is added to the float32 stream ``hidden
+    [M, N]`` in place; returned are ``hidden * norm_weight`` in bfloat16 and the sums of squares of
+    the new stream per 128-column tile and row, ``[ceil(N / 128), 128]``. ``row_norm = (sumsq,
+    eps)`` with such sums ``[parts, stride]`` (this kernel's or ``gemm_small_m``'s): the rows of the
+    result are divided by ``sqrt(sum / K + eps)``."""
+    if residual is not None:
+        epilogue = "residual"
+    if epilogue not in GEMM_EPILOGUES and epilogue != "residual":
+        raise ValueError(f"unknown epilogue {epilogue!r}")
+    for name, t in (("a", a), ("b_nk", b_nk)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a bfloat16 CUDA matrix with contiguous rows")
+    if not b_nk.is_contiguous():
+        raise ValueError("b_nk must be contiguous")
+    _need(status, torch.int32, "status")
+    m, k = a.shape
+    n = b_nk.shape[0]
+    if b_nk.shape[1] != k:
+        raise ValueError("inner sizes differ")
+    hidden = weight = sumsq_out = sumsq_in = None
+    parts, in_stride, eps = 0, 0, 0.0
+    if residual is not None:
+        hidden, weight = residual
+        _need(hidden, torch.float32, "hidden"); _need(weight, torch.float32, "norm weight")
+        if hidden.shape != (m, n) or weight.numel() != n:
+            raise ValueError("the residual epilogue needs a stream and a norm weight as wide as the product")
+        sumsq_out = torch.empty((-(-n // 128), 128), dtype=torch.float32, device=a.device)
+    if row_norm is not None:
+        sumsq_in, eps = row_norm
+        _need(sumsq_in, torch.float32, "sums of squares")
+        if sumsq_in.dim() != 2 or sumsq_in.shape[1] < m:
+            raise ValueError("sums of squares must be [parts, at least as many columns as rows]")
+        parts, in_stride = sumsq_in.shape
+    if epilogue == "silu_mul":
+        out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
+    else:
+        out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
+    fn = _fn("gemm_stream", "pkv_gemm_stream",
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
+              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    workspace = _stream_workspace(a.device)
+    code = 3 if epilogue == "residual" else GEMM_EPILOGUES[epilogue]
+    _check(fn(_ptr(a), a.stride(0), _ptr(b_nk), _ptr(out), m, n, k, code, int(n_out), float(clip), 1 if chained else 0,
+              _ptr(workspace), workspace.numel(), _ptr(hidden), _ptr(weight), _ptr(sumsq_out),
+              sumsq_out.shape[1] if sumsq_out is not None else 0, _ptr(sumsq_in), parts, in_stride, k, float(eps),
+              _ptr(status), _stream()), "gemm_stream")
+    return (out, sumsq_out) if residual is not None else out
+
+
 def finish_norm(xw: torch.Tensor, sumsq: torch.Tensor, eps: float) -> torch.Tensor:
-    """The RMS-normalised rows from the two pieces that ``gemm_small_m(..., residual=...)`` leaves:
+    """The RMS-normalised rows from the two pieces that ``gemm_small_m(..., residual=...)`` or
+    ``gemm_stream(..., residual=...)`` leaves (``sumsq [parts, stride]``):
     ``xw / sqrt(sum(sumsq) / width + eps)``, bfloat16."""
     _need(xw, torch.bfloat16, "xw"); _need(sumsq, torch.float32, "sums of squares")
     rows, d = xw.shape
     out = torch.empty_like(xw)
-    fn = _fn("elementwise", "pkv_finish_norm", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(_ptr(xw), _ptr(sumsq), sumsq.shape[0], float(eps), _ptr(out), rows, d, _stream()), "finish_norm")
+    fn = _fn("elementwise", "pkv_finish_norm", [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(xw), _ptr(sumsq), sumsq.shape[0], sumsq.shape[1], float(eps), _ptr(out), rows, d, _stream()), "finish_norm")
     return out
 
 

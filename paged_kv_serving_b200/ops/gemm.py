@@ -5,7 +5,8 @@ least ``TCGEN05_MIN_ROWS`` rows of activations (prompt portions) can run on the 
 tcgen05/TMA kernels of ``csrc/gemm_tcgen05.cu``: the gate/up product of the feed-forward always
 does, with its SiLU-times-up step fused into the epilogue, the plain products when
 ``PLAIN_PRODUCT_KERNEL`` says so. The up to ``SMALL_M_ROWS`` rows of a decode step go to the
-weight-streaming kernel of ``csrc/gemm_small_m.cu``. Everything else, and the float32 path, goes to cuBLAS
+weight-streaming kernel of ``csrc/gemm_small_m.cu``; a tcgen05 twin of it for up to 128 rows
+(``csrc/gemm_stream.cu``) stands behind the switch ``STREAM_ROWS``. Everything else, and the float32 path, goes to cuBLAS
 through ``torch.mm``, as the reference's engine hands its products to a library
 (src/paged_kv_serving/engine/model.py:249,258-259,264). Reduced-precision modes are switched
 off: float32 products use true float32 multiply-adds (no TF32), bfloat16 products accumulate in
@@ -46,14 +47,30 @@ SMALL_M_ROWS = 8
 #: Whether that kernel is launched as a programmatic dependent where the caller asks for it
 #: (``chain=True``).
 SMALL_M_CHAINED = True
+#: Products of ``SMALL_M_ROWS + 1`` to this many rows go to the tcgen05 weight-streaming kernel of
+#: ``csrc/gemm_stream.cu`` (tiles of 128 weight rows as the tall side of the MMA, weights through a
+#: TMA ring, the fused residual / norm / activation epilogues that cuBLAS cannot carry); 0, the
+#: default, leaves them with cuBLAS. Measured at the sizes of an 8-billion-parameter model: a ring
+#: of 16 KB TMA boxes alone streams the gate/up weights in 35.6 us (6.6 TB/s), but every tile of
+#: the product is shared by two or three blocks (112 pairs of tiles on 148 SMs) and settling the
+#: partial accumulators through the workspace costs 4 us at the end of the kernel: 43 to 45 us at 8
+#: and 16 rows, level with the kernel above (43) and cuBLAS + activation kernel (42). The smaller
+#: products pay the same fixed cost on less work (output projection 12.5 us against 7.6 and 9.2).
+#: Inside a decode step of 16 or 32 rows the kernel is slower than the cuBLAS path (4.23 against
+#: 3.81 ms, 5.06 against 4.34 ms a step), and mixed with the kernel above in steps of up to 8 rows
+#: it slows that kernel down (the two want opposite divisions of an SM's memory between L1 and
+#: shared memory). What it needs to pay off is a cheaper settle (the blocks that share a tile as
+#: one thread-block cluster, partial accumulators through distributed shared memory).
+STREAM_ROWS = 0
 
 
 class PendingNorm:
     """RMS-normalised rows that have not been divided by their root mean square yet: ``weighted``
-    is the stream times the norm's weight (bfloat16), ``sumsq [parts, 32]`` the sums of squares
-    of the stream per 16-column tile and row. ``linear`` and ``linear_silu_mul`` take it in place
-    of a tensor and divide their result rows instead (a product is linear in its rows); anything
-    else calls ``tensor()``."""
+    is the stream times the norm's weight (bfloat16), ``sumsq [parts, stride]`` the sums of squares
+    of the stream per tile of columns and row (``gemm_small_m`` leaves tiles of 16 columns and a
+    stride of 32, ``gemm_stream`` tiles of 128 columns and a stride of 128). ``linear`` and
+    ``linear_silu_mul`` take it in place of a tensor and divide their result rows instead (a
+    product is linear in its rows); anything else calls ``tensor()``."""
 
     __slots__ = ("weighted", "sumsq", "eps")
 
@@ -79,6 +96,11 @@ def as_tensor(x: "torch.Tensor | PendingNorm") -> torch.Tensor:
 def _small_m(x: torch.Tensor, w_nk: torch.Tensor, epilogue: str) -> bool:
     return (USE_TCGEN05 and x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
             and ops.gemm_small_m_supports(x, w_nk, epilogue))
+
+
+def _stream(x: torch.Tensor, w_nk: torch.Tensor, epilogue: str) -> bool:
+    return (USE_TCGEN05 and x.dtype == torch.bfloat16 and SMALL_M_ROWS < x.shape[0] <= STREAM_ROWS
+            and ops.gemm_stream_supports(x, w_nk, epilogue))
 
 
 def _own_kernel(x: torch.Tensor, w_nk: torch.Tensor) -> bool:
@@ -110,12 +132,17 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
     keeps the small L1 and streams at half speed, and so do the products chained after it."""
     wants_f32 = out_dtype == torch.float32
     if isinstance(x, PendingNorm):
-        if not wants_f32 and _small_m(x.weighted, w_nk, "bf16"):
+        if not wants_f32 and x.sumsq.shape[1] == 32 and _small_m(x.weighted, w_nk, "bf16"):
             return ops.gemm_small_m(x.weighted, w_nk, "bf16", chained=SMALL_M_CHAINED and chain,
                                     row_norm=(x.sumsq, x.eps))
+        if not wants_f32 and _stream(x.weighted, w_nk, "bf16"):
+            return ops.gemm_stream(x.weighted, w_nk, ops.status_word(w_nk.device), "bf16",
+                                   chained=SMALL_M_CHAINED and chain, row_norm=(x.sumsq, x.eps))
         x = x.tensor()
     if not wants_f32 and _small_m(x, w_nk, "bf16"):
         return ops.gemm_small_m(x, w_nk, "bf16", chained=SMALL_M_CHAINED and chain)
+    if not wants_f32 and _stream(x, w_nk, "bf16"):
+        return ops.gemm_stream(x, w_nk, ops.status_word(w_nk.device), "bf16", chained=SMALL_M_CHAINED and chain)
     # rows of the output must start on 16-byte boundaries for the kernel's vector stores
     if (PLAIN_PRODUCT_KERNEL == "tcgen05" and w_nk.shape[0] % (4 if wants_f32 else 8) == 0
             and _own_kernel(x, w_nk)):
@@ -132,10 +159,15 @@ def linear_rope_kv_store(x: "torch.Tensor | PendingNorm", w_nk: torch.Tensor, po
     pools at ``slots``. For the few rows of a decode step one kernel does both."""
     fused_ok = head_dim % 16 == 0 and k_pool.dtype == torch.bfloat16
     if isinstance(x, PendingNorm):
-        if fused_ok and _small_m(x.weighted, w_nk, "bf16"):
+        if fused_ok and x.sumsq.shape[1] == 32 and _small_m(x.weighted, w_nk, "bf16"):
             return ops.gemm_small_m(x.weighted, w_nk, chained=SMALL_M_CHAINED and chain,
                                     row_norm=(x.sumsq, x.eps),
                                     rope_kv=(positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size))
+        elif _stream(x.weighted, w_nk, "bf16"):
+            # the product divides its rows itself; rotation and cache write follow as their own kernel
+            qkv = linear(x, w_nk, chain=chain)
+            ops.rope_kv_store(qkv, positions, cos, sin, k_pool, v_pool, slots, n_heads, n_kv, head_dim, page_size)
+            return qkv
         x = x.tensor()
     if fused_ok and _small_m(x, w_nk, "bf16"):
         return ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and chain,
@@ -157,6 +189,11 @@ def linear_add_norm(x: torch.Tensor, w_nk: torch.Tensor, hidden: torch.Tensor, n
         weighted, sumsq = ops.gemm_small_m(x, w_nk, chained=SMALL_M_CHAINED and chain,
                                            residual=(hidden, norm_weight))
         return PendingNorm(weighted, sumsq, eps)
+    if out_dtype == torch.bfloat16 and w_nk.shape[0] % 64 == 0 and _stream(x, w_nk, "bf16"):
+        # (the stream's width is the inner size of the tcgen05 product that reads it: a multiple of 64)
+        weighted, sumsq = ops.gemm_stream(x, w_nk, ops.status_word(w_nk.device), chained=SMALL_M_CHAINED and chain,
+                                          residual=(hidden, norm_weight))
+        return PendingNorm(weighted, sumsq, eps)
     return ops.add_rmsnorm(hidden, linear(x, w_nk, chain=chain), norm_weight, eps, out_dtype)
 
 
@@ -165,10 +202,16 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleav
     """``silu(x @ gate^T) * (x @ up^T)`` for gate and up rows held in one matrix (``interleave``
     as in ``ops.silu_mul``); ``[T, ff]``."""
     if isinstance(x, PendingNorm):
-        if interleave == 128 and _small_m(x.weighted, w_gate_up, "silu_mul"):
+        if interleave == 128 and _stream(x.weighted, w_gate_up, "silu_mul"):
+            return ops.gemm_stream(x.weighted, w_gate_up, ops.status_word(w_gate_up.device), "silu_mul", n_out=ff,
+                                   clip=clip, chained=SMALL_M_CHAINED and chain, row_norm=(x.sumsq, x.eps))
+        if interleave == 128 and x.sumsq.shape[1] == 32 and _small_m(x.weighted, w_gate_up, "silu_mul"):
             return ops.gemm_small_m(x.weighted, w_gate_up, "silu_mul", n_out=ff, clip=clip,
                                     chained=SMALL_M_CHAINED and chain, row_norm=(x.sumsq, x.eps))
         x = x.tensor()
+    if interleave == 128 and _stream(x, w_gate_up, "silu_mul"):
+        return ops.gemm_stream(x, w_gate_up, ops.status_word(w_gate_up.device), "silu_mul", n_out=ff, clip=clip,
+                               chained=SMALL_M_CHAINED and chain)
     if interleave == 128 and _small_m(x, w_gate_up, "silu_mul"):
         return ops.gemm_small_m(x, w_gate_up, "silu_mul", n_out=ff, clip=clip,
                                 chained=SMALL_M_CHAINED and chain)

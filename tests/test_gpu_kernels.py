@@ -722,3 +722,97 @@ def test_copy_page_copies_one_page_of_every_layer_and_nothing_else(layers, pages
         ops.copy_page(k_pool, v_pool, 1, pages)          # outside the pool
     with pytest.raises(ValueError, match="size"):
         ops.copy_page(k_pool, v_pool, 2, 2)              # onto itself
+
+
+@pytest.mark.parametrize("chained", [True, False])
+@pytest.mark.parametrize("m, n, k", [(1, 128, 64), (3, 331, 192), (8, 520, 4096), (9, 100, 320), (16, 1000, 2048), (17, 72, 1792),
+                                     (32, 4096, 320), (33, 250, 64), (64, 6144, 512), (65, 3000, 256), (100, 9600, 512),
+                                     (128, 1024, 1024), (8, 28672, 4096), (4, 4096, 14336)])
+@pytest.mark.parametrize("epilogue", ["bf16", "f32"])
+def test_gemm_stream(m, n, k, epilogue, chained):
+    """The tcgen05 weight-streaming product (weights as the tall operand, 1 to 128 rows) against a
+    float64 product of the same operands: every row-count bucket and its edge, weight rows that
+    are no multiple of 128, few and many tiles (ranges that begin and end inside a tile, settled
+    through the workspace), long inner sizes; a row's result does not change with the rows beside
+    it; twice on the same workspace."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(m * 7 + n + k)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert ops.gemm_stream_supports(a, b, epilogue)
+    out = ops.gemm_stream(a, b, status, epilogue, chained=chained)
+    want = a.double() @ b.double().t()
+    scale = float(want.abs().max())
+    bound = 1e-5 * scale if epilogue == "f32" else 2 ** -8 * scale
+    assert int(status.item()) == 0
+    assert out.shape == (m, n) and float((out.double() - want).abs().max()) <= bound
+    assert torch.equal(ops.gemm_stream(a, b, status, epilogue, chained=chained), out)
+    alone = ops.gemm_stream(a[m - 1:], b, status, epilogue, chained=chained)
+    assert torch.equal(alone[0], out[m - 1])
+    wide = torch.zeros((m, k + 8), dtype=torch.bfloat16, device="cuda")
+    wide[:, :k] = a
+    assert torch.equal(ops.gemm_stream(wide[:, :k], b, status, epilogue, chained=chained), out)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("m, ff, k", [(1, 128, 64), (8, 200, 192), (13, 1000, 256), (32, 392, 2048), (20, 3000, 576),
+                                      (8, 14336, 4096), (64, 13824, 5120), (100, 1000, 512), (128, 2048, 256)])
+def test_gemm_stream_silu_mul_epilogue(m, ff, k):
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(ff + m)
+    blocks = -(-ff // 128)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    gate = torch.from_numpy(rng.standard_normal((ff, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    up = torch.from_numpy(rng.standard_normal((ff, k)).astype(np.float32) * 0.3).cuda().to(torch.bfloat16)
+    fused = torch.zeros((blocks, 2, 128, k), dtype=torch.bfloat16, device="cuda")
+    for b in range(blocks):
+        rows = min(128, ff - 128 * b)
+        fused[b, 0, :rows] = gate[128 * b:128 * b + rows]
+        fused[b, 1, :rows] = up[128 * b:128 * b + rows]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.gemm_stream(a, fused.view(-1, k), status, "silu_mul", n_out=ff)
+    g, u = (a.float() @ gate.float().t()).cpu().numpy(), (a.float() @ up.float().t()).cpu().numpy()
+    want = plain_model.silu(g) * u
+    assert int(status.item()) == 0 and out.shape == (m, ff)
+    assert np.abs(as_np(out) - want).max() <= 2 ** -8 * np.abs(want).max() + 1e-6
+    assert torch.equal(ops.gemm_stream(a, fused.view(-1, k), status, "silu_mul", n_out=ff), out)
+
+
+@pytest.mark.parametrize("m, d, k, n", [(1, 128, 64, 48), (5, 352, 192, 100), (8, 4096, 512, 256), (13, 992, 64, 520),
+                                        (32, 256, 2048, 72), (8, 4096, 14336, 256), (64, 5120, 13824, 64), (100, 640, 256, 333),
+                                        (128, 384, 128, 128)])
+def test_gemm_stream_residual_epilogue_and_row_norm(m, d, k, n):
+    """Residual add, RMS norm and the next product in two launches, as with the kernel for few
+    rows: the first product adds itself to the float32 stream and leaves the stream times the
+    norm's weight with per-tile sums of squares; the second divides its rows by the root mean
+    square. Against the plain formulas, twice in a row on the same stream."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(m + d)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((d, k)).astype(np.float32) * 0.2).cuda().to(torch.bfloat16)
+    d_pad = -(-d // 64) * 64
+    nxt = torch.zeros((n, d_pad), dtype=torch.bfloat16, device="cuda")
+    nxt[:, :d] = torch.from_numpy(rng.standard_normal((n, d)).astype(np.float32) * 0.2).cuda().to(torch.bfloat16)
+    weight = torch.from_numpy((1 + 0.1 * rng.standard_normal(d)).astype(np.float32)).cuda()
+    stream = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float32)).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    eps = 1e-5
+    for _ in range(2):
+        before = as_np(stream)
+        weighted, sumsq = ops.gemm_stream(a, b, status, residual=(stream, weight))
+        product = (a.double() @ b.double().t()).cpu().numpy()
+        want_stream = before + product
+        assert np.abs(as_np(stream) - want_stream).max() <= 2e-6 * max(1.0, (k / 2048) ** 0.5) * np.abs(want_stream).max()
+        assert sumsq.shape == (-(-d // 128), 128)
+        assert np.allclose(as_np(sumsq)[:, :m].sum(axis=0), (want_stream ** 2).sum(axis=1), rtol=1e-5)
+        want_normed = plain_model.rms_norm(want_stream.astype(np.float32), as_np(weight), eps)
+        if d % 64 == 0:
+            got = ops.gemm_stream(weighted, nxt, status, "f32", row_norm=(sumsq, eps))
+            # row_norm divides by sqrt(sum / K + eps) with K the inner size of the product that reads it
+            want = want_normed.astype(np.float64) @ as_np(nxt)[:, :d].astype(np.float64).T
+            assert np.abs(as_np(got) - want).max() <= 2 ** -7 * np.abs(want).max() + 1e-5
+    assert int(status.item()) == 0

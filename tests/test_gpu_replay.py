@@ -222,3 +222,34 @@ def test_even_shares_decode_attention_in_the_engine(monkeypatch, use_graphs):
     for i, p in enumerate(prompts):
         want = plain_model.forward(helpers.TINY_D, tensors, p)
         helpers.assert_close(np.stack(got[i]), want[len(p) - 40:], "bfloat16", f"even shares, request {i}")
+
+
+def test_decode_steps_of_9_to_20_rows_on_the_streaming_tensor_core_kernel():
+    """The tcgen05 weight-streaming product stands behind a switch (``ops.gemm.STREAM_ROWS``). With
+    the switch on, decode steps of 9 to 20 rows of the head-64 model run their products, with the
+    fused residual, norm and activation epilogues, on that kernel: the logits must be the plain
+    implementation's as with the switch off."""
+    from paged_kv_serving_b200 import ops
+    from paged_kv_serving_b200.ops import gemm
+
+    name, dtype = "D", "bfloat16"
+    config = helpers.CONFIGS[name]
+    before, original = gemm.STREAM_ROWS, ops.gemm_stream
+    calls = []
+    ops.gemm_stream = lambda *args, **options: calls.append(options.get("residual") is not None) or original(*args, **options)
+    gemm.STREAM_ROWS = 32
+    try:
+        session, tensors = _session(name, dtype, 20 * 64)
+        prompts = [helpers.random_tokens(config, 30 + i, seed=500 + i) for i in range(20)]
+        wants = [_reference(name, tensors, p) for p in prompts]
+        session.step([{"id": f"r{i}", "tokens": p[:20], "want": []} for i, p in enumerate(prompts)])
+        for position in range(20, 30):
+            live = range(20) if position < 25 else range(9)            # 20 rows, then 9
+            got = session.step([{"id": f"r{i}", "tokens": [prompts[i][position]], "want": [0]} for i in live],
+                               end=[f"r{i}" for i in range(9, 20)] if position == 24 else [])
+            want = np.stack([wants[i][position] for i in live])
+            helpers.assert_close(got, want, dtype, f"streaming kernel, {len(live)} rows at position {position}")
+        session.runner.check_status()
+    finally:
+        gemm.STREAM_ROWS, ops.gemm_stream = before, original
+    assert any(calls) and not all(calls), "plain and residual epilogues of the streaming kernel must have run"
