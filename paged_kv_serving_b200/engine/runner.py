@@ -25,7 +25,7 @@ from paged_kv_serving_b200.cache.manager import GroupSpec, plan_groups
 from paged_kv_serving_b200.cache.pages import NULL_PAGE
 from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
 from paged_kv_serving_b200.models.decoder import DecoderModel
-from paged_kv_serving_b200.ops import gemm
+from paged_kv_serving_b200.ops import arena, gemm
 from paged_kv_serving_b200.parts.base import CacheBinding, GroupView, IntArena, StepContext
 
 __all__ = ["CacheStorage", "ModelRunner", "StepResult"]
@@ -149,6 +149,9 @@ class ModelRunner:
         self._last_graph_step: tuple[ExecutionBatch, tuple[int, int]] | None = None
         self._ahead: dict | None = None
         self._graph_pool = torch.cuda.graph_pool_handle() if use_graphs else None
+        # memory for the outputs of a step's kernels (steps that are not graph replays); it grows to
+        # what the largest step needed and is reused by every step after it
+        self._arena = arena.StepArena(model.device)
 
     # --- storage behind the cache manager -------------------------------------------------
 
@@ -277,7 +280,10 @@ class ModelRunner:
         hidden = model.layout.embedding.forward(ctx)
         blocks = model.layout.blocks
         delta = None
+        step_arena = arena.active()
         for i, (call, binding) in enumerate(zip(self.order, self.bindings)):
+            if step_arena is not None:
+                step_arena.next_layer()
             # the block may carry the next block's first norm in the tail of its last kernel; the
             # last block hands on its plain update (the final norm takes only the wanted rows)
             following = blocks[self.order[i + 1].layer] if i + 1 < len(self.order) else None
@@ -285,6 +291,8 @@ class ModelRunner:
                 delta = blocks[call.layer].forward(hidden, delta, ctx, binding, next_norm=following.first_norm)
             else:
                 delta = blocks[call.layer].forward(hidden, delta, ctx, binding)
+        if step_arena is not None:
+            step_arena.end_layers()
         if not want_logits:
             return None
         normed = model.layout.final_norm.add_norm(hidden, delta, model.dtype, rows=ctx.ints(StepContext.LOGITS_ROWS))
@@ -295,8 +303,9 @@ class ModelRunner:
         """Run one batch: writes the cache for every token given, returns logits where wanted.
 
         A batch of single decoded tokens (every entry one token whose logits are wanted) replays
-        a CUDA graph captured for its size class; the logits tensor of such a step is reused by
-        the next one, so the caller reads it before stepping again.
+        a CUDA graph captured for its size class. The memory of a step's logits is used again by
+        the next step (a graph's static output, or the step's arena), so the caller reads or
+        samples from them before stepping again; work already queued on the stream is safe.
 
         ``feedback``: sequence id -> place in ``sampled_ids``, for one-token entries whose token
         was sampled by the step before and has not left the device: the embedding lookup reads
@@ -315,7 +324,12 @@ class ModelRunner:
         ctx.arena.upload(self.model.device)
         if clear_state_slots:
             self.storage.clear_state(clear_state_slots)
-        logits = self._forward(ctx, bool(rows))
+        self._arena.begin_step()
+        before = arena.activate(self._arena)
+        try:
+            logits = self._forward(ctx, bool(rows))
+        finally:
+            arena.activate(before)
         return StepResult(logits, rows, ctx.num_tokens, ctx.arena.bytes_uploaded)
 
     # --- decode steps as CUDA graphs -----------------------------------------------------

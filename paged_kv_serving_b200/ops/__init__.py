@@ -16,6 +16,7 @@ from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
+from paged_kv_serving_b200.ops.arena import empty as _empty
 from paged_kv_serving_b200.ops.build import build_all, library, library_names
 
 __all__ = [
@@ -108,7 +109,7 @@ def embedding_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tenso
         if fed_back_at.numel() != ids.numel():
             raise ValueError("fed_back_at needs one element per token")
     vocab, d = table.shape
-    out = torch.empty((ids.numel(), d), dtype=torch.float32, device=table.device)
+    out = _empty((ids.numel(), d), torch.float32, table.device)
     fn = _fn("elementwise", "pkv_embedding_gather",
              [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), ids.numel(), d, vocab,
@@ -134,7 +135,7 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     if rows is not None:
         _need(rows, torch.int32, "rows")
         n_rows = rows.numel()
-    out = torch.empty((n_rows, d), dtype=out_dtype, device=hidden.device)
+    out = _empty((n_rows, d), out_dtype, hidden.device)
     fn = _fn("elementwise", "pkv_add_rmsnorm",
              [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(weight),
@@ -166,7 +167,7 @@ def silu_mul(gate_up: torch.Tensor, clip: float, ff: int | None = None, interlea
     n, width = gate_up.shape
     if ff is None:
         ff = width // 2
-    out = torch.empty((n, ff), dtype=gate_up.dtype, device=gate_up.device)
+    out = _empty((n, ff), gate_up.dtype, gate_up.device)
     fn = _fn("elementwise", "pkv_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(_ptr(gate_up), _ptr(out), dtype_code(gate_up.dtype), n, ff, width, int(interleave), float(clip),
               _stream()), "silu_mul")
@@ -280,7 +281,7 @@ def paged_attention_generic(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
                     ("work_seq", work_seq), ("work_row0", work_row0)):
         _need(t, torch.int32, name)
     n = qkv.shape[0]
-    out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    out = _empty((n, n_heads * head_dim), qkv.dtype, qkv.device)
     fn = _fn("attention_generic", "pkv_paged_attention_generic",
              [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
@@ -592,9 +593,9 @@ def gemm_tcgen05(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epil
     if b_nk.shape[1] != k:
         raise ValueError("inner sizes differ")
     if epilogue == "silu_mul":
-        out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
+        out = _empty((m, n_out), torch.bfloat16, a.device)
     else:
-        out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
+        out = _empty((m, n), torch.float32 if epilogue == "f32" else torch.bfloat16, a.device)
     fn = _fn("gemm_tcgen05", "pkv_gemm_tcgen05",
              [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
               c_void_p, c_longlong, c_void_p, c_void_p])
@@ -675,7 +676,7 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
         _need(hidden, torch.float32, "hidden"); _need(weight, torch.float32, "norm weight")
         if hidden.shape != (m, n) or weight.numel() != n:
             raise ValueError("the residual epilogue needs a stream and a norm weight as wide as the product")
-        sumsq_out = torch.empty((-(-n // 16), 32), dtype=torch.float32, device=a.device)
+        sumsq_out = _empty((-(-n // 16), 32), torch.float32, a.device)
     if row_norm is not None:
         sumsq_in, eps = row_norm
         _need(sumsq_in, torch.float32, "sums of squares")
@@ -696,9 +697,9 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
         if n != (n_heads + 2 * n_kv) * head_dim or positions.numel() < m:
             raise ValueError("the projection's rows do not match (n_heads + 2*n_kv) * head_dim, or positions are missing")
     if epilogue == "silu_mul":
-        out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
+        out = _empty((m, n_out), torch.bfloat16, a.device)
     else:
-        out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
+        out = _empty((m, n), torch.float32 if epilogue == "f32" else torch.bfloat16, a.device)
     fn = _fn("gemm_small_m", "pkv_gemm_small_m",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
               c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
@@ -774,7 +775,7 @@ def gemm_stream(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epilo
         _need(hidden, torch.float32, "hidden"); _need(weight, torch.float32, "norm weight")
         if hidden.shape != (m, n) or weight.numel() != n:
             raise ValueError("the residual epilogue needs a stream and a norm weight as wide as the product")
-        sumsq_out = torch.empty((-(-n // 128), 128), dtype=torch.float32, device=a.device)
+        sumsq_out = _empty((-(-n // 128), 128), torch.float32, a.device)
     if row_norm is not None:
         sumsq_in, eps = row_norm
         _need(sumsq_in, torch.float32, "sums of squares")
@@ -782,9 +783,9 @@ def gemm_stream(a: torch.Tensor, b_nk: torch.Tensor, status: torch.Tensor, epilo
             raise ValueError("sums of squares must be [parts, at least as many columns as rows]")
         parts, in_stride = sumsq_in.shape
     if epilogue == "silu_mul":
-        out = torch.empty((m, n_out), dtype=torch.bfloat16, device=a.device)
+        out = _empty((m, n_out), torch.bfloat16, a.device)
     else:
-        out = torch.empty((m, n), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=a.device)
+        out = _empty((m, n), torch.float32 if epilogue == "f32" else torch.bfloat16, a.device)
     fn = _fn("gemm_stream", "pkv_gemm_stream",
              [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
@@ -803,7 +804,7 @@ def finish_norm(xw: torch.Tensor, sumsq: torch.Tensor, eps: float) -> torch.Tens
     ``xw / sqrt(sum(sumsq) / width + eps)``, bfloat16."""
     _need(xw, torch.bfloat16, "xw"); _need(sumsq, torch.float32, "sums of squares")
     rows, d = xw.shape
-    out = torch.empty_like(xw)
+    out = _empty(xw.shape, xw.dtype, xw.device)
     fn = _fn("elementwise", "pkv_finish_norm", [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_ptr(xw), _ptr(sumsq), sumsq.shape[0], sumsq.shape[1], float(eps), _ptr(out), rows, d, _stream()), "finish_norm")
     return out

@@ -18,6 +18,7 @@ from __future__ import annotations
 import torch
 
 from paged_kv_serving_b200 import ops
+from paged_kv_serving_b200.ops import arena
 
 __all__ = ["PendingNorm", "TCGEN05_MIN_ROWS", "as_tensor", "linear", "linear_add_norm", "linear_rope_kv_store",
            "linear_silu_mul", "matmul"]
@@ -116,6 +117,8 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         raise TypeError(f"operands differ in type: {x.dtype} and {w.dtype}")
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w, out_dtype=out_dtype)
+    if arena.active() is not None:      # the product's rows change with every batch: memory of the step's own
+        return torch.mm(x, w, out=arena.empty((x.shape[0], w.shape[1]), x.dtype, x.device))
     return torch.mm(x, w)
 
 

@@ -9,7 +9,7 @@ import torch
 
 from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.config.registry import register_part
-from paged_kv_serving_b200.ops import gemm
+from paged_kv_serving_b200.ops import arena, gemm
 from paged_kv_serving_b200.parts.base import CacheBinding, PagedKVRequest, ParamSpec, Part, StepContext
 from paged_kv_serving_b200.parts.position import PositionEncoding
 
@@ -272,7 +272,7 @@ class PagedAttention(Part):
     def _attend_fast(self, qkv, ctx: StepContext, group, k_pool, v_pool) -> torch.Tensor:
         plan = ctx.scratch[self._fast_key(group.page_size)]
         names = plan["names"]
-        out = torch.empty((qkv.shape[0], self.n_heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
+        out = arena.empty((qkv.shape[0], self.n_heads * self.head_dim), qkv.dtype, qkv.device)
         table, starts, first = ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS)
         if plan["n_prefill"] and self._tcgen05(group.page_size):
             ops.attention_prefill_tcgen05(qkv, out, k_pool, v_pool, table, starts, first,

@@ -25,6 +25,24 @@ class Sampler:
         self.device = torch.device(device)
         self._probs: torch.Tensor | None = None
         self._greedy: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+        # pinned staging buffers for the draws and parameters of a step, used in turn: the host may
+        # run a step ahead of the GPU, so a buffer is written again only once its copy has run
+        self._staging: list[tuple[torch.Tensor, torch.cuda.Event]] = []
+        self._turn = 0
+
+    def _stage(self, nbytes: int) -> tuple[torch.Tensor, "torch.cuda.Event"]:
+        if len(self._staging) < 4:
+            size = max(nbytes, 4096)
+            self._staging.append((torch.empty((size,), dtype=torch.uint8, pin_memory=torch.cuda.is_available()),
+                                  torch.cuda.Event()))
+            return self._staging[-1]
+        self._turn = (self._turn + 1) % 4
+        buffer, event = self._staging[self._turn]
+        event.synchronize()
+        if buffer.numel() < nbytes:
+            buffer = torch.empty((nbytes,), dtype=torch.uint8, pin_memory=torch.cuda.is_available())
+            self._staging[self._turn] = (buffer, event)
+        return buffer, event
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams],
                generators: list[np.random.Generator]) -> list[int]:
@@ -51,14 +69,15 @@ class Sampler:
             temperature, top_p, uniform = cached
         else:
             # one pinned buffer, one copy: [rows] float64 draws, then [rows] float32 temperatures and top-p
-            staged = torch.empty((rows * 16,), dtype=torch.uint8, pin_memory=torch.cuda.is_available())
+            buffer, copied = self._stage(rows * 16)
+            staged = buffer[:rows * 16]
             draws = staged[:rows * 8].view(torch.float64).numpy()
             floats = staged[rows * 8:].view(torch.float32).numpy()
-            for i, (p, rng) in enumerate(zip(params, generators)):
-                floats[i] = p.temperature
-                floats[rows + i] = p.top_p
-                draws[i] = 0.0 if p.greedy else float(rng.random())
+            floats[:rows] = [p.temperature for p in params]
+            floats[rows:] = [p.top_p for p in params]
+            draws[:] = [0.0 if p.greedy else rng.random() for p, rng in zip(params, generators)]
             dev = staged.to(self.device, non_blocking=True)
+            copied.record()
             uniform = dev[:rows * 8].view(torch.float64)
             temperature = dev[rows * 8:rows * 12].view(torch.float32)
             top_p = dev[rows * 12:].view(torch.float32)
