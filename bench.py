@@ -375,8 +375,14 @@ def run_serve(args) -> dict:
         block_size=block, num_blocks=count * per_sequence, max_batched_tokens=8192, max_running_seqs=count,
         max_prompt_tokens=4096, max_new_tokens=new_tokens, max_context_tokens=4096 + new_tokens,
         enable_prefix_cache=True, dtype="bfloat16"))
-    # one small request first: kernels, graphs and buffers of the sizes to come are built outside the timed run
-    engine.generate([Request("warm", tuple(prompts[0][:300]), SamplingParams(max_new_tokens=4, temperature=0.7))])
+    # warm-up outside the timed run, as a server has behind it when requests arrive: a full portion of
+    # prompts and decode steps of every row-count bucket, so that the library's kernels for these shapes
+    # are loaded; the graphs of the block-table widths to come are still captured inside the run
+    warm = [Request(f"warm{i}", tuple(int(t) for t in rng.integers(0, config.vocab_size, size=1365)),
+                    SamplingParams(max_new_tokens=3, temperature=0.7)) for i in range(12)]
+    warm += [Request(f"warm-short{i}", tuple(int(t) for t in rng.integers(0, config.vocab_size, size=24)),
+                     SamplingParams(max_new_tokens=3, temperature=0.7)) for i in range(count)]
+    engine.generate(warm)
     engine.flush_prefix_cache()
     torch.cuda.synchronize()
     started = time.perf_counter()

@@ -176,6 +176,8 @@ class KVCacheManager:
         # stand at the end of the sequence's tokens and cannot be hashed
         known = sequence.num_tokens - getattr(sequence, "num_unsettled_tokens", 0)
         complete = min(sequence.num_computed_tokens, known) // self.block_size
+        if len(sequence.block_hashes) >= complete:
+            return 0                       # the usual case of a decode step: no page was filled
         scope = self.prefix_cache.scope_bytes(sequence.request.key_id)
         accepted = 0
         while len(sequence.block_hashes) < complete:

@@ -12,6 +12,7 @@ least-recently-used first, and only when the cache is their last holder
 from __future__ import annotations
 
 import hashlib
+import struct
 from collections import OrderedDict
 from collections.abc import Sequence
 from dataclasses import dataclass
@@ -28,11 +29,21 @@ def chain_start(scope: bytes = b"") -> bytes:
     return hashlib.blake2b(_DOMAIN + b"|" + scope, digest_size=_DIGEST).digest()
 
 
+_PAGE_PACKERS: dict[int, struct.Struct] = {}
+
+
 def extend_chain(parent: bytes, tokens: Sequence[int], page_size: int) -> bytes:
     if len(tokens) != page_size:
         raise ValueError("only full pages are hashed")
-    body = b"".join(int(t).to_bytes(4, "little", signed=False) for t in tokens)
-    return hashlib.blake2b(parent + page_size.to_bytes(4, "little") + body, digest_size=_DIGEST).digest()
+    packer = _PAGE_PACKERS.get(page_size)
+    if packer is None:
+        # the page size, then every token id, as unsigned 32-bit little-endian integers
+        packer = _PAGE_PACKERS[page_size] = struct.Struct(f"<{page_size + 1}I")
+    try:
+        body = packer.pack(page_size, *tokens)
+    except struct.error as error:
+        raise OverflowError(f"a token id does not fit 32 unsigned bits: {error}") from None
+    return hashlib.blake2b(parent + body, digest_size=_DIGEST).digest()
 
 
 def hash_chain(tokens: Sequence[int], page_size: int, num_pages: int, scope: bytes = b"") -> list[bytes]:
