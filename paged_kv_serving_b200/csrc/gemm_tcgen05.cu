@@ -72,14 +72,28 @@ __device__ __forceinline__ void store_chunk(void* out, int ldo, int row, int col
 }
 
 
-// Persistent: each block walks over output tiles (row blocks fastest, so that the blocks in
-// flight share a few tiles of B, the weights, while all of A stays in L2). Two accumulators in
+// Where tile number `tile` of the walk lies. The row blocks of A are taken in groups of
+// `group_m`: within a group row blocks run fastest and every column block of B is visited before
+// the next group begins. The blocks in flight then share a few tiles of B (the weights), the
+// group's rows of A stay in L2 while B streams past them once per group, and A never has to fit
+// L2 as a whole (with all of A as one group, 8,192 rows of width 5,120 are read from memory again
+// for every column block, and the product is bound by that).
+__device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, int group_m, int& m_index, int& n_index) {
+  const int per_group = group_m * n_tiles;
+  const int group = tile / per_group, within = tile - group * per_group;
+  const int first = group * group_m;
+  const int rows_here = min(group_m, m_tiles - first);
+  n_index = within / rows_here;
+  m_index = first + (within - n_index * rows_here);
+}
+
+// Persistent: each block walks over output tiles in the order of tile_origin. Two accumulators in
 // TMEM alternate, so the epilogue of one tile runs under the MMAs of the next.
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    void* __restrict__ out, int ldo, int M, int n_valid, int K, int m_tiles, int n_tiles, float clip,
-                    int* __restrict__ status) {
+                    void* __restrict__ out, int ldo, int M, int n_valid, int K, int m_tiles, int n_tiles, int group_m,
+                    float clip, int* __restrict__ status) {
   constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;
   constexpr uint32_t B_BYTES = BN * GM_BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -119,7 +133,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * GM_BM, n0 = (tile / m_tiles) * BN;
+        int m_index, n_index;
+        tile_origin(tile, m_tiles, n_tiles, group_m, m_index, n_index);
+        const int m0 = m_index * GM_BM, n0 = n_index * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int stage = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty_bar[stage], ((it / STAGES) - 1) & 1, aborted)) { ok = false; break; }
@@ -173,7 +189,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
-      const int m0 = (tile % m_tiles) * GM_BM, n0 = (tile / m_tiles) * BN;
+      int m_index, n_index;
+      tile_origin(tile, m_tiles, n_tiles, group_m, m_index, n_index);
+      const int m0 = m_index * GM_BM, n0 = n_index * BN;
       const int row = m0 + quarter * 32 + lane;
       // every lane waits; the warp goes on only as a whole (tcgen05.ld needs all 32 lanes)
       const bool ready = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (local >> 1) & 1, aborted) ? 1 : 0) != 0;
@@ -495,8 +513,12 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
   }
   const int blocks = (int)(total < sm_count ? total : sm_count);
+  // as many row blocks of A to a group as hold about 32 MB (a quarter of L2)
+  long long group_m = (32LL << 20) / ((long long)GM_BM * K * 2);
+  if (group_m < 1) group_m = 1;
+  if (group_m > m_tiles) group_m = m_tiles;
   gemm_tcgen05_kernel<BN, STAGES, EPI><<<blocks, GM_THREADS, smem, s>>>(map_a, map_b, out, ldo, M, n_valid, K, m_tiles,
-                                                                       n_tiles_cols, clip, status);
+                                                                       n_tiles_cols, (int)group_m, clip, status);
   return launch_status();
 }
 

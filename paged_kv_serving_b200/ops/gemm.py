@@ -20,7 +20,7 @@ import torch
 from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.ops import arena
 
-__all__ = ["PendingNorm", "TCGEN05_MIN_ROWS", "as_tensor", "linear", "linear_add_norm", "linear_rope_kv_store",
+__all__ = ["PendingNorm", "SILU_TCGEN05_MIN_ROWS", "TCGEN05_MIN_ROWS", "as_tensor", "linear", "linear_add_norm", "linear_rope_kv_store",
            "linear_silu_mul", "matmul"]
 
 torch.backends.cuda.matmul.allow_tf32 = False
@@ -30,6 +30,14 @@ torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 #: Activations with at least this many rows use the tcgen05 kernel (its tiles are 128 rows tall).
 TCGEN05_MIN_ROWS = 128
+#: The fused gate/up product (SiLU(gate) * up in the epilogue) takes portions of at least this many
+#: rows; shorter ones go to cuBLAS followed by the activation kernel. Timed at the layer sizes of
+#: 1-, 8- and 13-billion-parameter models, the fused kernel is ahead from about 1,500 rows on (2,048
+#: rows, 8B: 337 against 384 us; 8,192 rows: 1,390 against 1,632) and behind below (544 rows, 13B:
+#: 145 against 124 us; 256 rows, 8B: 69 against 61): with few row blocks its 128 x 256 tiles fill the
+#: SMs' rounds unevenly and the library's wider two-SM tiles do more per byte of shared memory.
+#: Tests set it to ``TCGEN05_MIN_ROWS`` to run the kernel at their sizes.
+SILU_TCGEN05_MIN_ROWS = 1536
 #: Set to False to send every product to cuBLAS (used by tests that compare the two).
 USE_TCGEN05 = True
 #: Which kernel takes the plain products (no fused epilogue) of prompt portions: "library" for
@@ -218,7 +226,8 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, interleav
     if interleave == 128 and _small_m(x, w_gate_up, "silu_mul"):
         return ops.gemm_small_m(x, w_gate_up, "silu_mul", n_out=ff, clip=clip,
                                 chained=SMALL_M_CHAINED and chain)
-    if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and _own_kernel(x, w_gate_up):
+    if interleave == 128 and w_gate_up.shape[0] % 256 == 0 and ff % 8 == 0 and x.shape[0] >= SILU_TCGEN05_MIN_ROWS \
+            and _own_kernel(x, w_gate_up):
         # one SM per tile: with this many tiles the two-SM kernel's split of the last wave costs
         # more than it saves
         return ops.gemm_tcgen05(x, w_gate_up, ops.status_word(x.device), "silu_mul", n_out=ff, clip=clip,

@@ -30,6 +30,26 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(autouse=True)
+def fused_gate_up_at_test_sizes(request):
+    """The engine sends the gate/up product of a portion to the fused tcgen05 kernel only from
+    ``ops.gemm.SILU_TCGEN05_MIN_ROWS`` rows on (about 1,500: below that the library is faster at
+    the sizes of real models). The prompts of these tests are far shorter, so the GPU tests lower
+    the switch to the kernel's own minimum and keep running it inside whole models; one test of
+    tests/test_gpu_replay.py runs the routing as shipped."""
+    if "gpu" not in request.keywords:
+        yield
+        return
+    from paged_kv_serving_b200.ops import gemm
+
+    before = gemm.SILU_TCGEN05_MIN_ROWS
+    gemm.SILU_TCGEN05_MIN_ROWS = gemm.TCGEN05_MIN_ROWS
+    try:
+        yield
+    finally:
+        gemm.SILU_TCGEN05_MIN_ROWS = before
+
+
 def pytest_terminal_summary(terminalreporter):
     try:
         import helpers

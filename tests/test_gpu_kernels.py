@@ -415,7 +415,8 @@ def test_attention_refuses_what_it_cannot_do():
 
 
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (1, 520, 136), (200, 1000, 72), (300, 96, 4096), (2048, 1024, 200), (1000, 4000, 1032), (2100, 2304, 72), (520, 6400, 136),
-                                     (130, 1320, 120)])
+                                     (130, 1320, 120),
+                                     (4200, 520, 4096)])      # row blocks walked in groups (32 and a last one of 1), 3 column blocks
 @pytest.mark.parametrize("pairs", [True, False])
 @pytest.mark.parametrize("epilogue", ["bf16", "f32"])
 def test_gemm_tcgen05(m, n, k, epilogue, pairs):

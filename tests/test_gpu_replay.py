@@ -253,3 +253,36 @@ def test_decode_steps_of_9_to_20_rows_on_the_streaming_tensor_core_kernel():
     finally:
         gemm.STREAM_ROWS, ops.gemm_stream = before, original
     assert any(calls) and not all(calls), "plain and residual epilogues of the streaming kernel must have run"
+
+
+def test_short_portions_take_the_library_product_and_the_activation_kernel(monkeypatch):
+    """The routing as shipped: a portion of 150 tokens is far below the row count from which the
+    fused gate/up kernel pays, so its gate/up product goes to the library and the activation
+    kernel follows; the logits are the plain implementation's either way."""
+    from paged_kv_serving_b200 import ops
+    from paged_kv_serving_b200.ops import gemm
+
+    name, dtype = "D", "bfloat16"
+    config = helpers.CONFIGS[name]
+    calls = {"fused": 0, "activation": 0}
+    fused, activation = ops.gemm_tcgen05, ops.silu_mul
+
+    def count_fused(*args, **options):
+        calls["fused"] += 1 if (len(args) > 3 and args[3] == "silu_mul") or options.get("epilogue") == "silu_mul" else 0
+        return fused(*args, **options)
+
+    def count_activation(*args, **options):
+        calls["activation"] += 1
+        return activation(*args, **options)
+
+    monkeypatch.setattr(ops, "gemm_tcgen05", count_fused)
+    monkeypatch.setattr(ops, "silu_mul", count_activation)
+    tokens = helpers.random_tokens(config, 150, seed=77)
+    for threshold, expect_fused in ((1536, False), (gemm.TCGEN05_MIN_ROWS, True)):
+        monkeypatch.setattr(gemm, "SILU_TCGEN05_MIN_ROWS", threshold)
+        calls["fused"] = calls["activation"] = 0
+        session, tensors = _session(name, dtype, 256)
+        got = session.step([{"id": "a", "tokens": tokens, "want": list(range(150))}])
+        helpers.assert_close(got, _reference(name, tensors, tokens), dtype, f"gate/up routing at threshold {threshold}")
+        assert (calls["fused"] > 0) == expect_fused and (calls["activation"] > 0) != expect_fused, calls
+        session.runner.check_status()
