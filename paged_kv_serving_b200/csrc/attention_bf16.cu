@@ -53,6 +53,8 @@ struct AttnParams {
   int use_cluster;              // decode only: the splits of one (entry, kv head) are one thread-block cluster
   float* part_o;                // decode scratch [T*H, splits, HD]
   float* part_ml;               // decode scratch [T*H, splits, 2]
+  int num_pages;                // pages of the pools: table entries are checked against it
+  int* status;                  // the device's status word (may be null)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,17 +92,19 @@ struct PageLookup {
   const int32_t* cached;     // shared-memory copy of entries [first, first + count), or null
   int first;
   int page_size, page_shift;
+  int num_pages;
+  int* status;
   __device__ __forceinline__ int entry_of(int pos) const { return page_shift >= 0 ? pos >> page_shift : pos / page_size; }
   __device__ __forceinline__ int page_of(int pos, int& offset) const {
     const int e = entry_of(pos);
     offset = pos - e * page_size;
-    return cached ? cached[e - first] : table[e];
+    return checked_page(cached ? cached[e - first] : table[e], num_pages, status);
   }
 };
 
 __device__ __forceinline__ PageLookup make_page_lookup(int32_t* cache, const int32_t* table, int lo, int hi,
-                                                       int page_size, int page_shift) {
-  PageLookup look{table, nullptr, 0, page_size, page_shift};
+                                                       int page_size, int page_shift, int num_pages, int* status) {
+  PageLookup look{table, nullptr, 0, page_size, page_shift, num_pages, status};
   if (hi <= lo) return look;
   const int first = look.entry_of(lo), count = look.entry_of(hi - 1) - first + 1;
   if (count <= PAGE_CACHE) {
@@ -160,7 +164,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_prefill_kernel(const Att
   const int tile_begin = key_lo / AT_BN, tile_end = (key_hi - 1) / AT_BN;       // inclusive
   __shared__ int32_t page_cache[PAGE_CACHE];
   const PageLookup look = make_page_lookup(page_cache, p.block_table + (size_t)s * p.table_stride, key_lo, key_hi,
-                                           p.page_size, p.page_shift);
+                                           p.page_size, p.page_shift, p.num_pages, p.status);
 
   // queries of this block
   for (int idx = threadIdx.x; idx < AT_BM * (HD / 8); idx += AT_THREADS) {
@@ -335,7 +339,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
   __shared__ int32_t page_cache[PAGE_CACHE];
   const PageLookup look = make_page_lookup(page_cache, p.block_table + (size_t)s * p.table_stride,
                                            max(key_lo, tile_begin * AT_BN), min(key_hi, (tile_end + 1) * AT_BN),
-                                           p.page_size, p.page_shift);
+                                           p.page_size, p.page_shift, p.num_pages, p.status);
 
   for (int idx = threadIdx.x; idx < DEC_ROWS * (HD / 8); idx += AT_THREADS) {
     const int row = idx / (HD / 8), chunk = idx - row * (HD / 8);
@@ -641,13 +645,15 @@ PKV_EXPORT int pkv_attention_prefill_bf16(const void* qkv, int q_row_stride, voi
                                           const void* v_pool, const int32_t* block_table, int table_stride,
                                           const int32_t* seq_starts, const int32_t* first_pos,
                                           const int32_t* work_seq, const int32_t* work_q0, int n_work, int n_heads,
-                                          int n_kv, int hd, int page_size, int window, float scale, void* stream) {
+                                          int n_kv, int hd, int page_size, int window, float scale, int num_pages,
+                                          int* status, void* stream) {
   if (n_work <= 0) return 0;
   const int bad = check_common(n_heads, n_kv, hd, page_size, window, q_row_stride);
   if (bad) return bad;
+  if (num_pages <= 0) return PKV_ERR_SIZE;
   AttnParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
                table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size, log2_or_minus1(page_size), window,
-               scale * 1.4426950408889634f, 1, 0, nullptr, nullptr};
+               scale * 1.4426950408889634f, 1, 0, nullptr, nullptr, num_pages, status};
   cudaStream_t s = (cudaStream_t)stream;
 #define CALL(HD) return launch_prefill<HD>(p, n_work, s)
   PKV_HD_SWITCH(hd, CALL)
@@ -665,10 +671,12 @@ PKV_EXPORT int pkv_attention_decode_bf16(const void* qkv, int q_row_stride, void
                                          const int32_t* seq_starts, const int32_t* first_pos,
                                          const int32_t* work_seq, int n_work, int max_entry_tokens, int n_heads,
                                          int n_kv, int hd, int page_size, int window, float scale, int num_splits,
-                                         float* scratch, long long total_rows, void* stream) {
+                                         float* scratch, long long total_rows, int num_pages, int* status_word,
+                                         void* stream) {
   if (n_work <= 0) return 0;
   const int bad = check_common(n_heads, n_kv, hd, page_size, window, q_row_stride);
   if (bad) return bad;
+  if (num_pages <= 0) return PKV_ERR_SIZE;
   if (num_splits < 1 || num_splits > 65535 || n_work > 65535) return PKV_ERR_LIMIT;
   if (max_entry_tokens * (n_heads / n_kv) > DEC_ROWS) return PKV_ERR_LIMIT;
   // up to 8 splits (the portable cluster size) merge inside a cluster; more go through scratch
@@ -678,7 +686,7 @@ PKV_EXPORT int pkv_attention_decode_bf16(const void* qkv, int q_row_stride, void
   float* part_ml = scratch ? scratch + (size_t)total_rows * num_splits * hd : nullptr;
   AttnParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
                table_stride, seq_starts, first_pos, work_seq, nullptr, n_heads, n_kv, page_size, log2_or_minus1(page_size), window,
-               scale * 1.4426950408889634f, num_splits, use_cluster, part_o, part_ml};
+               scale * 1.4426950408889634f, num_splits, use_cluster, part_o, part_ml, num_pages, status_word};
   cudaStream_t s = (cudaStream_t)stream;
   int status = 0;
 #define CALL(HD) status = launch_decode<HD>(p, n_work, s)

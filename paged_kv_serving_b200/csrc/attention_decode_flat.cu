@@ -159,7 +159,7 @@ attention_decode_flat_kernel(const __grid_constant__ CUtensorMap map_k, const __
           if (has_box && pos < e.key_hi && pos + p.page_size > e.key_lo) {
             const int entry = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
             const int page = table[entry];
-            if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+            row = checked_pool_row(page, p.n_kv, kvh, p.page_size, p.pool_rows, p.status);
           }
           return row;
         };

@@ -183,7 +183,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         if (pos < key_hi && pos + p.page_size > key_lo) {
           const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
-          if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+          row = checked_pool_row(page, p.n_kv, kvh, p.page_size, p.pool_rows, p.status);
         }
         if (PANELS == 2) tma_load_4d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 0, 0, 0, row >> 3);
         else tma_load_2d(ring + (size_t)stage * STAGE_BYTES + dst_offset, map, &full_bar[stage], 64 * pn, row);

@@ -33,7 +33,8 @@ paged_attention_generic_kernel(const A* __restrict__ qkv, int q_row_stride, A* _
                                const int32_t* __restrict__ block_table, int table_stride,
                                const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ first_pos,
                                const int32_t* __restrict__ work_seq, const int32_t* __restrict__ work_row0,
-                               int n_heads, int n_kv, int hd, int page_size, int window, float scale) {
+                               int n_heads, int n_kv, int hd, int page_size, int window, float scale, int num_pages,
+                               int* __restrict__ status) {
   extern __shared__ float smem[];
   float* q_s = smem;                              // [ATT_WARPS][hd]
   float* k_s = q_s + ATT_WARPS * hd;              // [ATT_TILE][hd + 1]
@@ -80,7 +81,7 @@ paged_attention_generic_kernel(const A* __restrict__ qkv, int q_row_stride, A* _
       const int pos = base + j;
       float kv = 0.0f, vv = 0.0f;
       if (pos >= key_lo && pos < key_hi) {
-        const int page = table[pos / page_size];
+        const int page = checked_page(table[pos / page_size], num_pages, status);
         if (page >= 0) {
           const size_t at = (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * hd + d;
           kv = to_float(k_pool[at]);
@@ -140,7 +141,8 @@ template <typename A, typename C>
 static int launch_generic(const void* qkv, int q_row_stride, void* out, const void* k_pool, const void* v_pool,
                           const int32_t* block_table, int table_stride, const int32_t* seq_starts,
                           const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_row0, int n_work,
-                          int n_heads, int n_kv, int hd, int page_size, int window, float scale, cudaStream_t s) {
+                          int n_heads, int n_kv, int hd, int page_size, int window, float scale, int num_pages, int* status,
+                          cudaStream_t s) {
   const size_t smem = ((size_t)ATT_WARPS * hd + (size_t)ATT_TILE * (hd + 1) + (size_t)ATT_TILE * hd) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(paged_attention_generic_kernel<A, C>,
@@ -150,7 +152,7 @@ static int launch_generic(const void* qkv, int q_row_stride, void* out, const vo
   dim3 grid(n_work, n_kv);
   paged_attention_generic_kernel<A, C><<<grid, ATT_WARPS * 32, smem, s>>>(
       (const A*)qkv, q_row_stride, (A*)out, (const C*)k_pool, (const C*)v_pool, block_table, table_stride,
-      seq_starts, first_pos, work_seq, work_row0, n_heads, n_kv, hd, page_size, window, scale);
+      seq_starts, first_pos, work_seq, work_row0, n_heads, n_kv, hd, page_size, window, scale, num_pages, status);
   return launch_status();
 }
 
@@ -163,15 +165,15 @@ PKV_EXPORT int pkv_paged_attention_generic(const void* qkv, int q_row_stride, vo
                                            const int32_t* seq_starts, const int32_t* first_pos,
                                            const int32_t* work_seq, const int32_t* work_row0, int n_work,
                                            int n_heads, int n_kv, int hd, int page_size, int window, float scale,
-                                           void* stream) {
+                                           int num_pages, int* status, void* stream) {
   if (n_work <= 0) return 0;
-  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || hd <= 0 || (hd & 1) || page_size <= 0 || window < 0)
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || hd <= 0 || (hd & 1) || page_size <= 0 || window < 0 || num_pages <= 0)
     return PKV_ERR_SIZE;
   if (hd > 32 * ATT_MAX_ACC || n_kv > 65535) return PKV_ERR_LIMIT;
   cudaStream_t s = (cudaStream_t)stream;
 #define PKV_ATT(A, C)                                                                                         \
   return launch_generic<A, C>(qkv, q_row_stride, out, k_pool, v_pool, block_table, table_stride, seq_starts, \
-                              first_pos, work_seq, work_row0, n_work, n_heads, n_kv, hd, page_size, window, scale, s)
+                              first_pos, work_seq, work_row0, n_work, n_heads, n_kv, hd, page_size, window, scale, num_pages, status, s)
   if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_ATT(float, float);
   if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ATT(bf16, bf16);
   if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ATT(float, bf16);

@@ -159,7 +159,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (pos < key_hi && pos + p.page_size > key_lo) {
           const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
-          if (page >= 0) row = (page * p.n_kv + kvh) * p.page_size;
+          row = checked_pool_row(page, p.n_kv, kvh, p.page_size, p.pool_rows, p.status);
         }
         if (WIDE)
           tma_load_4d(dst + (i * p.page_size >> 3) * GROUP_BYTES, which ? &map_v : &map_k, full, 0, 0, 0, row >> 3);

@@ -22,9 +22,41 @@
 #define PKV_ERR_ALIGN (-4)
 #define PKV_ERR_LIMIT (-5)
 
+// codes kernels record in the device's status word; the host raises on any of them
+#define PKV_STATUS_BAD_ID 1        // a token id outside the embedding table
+#define PKV_STATUS_GAVE_UP 2       // a bounded wait ran out
+#define PKV_STATUS_OUT_OF_RANGE 3  // a page, a cache slot or a position outside its range
+
 namespace pkv {
 
 typedef __nv_bfloat16 bf16;
+
+// A page number read from a block table is a page of the pool or -1 ("no page": its keys read as
+// zeros). Anything else is recorded in the status word and treated as no page, so that a table
+// the host got wrong never becomes an address.
+__device__ __forceinline__ int checked_page(int page, int num_pages, int* status) {
+  if (page >= num_pages || page < -1) {
+    if (status) atomicExch(status, PKV_STATUS_OUT_OF_RANGE);
+    return -1;
+  }
+  return page;
+}
+
+// The same for the kernels that fetch pages with TMA: the pool row where a page's keys of one
+// key/value head begin, or `pool_rows` (a row the copy unit reads as zeros) for no page and for a
+// page outside the pool, which is recorded.
+__device__ __forceinline__ int checked_pool_row(int page, int n_kv, int kvh, int page_size, int pool_rows, int* status) {
+  if (page < 0) {
+    if (page < -1 && status) atomicExch(status, PKV_STATUS_OUT_OF_RANGE);
+    return pool_rows;
+  }
+  const long long row = ((long long)page * n_kv + kvh) * page_size;
+  if (row >= pool_rows) {
+    if (status) atomicExch(status, PKV_STATUS_OUT_OF_RANGE);
+    return pool_rows;
+  }
+  return (int)row;
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }

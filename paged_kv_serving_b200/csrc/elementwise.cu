@@ -230,6 +230,8 @@ __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ o
 //   cos/sin  [max_pos, hd/2] or null (no rotation: store only)
 //   k_pool / v_pool  [pages, KV, page_size, hd]  of one layer
 //   slots    [T]  page * page_size + offset, or -1 to skip the store of a token
+// A slot outside the pool (`num_slots`) or a position outside the tables (`max_pos`) is recorded
+// in the status word; the store is skipped, the rotation uses position 0.
 // grid (T, H + 2*KV): one block per (token, head); blockDim = hd/2 rounded up to a warp.
 // ---------------------------------------------------------------------------------------------
 template <typename A, typename C>
@@ -237,21 +239,27 @@ __global__ void rope_kv_store_kernel(A* __restrict__ qkv, const int32_t* __restr
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                      C* __restrict__ k_pool, C* __restrict__ v_pool,
                                      const int32_t* __restrict__ slots, int n_heads, int n_kv, int hd,
-                                     int page_size, int store) {
+                                     int page_size, int store, int num_slots, int max_pos, int* __restrict__ status) {
   dependents_may_launch();
   wait_for_prior_kernels();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // [0,H) q heads, [H,H+KV) k heads, [H+KV,H+2KV) v heads
   const int half = hd >> 1;
   A* row = qkv + ((size_t)t * (n_heads + 2 * n_kv) + head) * hd;
-  const int pos = positions[t];
+  int pos = positions[t];
+  if (cos_t && (pos < 0 || pos >= max_pos)) {
+    if (threadIdx.x == 0 && status) atomicExch(status, PKV_STATUS_OUT_OF_RANGE);
+    pos = 0;
+  }
   const bool is_q = head < n_heads;
   const bool is_k = !is_q && head < n_heads + n_kv;
   size_t base = 0;
   bool do_store = false;
   if (!is_q && store) {
     const int slot = slots[t];
-    if (slot >= 0) {
+    if (slot >= num_slots || slot < -1) {
+      if (threadIdx.x == 0 && status) atomicExch(status, PKV_STATUS_OUT_OF_RANGE);
+    } else if (slot >= 0) {
       const int kvh = is_k ? head - n_heads : head - n_heads - n_kv;
       const int page = slot / page_size, off = slot - page * page_size;
       base = (((size_t)page * n_kv + kvh) * page_size + off) * hd;
@@ -287,14 +295,20 @@ __global__ void rope_kv_store_vec_kernel(A* __restrict__ qkv, const int32_t* __r
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          C* __restrict__ k_pool, C* __restrict__ v_pool,
                                          const int32_t* __restrict__ slots, int n_heads, int n_kv, int hd,
-                                         int page_size, int store) {
+                                         int page_size, int store, int num_slots, int max_pos,
+                                         int* __restrict__ status) {
   dependents_may_launch();
   wait_for_prior_kernels();
   const int t = blockIdx.x;
   const int half = hd >> 1;
   const int quads = half >> 2;                       // groups of 4 pairs per head
-  const int pos = positions[t];
-  const int slot = store ? slots[t] : -1;
+  int pos = positions[t];
+  int slot = store ? slots[t] : -1;
+  if ((cos_t && (pos < 0 || pos >= max_pos)) || slot >= num_slots || slot < -1) {
+    if (threadIdx.x == 0 && status) atomicExch(status, PKV_STATUS_OUT_OF_RANGE);
+    if (cos_t && (pos < 0 || pos >= max_pos)) pos = 0;
+    if (slot >= num_slots || slot < -1) slot = -1;
+  }
   const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
   A* row = qkv + (size_t)t * (n_heads + 2 * n_kv) * hd;
   const int rot_tasks = (n_heads + n_kv) * quads;
@@ -438,9 +452,10 @@ PKV_EXPORT int pkv_silu_mul(const void* gate_up, void* out, int dtype, int n_tok
 PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positions, const float* cos_t,
                                  const float* sin_t, void* k_pool, void* v_pool, int cache_dtype,
                                  const int32_t* slots, int n_tokens, int n_heads, int n_kv, int hd, int page_size,
-                                 int store, void* stream) {
+                                 int store, int num_slots, int max_pos, int* status, void* stream) {
   if (n_tokens <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || hd <= 0 || (hd & 1) || page_size <= 0) return PKV_ERR_SIZE;
+  if ((store && num_slots <= 0) || (cos_t && max_pos <= 0)) return PKV_ERR_SIZE;
   if (n_heads + 2 * n_kv > 65535) return PKV_ERR_LIMIT;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd % 8 == 0) {
@@ -449,7 +464,8 @@ PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positi
     if (vthreads > 512) vthreads = 512;
 #define PKV_ROPE_VEC(A, C)                                                                                   \
   return launch_kernel(rope_kv_store_vec_kernel<A, C>, dim3(n_tokens), dim3(vthreads), 0, s, true, 0, (A*)qkv, \
-                       positions, cos_t, sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
+                       positions, cos_t, sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store, num_slots, \
+                       max_pos, status)
     if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_ROPE_VEC(float, float);
     if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(bf16, bf16);
     if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE_VEC(float, bf16);
@@ -462,7 +478,7 @@ PKV_EXPORT int pkv_rope_kv_store(void* qkv, int act_dtype, const int32_t* positi
   dim3 grid(n_tokens, n_heads + 2 * n_kv);
 #define PKV_ROPE(A, C)                                                                                           \
   return launch_kernel(rope_kv_store_kernel<A, C>, grid, dim3(threads), 0, s, true, 0, (A*)qkv, positions, cos_t, \
-                       sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store)
+                       sin_t, (C*)k_pool, (C*)v_pool, slots, n_heads, n_kv, hd, page_size, store, num_slots, max_pos, status)
   if (act_dtype == PKV_F32 && cache_dtype == PKV_F32) PKV_ROPE(float, float);
   if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16) PKV_ROPE(bf16, bf16);
   if (act_dtype == PKV_F32 && cache_dtype == PKV_BF16) PKV_ROPE(float, bf16);

@@ -92,6 +92,10 @@ struct SmallParams {
   bf16* v_pool;
   const int32_t* slots;      // [M] or null
   int n_heads, n_kv, head_dim, page_size;
+  // a slot outside the pools or a position outside the tables is recorded in the status word;
+  // the store is then skipped and the rotation uses position 0
+  int num_slots, max_pos;
+  int* status;
 };
 
 template <int RT, int EPI>
@@ -307,11 +311,23 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32, PER_SM) gemm_small_m_kernel(
             const int per_head = p.head_dim >> 4, head = tile / per_head;
             const int e = (tile - head * per_head) * 8 + (l >> 2);
             if (p.cos_t != nullptr && head < p.n_heads + p.n_kv) {
-              const size_t at = (size_t)p.positions[m] * (p.head_dim >> 1) + e;
+              int position = p.positions[m];
+              if (position < 0 || position >= p.max_pos) {
+                if (p.status) atomicExch(p.status, PKV_STATUS_OUT_OF_RANGE);
+                position = 0;
+              }
+              const size_t at = (size_t)position * (p.head_dim >> 1) + e;
               early_a[it] = p.cos_t[at];
               early_b[it] = p.sin_t[at];
             }
-            if (p.slots != nullptr && head >= p.n_heads) early_slot[it] = p.slots[m];
+            if (p.slots != nullptr && head >= p.n_heads) {
+              int slot = p.slots[m];
+              if (slot >= p.num_slots || slot < -1) {
+                if (p.status) atomicExch(p.status, PKV_STATUS_OUT_OF_RANGE);
+                slot = -1;
+              }
+              early_slot[it] = slot;
+            }
           }
         }
       }
@@ -513,13 +529,14 @@ PKV_EXPORT long long pkv_gemm_small_m_workspace_bytes() {
 // the tables cos_t, sin_t [positions][head_dim / 2] (half-split pairs; null tables: no rotation);
 // `out` [M, N] receives the queries (its key and value columns are left unwritten); keys and
 // values go to the pools [pages, n_kv, page_size, head_dim] at `slots[row]` (null or negative:
-// not stored).
+// not stored); `num_slots` = pages x page_size and `max_pos` = rows of the tables bound them, and a
+// value outside is recorded in `status` (may be null) instead of being used.
 PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int epilogue,
                                 int n_out, float clip, int chained, void* workspace, long long workspace_bytes,
                                 float* hidden, const float* norm_weight, float* sumsq_out, const float* sumsq_in,
                                 int sumsq_parts, int width, float norm_eps, const int* positions, const float* cos_t,
                                 const float* sin_t, void* k_pool, void* v_pool, const int* slots, int n_heads, int n_kv,
-                                int head_dim, int page_size, void* stream) {
+                                int head_dim, int page_size, int num_slots, int max_pos, int* status, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return PKV_ERR_SIZE;
   if (K % SMALL_CHUNK != 0 || ldx % 8 != 0) return PKV_ERR_SIZE;
   if (M > pkv_gemm_small_m_max_rows(epilogue)) return PKV_ERR_LIMIT;
@@ -537,7 +554,7 @@ PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, 
   if (sumsq_in && (sumsq_parts <= 0 || width <= 0)) return PKV_ERR_SIZE;
   p.positions = positions; p.cos_t = cos_t; p.sin_t = sin_t; p.k_pool = static_cast<bf16*>(k_pool);
   p.v_pool = static_cast<bf16*>(v_pool); p.slots = slots; p.n_heads = n_heads; p.n_kv = n_kv; p.head_dim = head_dim;
-  p.page_size = page_size;
+  p.page_size = page_size; p.num_slots = num_slots; p.max_pos = max_pos; p.status = status;
   p.chunks = K / SMALL_CHUNK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (epilogue) {
@@ -550,7 +567,8 @@ PKV_EXPORT int pkv_gemm_small_m(const void* x, const void* w, void* out, int M, 
       if (head_dim <= 0 || head_dim % 16 != 0 || n_heads <= 0 || n_kv <= 0 || N != (n_heads + 2 * n_kv) * head_dim)
         return PKV_ERR_SIZE;
       if (!positions || (cos_t != nullptr) != (sin_t != nullptr) || page_size <= 0) return PKV_ERR_SIZE;
-      if (slots && (!k_pool || !v_pool)) return PKV_ERR_SIZE;
+      if (slots && (!k_pool || !v_pool || num_slots <= 0)) return PKV_ERR_SIZE;
+      if (cos_t && max_pos <= 0) return PKV_ERR_SIZE;
       p.tiles = N / 16; p.ld_out = N; p.n_out = N;
       if (p.tiles > SMALL_MAX_TILES) return PKV_ERR_LIMIT;
       return dispatch_small<EPI_ROPE_KV>(p, chained, s);

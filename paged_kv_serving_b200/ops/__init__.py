@@ -177,16 +177,27 @@ def silu_mul(gate_up: torch.Tensor, clip: float, ff: int | None = None, interlea
 _STATUS: dict[str, torch.Tensor] = {}
 
 
+def _device_key(device: torch.device | str) -> str:
+    """One name per device for the tables kept here: "cuda" means the current device, so that
+    ``"cuda"`` and ``"cuda:0"`` find the same status word and workspaces."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return str(device)
+
+
 def status_word(device: torch.device | str) -> torch.Tensor:
     """The int32 status word of a device: kernels record a code there instead of trapping
-    (1: a token id outside the embedding table, 2: a kernel gave up a bounded wait)."""
-    key = str(torch.device(device))
+    (1: a token id outside the embedding table, 2: a kernel gave up a bounded wait, 3: a page, a
+    cache slot or a position outside its range, which the kernel did not use)."""
+    key = _device_key(device)
     if key not in _STATUS:
         _STATUS[key] = torch.zeros((1,), dtype=torch.int32, device=device)
     return _STATUS[key]
 
 
-STATUS_MEANINGS = {1: "a token id outside the embedding table", 2: "a kernel gave up a bounded wait"}
+STATUS_MEANINGS = {1: "a token id outside the embedding table", 2: "a kernel gave up a bounded wait",
+                   3: "a page, a cache slot or a position outside its range"}
 
 
 def raise_for_status(code: int, device: torch.device | str) -> None:
@@ -205,7 +216,7 @@ def raise_for_status(code: int, device: torch.device | str) -> None:
 def reset_workspaces(device: torch.device | str) -> None:
     """Zero the counters, flags and partial sums that kernels of this module keep on a device
     between launches (they are left zero by every launch that ends in order)."""
-    key = str(torch.device(device))
+    key = _device_key(device)
     for kept in _DECODE_FLAT_SCRATCH.get(key, []):
         kept[1].zero_()
     for table in (_GEMM_WORKSPACE, _SMALL_M_WORKSPACE, _STREAM_WORKSPACE):
@@ -221,7 +232,7 @@ def _one_stream(device: torch.device | str) -> None:
     overlap would count each other's tiles. The first stream that uses them is remembered; a
     launch from another stream is refused unless it is being captured into a graph (a capture
     runs on a stream of its own and records launches, it runs none)."""
-    key = str(torch.device(device))
+    key = _device_key(device)
     stream = torch.cuda.current_stream(device).cuda_stream
     known = _WORKSPACE_STREAM.setdefault(key, stream)
     if known != stream and not torch.cuda.is_current_stream_capturing():
@@ -245,7 +256,9 @@ def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor 
                   k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor | None,
                   n_heads: int, n_kv: int, head_dim: int, page_size: int) -> None:
     """Rotate q and k of ``qkv [T, (H+2KV)*hd]`` by position (q in place) and write k, v to the
-    pools ``[pages, KV, page_size, hd]`` at ``slots`` (``None``: rotate q only, store nothing)."""
+    pools ``[pages, KV, page_size, hd]`` at ``slots`` (``None``: rotate q only, store nothing).
+    A slot outside the pools or a position outside the tables is not used: the kernel records
+    code 3 in the device's status word, skips the store and rotates by position 0."""
     _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions")
     _need(k_pool, None, "k_pool"); _need(v_pool, None, "v_pool")
     n = qkv.shape[0]
@@ -259,10 +272,11 @@ def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor 
         _need(slots, torch.int32, "slots")
     fn = _fn("elementwise", "pkv_rope_kv_store",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), dtype_code(qkv.dtype), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_pool), _ptr(v_pool),
               dtype_code(k_pool.dtype), _ptr(slots), n, n_heads, n_kv, head_dim, page_size,
-              0 if slots is None else 1, _stream()), "rope_kv_store")
+              0 if slots is None else 1, k_pool.shape[0] * page_size, 0 if cos is None else cos.shape[0],
+              _ptr(status_word(qkv.device)), _stream()), "rope_kv_store")
 
 
 def attention_rows_per_block() -> int:
@@ -275,7 +289,9 @@ def paged_attention_generic(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
                             block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
                             work_seq: torch.Tensor, work_row0: torch.Tensor, n_heads: int, n_kv: int,
                             head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
-    """Causal attention of the (rotated) queries in ``qkv`` over the paged cache; ``[T, H*hd]``."""
+    """Causal attention of the (rotated) queries in ``qkv`` over the paged cache; ``[T, H*hd]``.
+    A table entry that is neither a page of the pool nor -1 is read as no page (zeros) and
+    recorded as code 3 in the device's status word."""
     _need(qkv, None, "qkv"); _need(k_pool, None, "k_pool"); _need(v_pool, None, "v_pool")
     for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
                     ("work_seq", work_seq), ("work_row0", work_row0)):
@@ -284,11 +300,11 @@ def paged_attention_generic(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     out = _empty((n, n_heads * head_dim), qkv.dtype, qkv.device)
     fn = _fn("attention_generic", "pkv_paged_attention_generic",
              [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), dtype_code(qkv.dtype), _ptr(k_pool), _ptr(v_pool),
               dtype_code(k_pool.dtype), _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos),
               _ptr(work_seq), _ptr(work_row0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window),
-              float(scale), _stream()), "paged_attention_generic")
+              float(scale), k_pool.shape[0], _ptr(status_word(qkv.device)), _stream()), "paged_attention_generic")
     return out
 
 
@@ -439,7 +455,7 @@ def _decode_flat_scratch(device: torch.device, floats: int, pairs: int) -> tuple
     once and left zero by every launch. A buffer that has become too small is replaced but kept
     alive, since captured graphs may still point at it."""
     _one_stream(device)
-    key = str(torch.device(device))
+    key = _device_key(device)
     kept = _DECODE_FLAT_SCRATCH.setdefault(key, [])
     if not kept or kept[-1][0].numel() < floats or kept[-1][1].numel() < pairs:
         kept.append((torch.empty((max(floats, 1 << 21),), dtype=torch.float32, device=device),
@@ -508,11 +524,11 @@ def attention_prefill_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.T
         _need(t, torch.int32, name)
     fn = _fn("attention_bf16", "pkv_attention_prefill_bf16",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
               block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_q0),
-              work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), float(scale), _stream()),
-           "attention_prefill_bf16")
+              work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), float(scale), k_pool.shape[0],
+              _ptr(status_word(qkv.device)), _stream()), "attention_prefill_bf16")
 
 
 def attention_decode_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -534,11 +550,13 @@ def attention_decode_bf16(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Te
             raise ValueError("attention scratch is too small for this many splits")
     fn = _fn("attention_bf16", "pkv_attention_decode_bf16",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_int, c_void_p,
+              c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
               block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), work_seq.numel(),
               int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(num_splits),
-              _ptr(scratch), total_rows, _stream()), "attention_decode_bf16")
+              _ptr(scratch), total_rows, k_pool.shape[0], _ptr(status_word(qkv.device)), _stream()),
+           "attention_decode_bf16")
     if num_splits > 8:
         LAUNCHES["count"] += 1   # the merge kernel
 
@@ -562,7 +580,7 @@ def gemm_workspace(device: torch.device | str) -> torch.Tensor:
     """The workspace of the two-SM tcgen05 product on a device (partial accumulators and flags of
     its stream-K hand-over), allocated and zeroed once. Launches on one stream share it."""
     _one_stream(device)
-    key = str(torch.device(device))
+    key = _device_key(device)
     if key not in _GEMM_WORKSPACE:
         lib = library("gemm_tcgen05")
         lib.pkv_gemm_tcgen05_workspace_bytes.restype = c_longlong
@@ -626,7 +644,7 @@ def _small_m_workspace(device: torch.device) -> torch.Tensor:
     """Partial sums and tile counters of ``gemm_small_m`` on a device: allocated and zeroed once,
     left zero by every launch, shared by the launches of a stream."""
     _one_stream(device)
-    key = str(torch.device(device))
+    key = _device_key(device)
     if key not in _SMALL_M_WORKSPACE:
         lib = library("gemm_small_m")
         lib.pkv_gemm_small_m_workspace_bytes.restype = c_longlong
@@ -703,13 +721,17 @@ def gemm_small_m(a: torch.Tensor, b_nk: torch.Tensor, epilogue: str = "bf16", n_
     fn = _fn("gemm_small_m", "pkv_gemm_small_m",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
               c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
-              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_void_p, c_void_p])
     workspace = _small_m_workspace(a.device)
+    num_slots = k_pool.shape[0] * int(page_size) if k_pool is not None else 0
+    max_pos = cos.shape[0] if cos is not None else 0
     code = {"residual": 3, "rope_kv": 4}.get(epilogue) or GEMM_EPILOGUES[epilogue]
     _check(fn(_ptr(a), _ptr(b_nk), _ptr(out), m, n, k, a.stride(0), code, int(n_out), float(clip),
               1 if chained else 0, _ptr(workspace), workspace.numel(), _ptr(hidden), _ptr(weight), _ptr(sumsq_out),
               _ptr(sumsq_in), parts, k, float(eps), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_pool), _ptr(v_pool),
-              _ptr(slots), int(n_heads), int(n_kv), int(head_dim), int(page_size), _stream()), "gemm_small_m")
+              _ptr(slots), int(n_heads), int(n_kv), int(head_dim), int(page_size), num_slots, max_pos,
+              _ptr(status_word(a.device)) if rope_kv is not None else None, _stream()), "gemm_small_m")
     return (out, sumsq_out) if residual is not None else out
 
 
@@ -731,7 +753,7 @@ def _stream_workspace(device: torch.device) -> torch.Tensor:
     """Partial accumulators and tile counters of ``gemm_stream`` on a device: allocated and zeroed
     once, left zero by every launch, shared by the launches of a stream."""
     _one_stream(device)
-    key = str(torch.device(device))
+    key = _device_key(device)
     if key not in _STREAM_WORKSPACE:
         lib = library("gemm_stream")
         lib.pkv_gemm_stream_workspace_bytes.restype = c_longlong

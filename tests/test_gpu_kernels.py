@@ -147,9 +147,12 @@ def test_rope_kv_store(dtype, heads, kv, hd):
 
 
 def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtype, spike=True, fast=False, splits=1,
-                    tcgen05=False, deep_ring=True, flat_blocks=None):
+                    tcgen05=False, deep_ring=True, flat_blocks=None, corrupt=None, expect_status=0):
     """Random sequences already in the cache (``contexts`` tokens each), of which the last
-    ``queries`` tokens are this step's queries. Returns device inputs and the plain answer."""
+    ``queries`` tokens are this step's queries. Returns device inputs and the plain answer.
+    ``corrupt = (sequence, table entry, value)`` puts ``value`` (no page of the pool) into that
+    sequence's block table; the plain answer then has zeros for the keys and values of that page,
+    which is how a kernel must read an entry it cannot use."""
     from paged_kv_serving_b200 import ops
 
     torch_dtype = DTYPES[dtype]
@@ -181,6 +184,10 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
             k_pool[p, :, o] = torch.from_numpy(k[position]).to(torch_dtype).cuda()
             v_pool[p, :, o] = torch.from_numpy(v[position]).to(torch_dtype).cuda()
         tables.append(np.concatenate([table, np.full(width - n_pages, -1)]))
+        if corrupt is not None and corrupt[0] == len(tables) - 1:
+            tables[-1][corrupt[1]] = corrupt[2]
+            k[corrupt[1] * page:(corrupt[1] + 1) * page] = 0.0
+            v[corrupt[1] * page:(corrupt[1] + 1) * page] = 0.0
         full = plain_model.causal_attention(q, k, v, 1.0 / math.sqrt(hd), window=window)
         wants.append(full[context - n_q:].reshape(n_q, heads * hd))
         q_rows.append(q[context - n_q:].reshape(n_q, heads * hd))
@@ -205,7 +212,7 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
                                           dev(np.asarray([s for s, _ in large], dtype=np.int32)),
                                           dev(np.asarray([q for _, q in large], dtype=np.int32)),
                                           heads, kv, hd, page, window or 0, 1.0 / math.sqrt(hd), status)
-            assert int(status.item()) == 0
+            assert int(status.item()) == expect_status
         elif large:
             ops.attention_prefill_bf16(qkv_d, out, k_pool, v_pool, *common,
                                        dev(np.asarray([s for s, _ in large], dtype=np.int32)),
@@ -221,13 +228,13 @@ def _attention_case(rng, *, heads, kv, hd, page, window, contexts, queries, dtyp
                 ops.attention_decode_flat(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
                                           dev(units.astype(np.int32)), max(queries[s] for s in small), heads, kv, hd,
                                           page, window or 0, 1.0 / math.sqrt(hd), flat_blocks, status)
-            assert int(status.item()) == 0
+            assert int(status.item()) == expect_status
         elif small and tcgen05 and ops.attention_decode_tma_supports(hd, page, qkv.shape[1]):
             status = torch.zeros(1, dtype=torch.int32, device="cuda")
             ops.attention_decode_tma(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),
                                      max(queries[s] for s in small), heads, kv, hd, page, window or 0,
                                      1.0 / math.sqrt(hd), splits, status, deep_ring=deep_ring)
-            assert int(status.item()) == 0
+            assert int(status.item()) == expect_status
         elif small:
             scratch = torch.full((q_all.shape[0] * heads * splits * (hd + 2),), float("nan"), device="cuda")
             ops.attention_decode_bf16(qkv_d, out, k_pool, v_pool, *common, dev(np.asarray(small, dtype=np.int32)),

@@ -1,8 +1,10 @@
 """The device's status word and the bounded waits behind it (``-m gpu``).
 
 The kernels that wait on mbarriers give up after a limit, record code 2 in the device's status
-word and return in order; an embedding lookup of an id outside the table records code 1. The
-host reads the word in the copy that brings a step's results back and raises. Nothing here
+word and return in order; an embedding lookup of an id outside the table records code 1; a
+page, a cache slot or a position outside its range records code 3 and is not used (the bad
+index never becomes an address: the store is skipped, the page reads as zeros). The host reads
+the word in the copy that brings a step's results back and raises. Nothing here
 faults, traps or hangs the GPU: the one wait that runs out is a probe that waits, for about a
 millisecond, on a barrier nothing arrives at, and returns by itself.
 """
@@ -120,3 +122,120 @@ def test_sampling_a_draw_at_the_very_top_lands_on_a_kept_token():
             p = plain_model.sample_distribution(logits[row], 0.9, top_p)
             assert p[ids[row]] > 0.0, (vocab, row, int(ids[row]))
             assert ids[row] == int(np.nonzero(p)[0].max()), "the top of the distribution is the last kept id"
+
+
+@pytest.fixture
+def device_status():
+    """The device's own status word (the kernels without a status argument record there), zero
+    before and after."""
+    from paged_kv_serving_b200 import ops
+
+    word = ops.status_word("cuda")
+    word.zero_()
+    yield word
+    word.zero_()
+
+
+@pytest.mark.parametrize("value", [10 ** 6, -5])
+@pytest.mark.parametrize("kernel", ["generic", "mma", "mma-prefill", "tma", "flat", "tcgen05"])
+def test_a_table_entry_that_is_no_page_is_recorded_and_read_as_zeros(kernel, value, device_status):
+    """A block-table entry beyond the pool (or negative and not -1) in the middle of a sequence:
+    every attention kernel records code 3 and reads that page's keys and values as zeros, as it
+    reads -1; the answer is the plain one with those keys and values zeroed."""
+    import test_gpu_kernels as kernels
+
+    rng = np.random.default_rng(len(kernel) + abs(value) % 7)
+    common = dict(heads=8, kv=2, hd=64, page=16, window=None, dtype="bfloat16", spike=False, corrupt=(1, 2, value))
+    if kernel == "generic":
+        got, want = kernels._attention_case(rng, contexts=[40, 100, 17], queries=[1, 3, 17], **common)
+    elif kernel == "mma":
+        got, want = kernels._attention_case(rng, contexts=[40, 100, 17], queries=[1, 2, 1], fast=True, splits=2, **common)
+    elif kernel == "mma-prefill":
+        got, want = kernels._attention_case(rng, contexts=[40, 100, 70], queries=[40, 100, 70], fast=True, **common)
+    elif kernel == "tma":
+        got, want = kernels._attention_case(rng, contexts=[40, 100, 17], queries=[1, 2, 1], fast=True, tcgen05=True, splits=2,
+                                            expect_status=3, **common)
+    elif kernel == "flat":
+        got, want = kernels._attention_case(rng, contexts=[40, 100, 17], queries=[1, 2, 1], fast=True, tcgen05=True,
+                                            flat_blocks=5, expect_status=3, **common)
+    else:
+        got, want = kernels._attention_case(rng, contexts=[40, 200, 70], queries=[40, 200, 70], fast=True, tcgen05=True,
+                                            expect_status=3, **common)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-2 * max(1.0, np.abs(want).max())
+    if kernel in ("generic", "mma", "mma-prefill"):
+        assert int(device_status.item()) == 3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd", [20, 64])
+def test_a_slot_or_position_out_of_range_is_recorded_and_not_used(hd, dtype, device_status):
+    """The rotation and cache-write kernel (both of its forms): a slot beyond the pools is not
+    written to, a position beyond the tables is not looked up; both are recorded as code 3 and
+    every other token is treated as always."""
+    from paged_kv_serving_b200 import ops
+    import plain_model
+    import test_gpu_kernels as kernels
+
+    rng = np.random.default_rng(hd)
+    heads, kv, page, pages, tokens = 4, 2, 4, 6, 7
+    torch_dtype = kernels.DTYPES[dtype]
+    cos, sin = plain_model.rope_tables(32, hd, 10000.0)
+    qkv = rng.standard_normal((tokens, (heads + 2 * kv) * hd)).astype(np.float32)
+    positions = rng.integers(0, 32, size=tokens).astype(np.int32)
+    slots = rng.permutation(pages * page)[:tokens].astype(np.int32)
+    for bad_slot, bad_position in ((pages * page + 3, None), (-9, None), (None, 32), (None, -1)):
+        device_status.zero_()
+        s, p = slots.copy(), positions.copy()
+        if bad_slot is not None:
+            s[2] = bad_slot
+        if bad_position is not None:
+            p[4] = bad_position
+        qkv_d = kernels.dev(qkv, torch_dtype)
+        seen = kernels.as_np(qkv_d).copy()
+        k_pool = torch.full((pages, kv, page, hd), float("nan"), dtype=torch_dtype, device="cuda")
+        v_pool = torch.full((pages, kv, page, hd), float("nan"), dtype=torch_dtype, device="cuda")
+        ops.rope_kv_store(qkv_d, kernels.dev(p), kernels.dev(cos), kernels.dev(sin), k_pool, v_pool, kernels.dev(s),
+                          heads, kv, hd, page)
+        assert int(device_status.item()) == 3
+        kp, vp = kernels.as_np(k_pool), kernels.as_np(v_pool)
+        k = seen[:, heads * hd:(heads + kv) * hd].reshape(tokens, kv, hd)
+        v = seen[:, (heads + kv) * hd:].reshape(tokens, kv, hd)
+        used = np.where((p >= 0) & (p < 32), p, 0)
+        k_rot = plain_model.apply_rope(k, used, cos, sin)
+        written = np.zeros((pages, page), dtype=bool)
+        for t in range(tokens):
+            if not 0 <= s[t] < pages * page:
+                continue
+            at, offset = divmod(int(s[t]), page)
+            written[at, offset] = True
+            assert np.abs(kp[at, :, offset] - k_rot[t]).max() <= kernels.tol(dtype, 4)
+            assert np.abs(vp[at, :, offset] - v[t]).max() <= kernels.tol(dtype, 1e-3)
+        untouched = np.broadcast_to(~written[:, None, :], (pages, kv, page))
+        assert np.isnan(kp[untouched]).all() and np.isnan(vp[untouched]).all()
+
+
+def test_the_fused_projection_checks_slots_and_positions_too(device_status):
+    """The decode projection with rotation and cache write in its epilogue: the same two checks."""
+    from paged_kv_serving_b200 import ops
+    import plain_model
+    import test_gpu_kernels as kernels
+
+    rng = np.random.default_rng(5)
+    heads, kv, hd, page, pages, rows, width = 4, 2, 64, 16, 3, 5, 256
+    cos, sin = plain_model.rope_tables(64, hd, 10000.0)
+    x = kernels.dev(rng.standard_normal((rows, width)).astype(np.float32), torch.bfloat16)
+    w = kernels.dev((rng.standard_normal(((heads + 2 * kv) * hd, width)) * 0.05).astype(np.float32), torch.bfloat16)
+    positions = np.asarray([3, 9, 64, 1, 0], dtype=np.int32)                  # one beyond the tables
+    slots = np.asarray([0, 17, 5, pages * page, 40], dtype=np.int32)          # one beyond the pools
+    k_pool = torch.full((pages, kv, page, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    v_pool = torch.full((pages, kv, page, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = ops.gemm_small_m(x, w, "rope_kv", rope_kv=(kernels.dev(positions), kernels.dev(cos), kernels.dev(sin), k_pool,
+                                                      v_pool, kernels.dev(slots), heads, kv, hd, page))
+    assert int(device_status.item()) == 3
+    assert torch.isfinite(out[:, :heads * hd].float()).all()
+    written = torch.isfinite(k_pool.float()).any(dim=(1, 3))                  # [pages, page]
+    expect = torch.zeros_like(written)
+    for slot in (0, 17, 5, 40):
+        expect[slot // page, slot % page] = True
+    assert torch.equal(written, expect)
