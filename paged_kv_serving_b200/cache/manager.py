@@ -75,6 +75,7 @@ class KVCacheManager:
         if not groups:
             groups = []
         self.group_specs = list(groups)
+        self._windowed = any(spec.window is not None for spec in self.group_specs)
         self.block_size = block_size
         self.num_blocks = num_blocks
         self.store = store
@@ -203,6 +204,13 @@ class KVCacheManager:
         bs = self.block_size
         first = sequence.num_computed_tokens // bs
         last = -(-up_to_tokens // bs)
+        # the usual decode step: the token's page is there and nobody else holds it
+        if last == first + 1:
+            for allocator, table in zip(self.allocators, sequence.block_tables):
+                if first >= len(table) or (table[first] != NULL_PAGE and allocator.holders(table[first]) != 1):
+                    break
+            else:
+                return
         plans = []
         for allocator, table in zip(self.allocators, sequence.block_tables):
             extra = max(0, last - len(table))
@@ -231,16 +239,21 @@ class KVCacheManager:
         ``num_computed_tokens - W`` is out of reach. Returns the number of pages given back.
         """
         released = 0
+        if not self._windowed:
+            return released
         for spec, allocator, table in zip(self.group_specs, self.allocators, sequence.block_tables):
             if spec.window is None:
                 continue
             dead_positions = sequence.num_computed_tokens - spec.window + 1   # positions < this are dead
             dead_pages = max(0, dead_positions // self.block_size)
-            for i in range(min(dead_pages, len(table))):
-                if table[i] != NULL_PAGE:
-                    allocator.release(table[i])
-                    table[i] = NULL_PAGE
-                    released += 1
+            # pages are given back from the front, so the ones already gone form a prefix: walk
+            # back from the newest dead page until one of them is met
+            i = min(dead_pages, len(table)) - 1
+            while i >= 0 and table[i] != NULL_PAGE:
+                allocator.release(table[i])
+                table[i] = NULL_PAGE
+                released += 1
+                i -= 1
         return released
 
     # --- state slots ---------------------------------------------------------------------

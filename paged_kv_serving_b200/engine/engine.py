@@ -355,6 +355,7 @@ class Engine:
         flight = _Flight(self._iteration, self.clock(), plan, [])
         device_logits, host_rows, row_of = self._run(plan)
         enders: list[Sequence] = []
+        block_size = self.config.block_size
         for item in plan.scheduled:
             sequence = item.sequence
             state = self._requests.get(sequence.request.request_id)
@@ -362,7 +363,8 @@ class Engine:
                 state.cached_prompt_tokens = max(state.cached_prompt_tokens,
                                                  sequence.cached_prefix_blocks * self.config.block_size)
             sequence.num_computed_tokens += item.num_tokens
-            self.cache.publish_full_blocks(sequence)
+            if sequence.num_computed_tokens // block_size > len(sequence.block_hashes):
+                self.cache.publish_full_blocks(sequence)      # a page was filled
             self.cache.release_behind_window(sequence)
             if item.produces_token:
                 enders.append(sequence)

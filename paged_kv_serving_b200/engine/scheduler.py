@@ -196,8 +196,9 @@ class Scheduler:
 
     def _decode_phase(self, plan: _StepPlan) -> None:
         pending = sorted((s for s in self._running if s.is_decoding), key=Sequence.priority_key)
-        while pending and plan.budget > 0:
-            sequence = pending[0]
+        at = 0                                   # pending[at:] are still to be scheduled
+        while at < len(pending) and plan.budget > 0:
+            sequence = pending[at]
             try:
                 self.cache.reserve(sequence, sequence.num_tokens)
             except OutOfPages:
@@ -210,7 +211,7 @@ class Scheduler:
                     pending.pop()
                 self._preempt(victim, plan)
                 continue
-            pending.pop(0)
+            at += 1
             plan.spend(sequence, 1, prefill=False, produces=True)
 
     def _prompt_phase(self, plan: _StepPlan) -> None:

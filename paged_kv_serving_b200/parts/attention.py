@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import contextlib
 import math
 
 import numpy as np
@@ -34,6 +35,20 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
     if key not in _SIDE_STREAM:
         _SIDE_STREAM[key] = torch.cuda.Stream(device=device, priority=-1)
     return _SIDE_STREAM[key]
+
+
+@contextlib.contextmanager
+def _second_stream(device: torch.device):
+    """What is launched inside runs on the device's second stream, after everything the current
+    stream holds so far; the caller lets the current stream wait for it when it needs the result."""
+    main = torch.cuda.current_stream(device)
+    side = _side_stream(device)
+    side.wait_stream(main)
+    torch.cuda.set_stream(side)
+    try:
+        yield side
+    finally:
+        torch.cuda.set_stream(main)
 
 
 @register_part("mixer", "attention")
@@ -294,23 +309,13 @@ class PagedAttention(Part):
             # In a mixed step the portions' kernel (few blocks, bound by its own latencies) and the
             # decode kernel (bound by memory) work on different entries and write different rows:
             # the first runs on a second stream of higher priority beside the other
-            beside = (self.OVERLAP_MIXED and plan["n_decode"] and self._decode_tma(group.page_size)
-                      and not torch.cuda.is_current_stream_capturing())
-            main = torch.cuda.current_stream(qkv.device) if beside else None
-            if beside:
-                side = _side_stream(qkv.device)
-                side.wait_stream(main)
-                torch.cuda.set_stream(side)
-            try:
+            joined = bool(self.OVERLAP_MIXED and plan["n_decode"] and self._decode_tma(group.page_size)
+                          and not torch.cuda.is_current_stream_capturing())
+            with _second_stream(qkv.device) if joined else contextlib.nullcontext():
                 ops.attention_prefill_tcgen05(qkv, out, k_pool, v_pool, table, starts, first,
                                               ctx.ints(names["prefill_seq"]), ctx.ints(names["prefill_q0"]), self.n_heads,
                                               self.n_kv_heads, self.head_dim, group.page_size, self.window or 0,
                                               self.scale, ops.status_word(qkv.device))
-            finally:
-                if beside:
-                    torch.cuda.set_stream(main)
-            if beside:
-                joined = True
         elif plan["n_prefill"]:
             ops.attention_prefill_bf16(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["prefill_seq"]),
                                        ctx.ints(names["prefill_q0"]), self.n_heads, self.n_kv_heads, self.head_dim,
