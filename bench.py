@@ -55,7 +55,10 @@ def load_peaks() -> dict:
     if path.is_file():
         try:
             data = json.loads(path.read_text())
-            return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+            peaks = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in data:
+                peaks["bf16_tflops_sustained"] = float(data["bf16_tflops_sustained"])
+            return peaks
         except (ValueError, KeyError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -176,6 +179,9 @@ def run(args) -> dict:
     prefill_flops = gemm_flops + attention_flops
     prefill = {"value": t / (prefill_ms / 1e3), "tokens": t, "ms": prefill_ms,
                "frac": prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+    if "bf16_tflops_sustained" in peaks:
+        # beside the burst rate: the library's rate in a seconds-long loop under the power cap
+        prefill["frac_of_sustained"] = prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12)
 
     # ---- fill the cache of every sequence (not timed) ------------------------------------------
     per_step = max(1, 4096 // prompt_len)
