@@ -149,6 +149,7 @@ class ModelRunner:
         self._last_graph_step: tuple[ExecutionBatch, tuple[int, int]] | None = None
         self._ahead: dict | None = None
         self._graph_pool = torch.cuda.graph_pool_handle() if use_graphs else None
+        self._capture_stream = None
         # memory for the outputs of a step's kernels (steps that are not graph replays); it grows to
         # what the largest step needed and is reused by every step after it
         self._arena = arena.StepArena(model.device)
@@ -378,14 +379,27 @@ class ModelRunner:
         # middle of it, an object that owns CUDA resources (the graphs and memory pool of a runner
         # that died in a reference cycle), the driver would refuse the call during capture and the
         # capture would be void. (Entering the capture collects garbage first.)
+        # The capture runs on a stream of its own between capture_begin and capture_end; the
+        # library's context manager would also collect garbage and empty the allocator's cache
+        # first, which costs tens of milliseconds with a few hundred live requests and is not
+        # needed with a memory pool of the graphs' own.
         collecting = gc.isenabled()
         gc.disable()
+        main = torch.cuda.current_stream(self.model.device)
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.model.device)
+        self._capture_stream.wait_stream(main)
         try:
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                captured = self._forward(ctx, True)
+            with torch.cuda.stream(self._capture_stream):
+                graph.capture_begin(pool=self._graph_pool)
+                try:
+                    captured = self._forward(ctx, True)
+                finally:
+                    graph.capture_end()
         finally:
             if collecting:
                 gc.enable()
+        main.wait_stream(self._capture_stream)
         launches = ops.launch_count() - before
         ops.LAUNCHES["count"] = before                     # a capture records launches, it runs none
         self._graphs[key] = {"graph": graph, "ints": ints, "logits": captured, "signature": ctx.arena.signature(),
