@@ -147,6 +147,38 @@ def test_odd_feed_forward_and_vocabulary_sizes(name, d_ff, vocab, n_kv, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd, heads, kv, page", [(16, 5, 5, 32), (48, 4, 2, 16), (80, 2, 1, 8), (96, 3, 3, 16), (112, 2, 2, 4),
+                                                   (144, 2, 1, 16), (128, 4, 1, 128), (64, 6, 3, 64)])
+def test_head_sizes_head_counts_and_page_sizes_through_the_engine(hd, heads, kv, page, dtype):
+    """Head sizes in steps of 16 (and one beyond 128), head counts and groupings that are no
+    power of two, pages of 4 to 128 keys: whichever attention kernel the engine picks for them, a
+    prompt in two portions beside a second request, then both decoding, against the plain
+    implementation."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    config = dict(helpers.TINY_A, d_model=heads * hd, n_heads=heads, n_kv_heads=kv, head_dim=hd, d_ff=96, vocab_size=300,
+                  n_layers=2, max_seq_len=256)
+    tensors = plain_model.random_tensors(config, seed=hd, std=0.05)
+    if dtype == "bfloat16":
+        tensors = {k: (plain_model.round_to_bfloat16(v) if v.ndim == 2 else v) for k, v in tensors.items()}
+    model = helpers.build_model(config, tensors, dtype)
+    rng = np.random.default_rng(hd)
+    a = [int(t) for t in rng.integers(0, 300, size=170)]
+    b = [int(t) for t in rng.integers(0, 300, size=80)]
+    want_a, want_b = plain_model.forward(config, tensors, np.asarray(a)), plain_model.forward(config, tensors, np.asarray(b))
+    session = ReplaySession(model, max_tokens=320, block_size=page)
+    got = session.step([{"id": "a", "tokens": a[:150], "want": [0, 77, 149]}])
+    helpers.assert_close(got, want_a[[0, 77, 149]], dtype, f"head size {hd}: first portion")
+    got = session.step([{"id": "a", "tokens": a[150:152], "want": [1]}, {"id": "b", "tokens": b[:60], "want": [59]}])
+    helpers.assert_close(got, np.stack([want_a[151], want_b[59]]), dtype, f"head size {hd}: two tokens beside a prompt")
+    for i in range(152, 170):
+        entries = [{"id": "a", "tokens": [a[i]], "want": [0]}, {"id": "b", "tokens": [b[i - 92]], "want": [0]}]
+        got = session.step(entries)
+        helpers.assert_close(got, np.stack([want_a[i], want_b[i - 92]]), dtype, f"head size {hd}: decoding at {i}")
+    session.runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_and_single_token_prompt(dtype):
     session, tensors = _session("B", dtype, 256)
     tokens = helpers.random_tokens(helpers.TINY_B, 5, seed=14)
