@@ -399,6 +399,70 @@ def test_attention_bf16_tensor_core_kernels_window_edges(window):
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 
 
+@pytest.mark.parametrize("kernel", ["generic", "mma", "tma", "flat", "tcgen05"])
+def test_attention_kernels_at_a_long_context(kernel):
+    """One sequence of 40,000 cached tokens (2,500 pages in shuffled order): the last token's
+    decode step, and for the prefill kernel the last 128 positions as one portion. One key near
+    the beginning and one near the end stand out for every query, so a tile that is dropped, read
+    twice or taken from the wrong page changes the answer; the plain answer is computed for the
+    queried rows only."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(40)
+    heads, kv, hd, page, context = 4, 2, 128, 16, 40_000
+    n_q = 128 if kernel == "tcgen05" else 1
+    pages = context // page
+    order = rng.permutation(pages + 5)[:pages]
+    k = rng.standard_normal((context, kv, hd)).astype(np.float32) * 0.5
+    v = rng.standard_normal((context, kv, hd)).astype(np.float32)
+    q = rng.standard_normal((n_q, heads, hd)).astype(np.float32) * 0.5
+    for far in (37, context - 300):
+        k[far] = 0.0
+        k[far, :, 0] = 5.0
+    q[:, :, 0] = 5.0
+    k, v, q = (torch.from_numpy(t).to(torch.bfloat16).float().numpy() for t in (k, v, q))
+    k_pool = torch.zeros((pages + 5, kv, page, hd), dtype=torch.bfloat16, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    k_pool[torch.from_numpy(order).cuda()] = torch.from_numpy(k).to(torch.bfloat16).cuda().view(pages, page, kv, hd).transpose(1, 2)
+    v_pool[torch.from_numpy(order).cuda()] = torch.from_numpy(v).to(torch.bfloat16).cuda().view(pages, page, kv, hd).transpose(1, 2)
+    scale = 1.0 / math.sqrt(hd)
+    want = np.zeros((n_q, heads, hd), dtype=np.float32)
+    for row in range(n_q):
+        visible = context - n_q + row + 1
+        for h in range(heads):
+            scores = (k[:visible, h // (heads // kv)] @ q[row, h]) * np.float32(scale)
+            weights = np.exp(scores - scores.max())
+            want[row, h] = (weights / weights.sum()) @ v[:visible, h // (heads // kv)]
+    want = want.reshape(n_q, heads * hd)
+    qkv = np.concatenate([q.reshape(n_q, heads * hd), np.zeros((n_q, 2 * kv * hd), dtype=np.float32)], axis=1)
+    qkv_d = dev(qkv, torch.bfloat16)
+    table, starts, first = dev(order[None, :].astype(np.int32)), dev(np.asarray([0, n_q], dtype=np.int32)), \
+        dev(np.asarray([context - n_q], dtype=np.int32))
+    out = torch.full((n_q, heads * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    one = dev(np.asarray([0], dtype=np.int32))
+    if kernel == "generic":
+        rows = ops.attention_rows_per_block()
+        work = np.arange(0, n_q * (heads // kv), rows, dtype=np.int32)
+        out = ops.paged_attention_generic(qkv_d, k_pool, v_pool, table, starts, first, dev(np.zeros_like(work)), dev(work),
+                                          heads, kv, hd, page, 0, scale)
+    elif kernel == "mma":
+        ops.attention_decode_bf16(qkv_d, out, k_pool, v_pool, table, starts, first, one, 1, heads, kv, hd, page, 0, scale, 8, None)
+    elif kernel == "tma":
+        ops.attention_decode_tma(qkv_d, out, k_pool, v_pool, table, starts, first, one, 1, heads, kv, hd, page, 0, scale, 8, status)
+    elif kernel == "flat":
+        units = dev(np.asarray([0, context // 64], dtype=np.int32))
+        ops.attention_decode_flat(qkv_d, out, k_pool, v_pool, table, starts, first, one, units, 1, heads, kv, hd, page, 0, scale,
+                                  64, status)
+    else:
+        ops.attention_prefill_tcgen05(qkv_d, out, k_pool, v_pool, table, starts, first, one, one, heads, kv, hd, page, 0, scale,
+                                      status)
+    assert int(status.item()) == 0
+    got = as_np(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol("bfloat16", 2)
+
+
 def test_attention_refuses_what_it_cannot_do():
     from paged_kv_serving_b200 import ops
 
