@@ -202,6 +202,32 @@ def test_long_decoding(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_a_prompt_of_2500_tokens_in_two_portions_then_decoding(dtype):
+    """Config D with room for longer sequences: 1,300 tokens, then 1,190 above them (the second
+    portion's query blocks start over 1,300 cached keys, 40 key tiles deep at the end), then ten
+    tokens one by one; every 97th position and the last ones against the plain implementation."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    config = dict(helpers.TINY_D, max_seq_len=4096)
+    tensors = plain_model.random_tensors(config, seed=21, std=0.05)
+    if dtype == "bfloat16":
+        tensors = {k: (plain_model.round_to_bfloat16(v) if v.ndim == 2 else v) for k, v in tensors.items()}
+    model = helpers.build_model(config, tensors, dtype)
+    tokens = helpers.random_tokens(config, 2500, seed=22)
+    want = plain_model.forward(config, tensors, np.asarray(tokens))
+    session = ReplaySession(model, max_tokens=2560, block_size=16)
+    first = list(range(0, 1300, 97)) + [1299]
+    got = session.step([{"id": "r", "tokens": tokens[:1300], "want": first}])
+    helpers.assert_close(got, want[first], dtype, "first 1,300 tokens")
+    second = list(range(5, 1190, 97)) + [1188, 1189]
+    got = session.step([{"id": "r", "tokens": tokens[1300:2490], "want": second}])
+    helpers.assert_close(got, want[[1300 + i for i in second]], dtype, "1,190 tokens above 1,300 cached ones")
+    got = [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens[2490:]]
+    helpers.assert_close(np.concatenate(got), want[2490:], dtype, "decoding at 2,490 tokens of context")
+    session.runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_captured_decode_steps_equal_eager_ones(dtype):
     """Decode-only steps replay CUDA graphs; the same steps without graphs give the same logits,
     also when the number of live requests changes from step to step."""
