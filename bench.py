@@ -386,9 +386,10 @@ def run_serve(args) -> dict:
     # are loaded; the graphs of the block-table widths to come are still captured inside the run
     warm = [Request(f"warm{i}", tuple(int(t) for t in rng.integers(0, config.vocab_size, size=1365)),
                     SamplingParams(max_new_tokens=3, temperature=0.7)) for i in range(12)]
-    warm += [Request(f"warm-short{i}", tuple(int(t) for t in rng.integers(0, config.vocab_size, size=24)),
-                     SamplingParams(max_new_tokens=3, temperature=0.7)) for i in range(count)]
     engine.generate(warm)
+    for size in (24, 48, 100, count):         # decode steps of the 32-, 64-, 128- and 256-row buckets
+        engine.generate([Request(f"warm{size}-{i}", tuple(int(t) for t in rng.integers(0, config.vocab_size, size=24)),
+                                 SamplingParams(max_new_tokens=3, temperature=0.7)) for i in range(min(size, count))])
     engine.flush_prefix_cache()
     torch.cuda.synchronize()
     started = time.perf_counter()

@@ -29,7 +29,7 @@ import torch
 from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.cache.manager import KVCacheManager
 from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
-from paged_kv_serving_b200.engine.sequence import Request, SamplingParams, Sequence
+from paged_kv_serving_b200.engine.sequence import PageTable, Request, SamplingParams, Sequence
 
 __all__ = ["ReplaySession", "main"]
 
@@ -82,7 +82,8 @@ class ReplaySession:
             self.cache.reserve(sequence, start + len(tokens))
             batch_entries.append(BatchEntry(
                 seq_id=name, token_ids=tuple(tokens), first_position=start,
-                block_tables=tuple(tuple(table) for table in sequence.block_tables),
+                block_tables=tuple(table.snapshot() if isinstance(table, PageTable) else tuple(table)
+                                   for table in sequence.block_tables),
                 logits_at=want, state_slot=sequence.state_slot))
             advanced.append((sequence, len(tokens)))
         clear = self.cache.state_slots.take_slots_to_clear() if self.cache.state_slots is not None else None

@@ -24,6 +24,7 @@ from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.cache.manager import GroupSpec, plan_groups
 from paged_kv_serving_b200.cache.pages import NULL_PAGE
 from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+from paged_kv_serving_b200.engine.sequence import TableSnapshot
 from paged_kv_serving_b200.models.decoder import DecoderModel
 from paged_kv_serving_b200.ops import arena, gemm
 from paged_kv_serving_b200.parts.base import CacheBinding, GroupView, IntArena, StepContext
@@ -257,7 +258,8 @@ class ModelRunner:
                 width = table_width
             table = np.full((len(entries), width), NULL_PAGE, dtype=np.int32)
             for i, e in enumerate(entries):
-                table[i, :len(e.block_tables[g])] = e.block_tables[g]
+                pages = e.block_tables[g]
+                table[i, :len(pages)] = pages.array if isinstance(pages, TableSnapshot) else pages
             page_of_token = table[seq_of_token, positions // self.block_size].astype(np.int64)
             slots = np.where(page_of_token >= 0, page_of_token * self.block_size + positions % self.block_size, -1)
             table_name, slots_name = f"group{g}/block_table", f"group{g}/slots"

@@ -31,7 +31,7 @@ from paged_kv_serving_b200.cache.manager import KVCacheManager
 from paged_kv_serving_b200.cache.pages import OutOfPages
 from paged_kv_serving_b200.config.engine_config import EngineConfig
 from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
-from paged_kv_serving_b200.engine.sequence import Sequence, SequenceStatus
+from paged_kv_serving_b200.engine.sequence import PageTable, Sequence, SequenceStatus
 
 __all__ = ["ScheduledSequence", "Scheduler", "SchedulerOutput", "SchedulerStats"]
 
@@ -291,7 +291,8 @@ class Scheduler:
             seq_id=sequence.seq_id,
             token_ids=tuple(sequence.token_ids[start:start + item.num_tokens]),
             first_position=start,
-            block_tables=tuple(tuple(table) for table in sequence.block_tables),
+            block_tables=tuple(table.snapshot() if isinstance(table, PageTable) else tuple(table)
+                               for table in sequence.block_tables),
             logits_at=(item.num_tokens - 1,) if item.produces_token else (),
             state_slot=sequence.state_slot,
         )

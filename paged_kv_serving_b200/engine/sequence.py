@@ -19,8 +19,8 @@ from enum import Enum
 import numpy as np
 
 __all__ = [
-    "GREEDY_TEMPERATURE", "FinishReason", "Request", "SamplingParams", "Sequence", "SequenceStatus",
-    "SloClass", "finish_reason_for", "new_sequence_id",
+    "GREEDY_TEMPERATURE", "FinishReason", "PageTable", "Request", "SamplingParams", "Sequence", "SequenceStatus",
+    "SloClass", "TableSnapshot", "finish_reason_for", "new_sequence_id",
 ]
 
 #: Below this temperature a request is decoded greedily
@@ -128,6 +128,59 @@ def new_sequence_id(request_id: str, index: int) -> str:
     return f"{request_id}#{index}"
 
 
+class TableSnapshot(tuple):
+    """The page numbers of a ``PageTable`` at one moment: a tuple (what a batch entry holds) that
+    also gives them as an int32 array, made once."""
+
+    @property
+    def array(self) -> np.ndarray:
+        made = self.__dict__.get("_array")
+        if made is None:
+            made = self.__dict__["_array"] = np.asarray(self, dtype=np.int32)
+            made.flags.writeable = False
+        return made
+
+
+class PageTable(list):
+    """A sequence's pages in one page group, in logical order: a list that keeps an immutable
+    copy of itself until it is changed. A decode step of hundreds of sequences changes a few
+    tables (a page is added every ``block_size`` tokens); the others hand the step the tuple and
+    the array they made before."""
+
+    __slots__ = ("_snapshot",)
+
+    def __init__(self, *args) -> None:
+        super().__init__(*args)
+        self._snapshot = None
+
+    def snapshot(self) -> TableSnapshot:
+        made = self._snapshot
+        if made is None:
+            made = self._snapshot = TableSnapshot(self)
+        return made
+
+    def _changed(method):  # noqa: N805 - wraps the list methods that change the content
+        def wrapper(self, *args, **kwargs):
+            self._snapshot = None
+            return method(self, *args, **kwargs)
+        wrapper.__name__ = method.__name__
+        return wrapper
+
+    append = _changed(list.append)
+    extend = _changed(list.extend)
+    insert = _changed(list.insert)
+    pop = _changed(list.pop)
+    remove = _changed(list.remove)
+    clear = _changed(list.clear)
+    reverse = _changed(list.reverse)
+    sort = _changed(list.sort)
+    __setitem__ = _changed(list.__setitem__)
+    __delitem__ = _changed(list.__delitem__)
+    __iadd__ = _changed(list.__iadd__)
+    __imul__ = _changed(list.__imul__)
+    del _changed
+
+
 @dataclass(slots=True)
 class Sequence:
     """One sample of a request."""
@@ -136,7 +189,7 @@ class Sequence:
     request: Request
     sample_index: int = 0
     token_ids: list[int] = field(default_factory=list)
-    block_tables: list[list[int]] = field(default_factory=lambda: [[]])   # one table per page group
+    block_tables: list[list[int]] = field(default_factory=lambda: [PageTable()])   # one table per page group
     num_computed_tokens: int = 0
     status: SequenceStatus = SequenceStatus.WAITING
     finish_reason: FinishReason | None = None
@@ -161,7 +214,7 @@ class Sequence:
         seed = np.random.SeedSequence(entropy=request.sampling.seed, spawn_key=(sample_index,))
         return cls(seq_id=new_sequence_id(request.request_id, sample_index), request=request,
                    sample_index=sample_index, token_ids=[int(t) for t in request.prompt_token_ids],
-                   block_tables=[[] for _ in range(max(1, num_groups))], rng=np.random.default_rng(seed))
+                   block_tables=[PageTable() for _ in range(max(1, num_groups))], rng=np.random.default_rng(seed))
 
     # --- lengths -------------------------------------------------------------------------
 
@@ -216,7 +269,7 @@ class Sequence:
         self.preemption_count += 1
         self.num_computed_tokens = self.cached_prefix_blocks = 0
         self.block_hashes = []
-        self.block_tables = [[] for _ in self.block_tables]
+        self.block_tables = [PageTable() for _ in self.block_tables]
 
     def finish(self, reason: FinishReason, now: float) -> None:
         aborted = reason is FinishReason.ABORTED

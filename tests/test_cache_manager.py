@@ -11,13 +11,14 @@ from __future__ import annotations
 import random
 from types import SimpleNamespace
 
+import numpy as np
 import pytest
 
 from paged_kv_serving_b200.cache import (
     NULL_PAGE, AllocatorInvariantError, GroupSpec, KVCacheManager, OutOfPages, PageAllocator, PrefixCache,
     RecordingPageStore, StateSlotPool, hash_chain, plan_groups,
 )
-from paged_kv_serving_b200.engine.sequence import Request, SamplingParams, Sequence
+from paged_kv_serving_b200.engine.sequence import PageTable, Request, SamplingParams, Sequence
 from paged_kv_serving_b200.parts import PagedKVRequest, StateRequest
 
 
@@ -330,8 +331,26 @@ def test_random_orders_keep_the_books(seed, windowed):
             assert tuple(expected) == allocator.snapshot()
         for s in live:
             store.check(s, windows)
+            # the immutable copy a table hands to a step follows every change made to the table
+            assert all(isinstance(t, PageTable) and t.snapshot() == tuple(t) and t.snapshot().array.tolist() == list(t)
+                       for t in s.block_tables)
     for s in live:
         manager.free(s)
     manager.prefix_cache.flush()
     manager.check_invariants()
     assert all(a.num_free == a.num_pages for a in manager.allocators)
+
+
+def test_a_page_table_makes_its_copy_once_and_again_after_any_change():
+    table = PageTable([4, 7])
+    first = table.snapshot()
+    assert first == (4, 7) and table.snapshot() is first and first.array.dtype == np.int32
+    changes = [lambda t: t.append(1), lambda t: t.extend([2, 3]), lambda t: t.__setitem__(0, NULL_PAGE), lambda t: t.pop(),
+               lambda t: t.insert(1, 9), lambda t: t.__delitem__(0), lambda t: t.__iadd__([5]), lambda t: t.clear()]
+    for change in changes:
+        before = table.snapshot()
+        frozen = tuple(before)
+        change(table)
+        after = table.snapshot()
+        assert after == tuple(table) and after is not before and before == frozen, "a copy never changes, a change makes a new one"
+        assert after.array.tolist() == list(table) and not after.array.flags.writeable
