@@ -144,7 +144,8 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
   }
 }
 
-// Tensor maps over the page pools, one per (pool, size): [rows = pages x kv heads x page size,
+// Tensor maps over the page pools, one per (pool, size), copied to the caller (a later lookup may
+// take a table entry's place): [rows = pages x kv heads x page size,
 // head size], boxes of one page: of its one 64-column panel (head size 64) or of both, group of 8
 // rows by group (head size 128). Kept for the life of the library, since a captured graph holds
 // them by value and a step asks for the same few again and again.
@@ -155,18 +156,27 @@ struct DecMapKey {
   CUtensorMap map;
 };
 
-static const CUtensorMap* decode_pool_map(const void* base, long long rows, int hd, int box_rows) {
+static bool decode_pool_map(const void* base, long long rows, int hd, int box_rows, CUtensorMap* out) {
   static DecMapKey cache[512];
   static int used = 0;
   for (int i = 0; i < used; ++i)
-    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) return &cache[i].map;
-  DecMapKey& slot = cache[used < 512 ? used : 511];
+    if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows) {
+      *out = cache[i].map;
+      return true;
+    }
+  static int victim = 0;              // a full table gives up its entries in turn
+  DecMapKey& slot = cache[used < 512 ? used : victim];
   const int rc = hd == 128 ? make_panel_group_map(&slot.map, base, rows, 2, box_rows)
                            : make_tile_map(&slot.map, base, rows, hd, hd, box_rows);
-  if (rc) return nullptr;
+  if (rc) {
+    slot.base = nullptr;
+    return false;
+  }
   slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows;
   if (used < 512) ++used;
-  return &slot.map;
+  else victim = (victim + 1) % 512;
+  *out = slot.map;
+  return true;
 }
 
 }  // namespace pkv

@@ -447,9 +447,9 @@ PKV_EXPORT int pkv_attention_decode_flat(const void* qkv, int q_row_stride, void
   const long long pool_rows = n_pages * n_kv * page_size;
   if (pool_rows >= (1LL << 31) - page_size) return PKV_ERR_LIMIT;
   if ((uintptr_t)qkv % 4 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)workspace % 16) return PKV_ERR_ALIGN;
-  const CUtensorMap* map_k = decode_pool_map(k_pool, pool_rows, hd, page_size);
-  const CUtensorMap* map_v = decode_pool_map(v_pool, pool_rows, hd, page_size);
-  if (!map_k || !map_v) return PKV_ERR_SIZE;
+  alignas(64) CUtensorMap map_k, map_v;
+  if (!decode_pool_map(k_pool, pool_rows, hd, page_size, &map_k) || !decode_pool_map(v_pool, pool_rows, hd, page_size, &map_v))
+    return PKV_ERR_SIZE;
   int shift = -1;
   for (int i = 0; i < 31; ++i)
     if ((1 << i) == page_size) shift = i;
@@ -457,5 +457,5 @@ PKV_EXPORT int pkv_attention_decode_flat(const void* qkv, int q_row_stride, void
                   unit_starts, n_work, n_heads, n_kv, page_size, shift, window, scale * 1.4426950408889634f,
                   (int)pool_rows, (float*)workspace, counters, status};
   cudaStream_t s = (cudaStream_t)stream;
-  return hd == 128 ? launch_flat<128>(*map_k, *map_v, p, blocks, s) : launch_flat<64>(*map_k, *map_v, p, blocks, s);
+  return hd == 128 ? launch_flat<128>(map_k, map_v, p, blocks, s) : launch_flat<64>(map_k, map_v, p, blocks, s);
 }

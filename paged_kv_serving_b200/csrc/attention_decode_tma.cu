@@ -443,9 +443,9 @@ PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void*
   const long long pool_rows = n_pages * n_kv * page_size;
   if (pool_rows >= (1LL << 31) - page_size) return PKV_ERR_LIMIT;
   if ((uintptr_t)qkv % 4 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16) return PKV_ERR_ALIGN;
-  const CUtensorMap* map_k = decode_pool_map(k_pool, pool_rows, hd, page_size);
-  const CUtensorMap* map_v = decode_pool_map(v_pool, pool_rows, hd, page_size);
-  if (!map_k || !map_v) return PKV_ERR_SIZE;
+  alignas(64) CUtensorMap map_k, map_v;
+  if (!decode_pool_map(k_pool, pool_rows, hd, page_size, &map_k) || !decode_pool_map(v_pool, pool_rows, hd, page_size, &map_v))
+    return PKV_ERR_SIZE;
   int shift = -1;
   for (int i = 0; i < 31; ++i)
     if ((1 << i) == page_size) shift = i;
@@ -458,6 +458,6 @@ PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void*
   // deep ring: one block per SM with six stages in flight (few blocks, long key ranges);
   // shallow ring: three stages, two blocks per SM, so that one block's start and merge hide
   // behind the other's streaming (many blocks)
-  if (hd == 128) return deep_ring ? launch_dec<128, 6>(*map_k, *map_v, p, n_work, s) : launch_dec<128, 3>(*map_k, *map_v, p, n_work, s);
-  return deep_ring ? launch_dec<64, 6>(*map_k, *map_v, p, n_work, s) : launch_dec<64, 3>(*map_k, *map_v, p, n_work, s);
+  if (hd == 128) return deep_ring ? launch_dec<128, 6>(map_k, map_v, p, n_work, s) : launch_dec<128, 3>(map_k, map_v, p, n_work, s);
+  return deep_ring ? launch_dec<64, 6>(map_k, map_v, p, n_work, s) : launch_dec<64, 3>(map_k, map_v, p, n_work, s);
 }

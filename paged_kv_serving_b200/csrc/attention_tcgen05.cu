@@ -389,22 +389,30 @@ struct PoolMapKey {
   CUtensorMap map;
 };
 
-// The tensor map of a key or value pool, kept per (pool, sizes, form); null when the driver
-// refuses to encode it.
-static const CUtensorMap* pool_map(const void* base, long long rows, int hd, int box_rows, int wide) {
+// The tensor map of a key or value pool, kept per (pool, sizes, form) and copied to the caller (a
+// later lookup may take a table entry's place); false when the driver refuses to encode it.
+static bool pool_map(const void* base, long long rows, int hd, int box_rows, int wide, CUtensorMap* out) {
   static PoolMapKey cache[512];
   static int used = 0;
   for (int i = 0; i < used; ++i)
     if (cache[i].base == base && cache[i].rows == rows && cache[i].hd == hd && cache[i].box == box_rows &&
-        cache[i].wide == wide)
-      return &cache[i].map;
-  PoolMapKey& slot = cache[used < 512 ? used : 511];
+        cache[i].wide == wide) {
+      *out = cache[i].map;
+      return true;
+    }
+  static int victim = 0;              // a full table gives up its entries in turn
+  PoolMapKey& slot = cache[used < 512 ? used : victim];
   const int rc = wide ? make_panel_group_map(&slot.map, base, rows, hd / 64, box_rows)
                       : make_tile_map(&slot.map, base, rows, hd, hd, box_rows);
-  if (rc) return nullptr;
+  if (rc) {
+    slot.base = nullptr;
+    return false;
+  }
   slot.base = base; slot.rows = rows; slot.hd = hd; slot.box = box_rows; slot.wide = wide;
   if (used < 512) ++used;
-  return &slot.map;
+  else victim = (victim + 1) % 512;
+  *out = slot.map;
+  return true;
 }
 
 template <int HD, int KT, bool WIDE>
@@ -454,14 +462,13 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   if (r) return r;
   // head size 128: a page in one copy (both 64-column panels) where the driver encodes that map
   int wide = hd == 128 && pool_rows % 8 == 0 && !g_narrow_boxes;
-  const CUtensorMap* map_k = pool_map(k_pool, pool_rows, hd, page_size, wide);
-  const CUtensorMap* map_v = pool_map(v_pool, pool_rows, hd, page_size, wide);
-  if (wide && (!map_k || !map_v)) {
+  alignas(64) CUtensorMap map_k, map_v;
+  bool mapped = pool_map(k_pool, pool_rows, hd, page_size, wide, &map_k) && pool_map(v_pool, pool_rows, hd, page_size, wide, &map_v);
+  if (wide && !mapped) {
     wide = 0;
-    map_k = pool_map(k_pool, pool_rows, hd, page_size, 0);
-    map_v = pool_map(v_pool, pool_rows, hd, page_size, 0);
+    mapped = pool_map(k_pool, pool_rows, hd, page_size, 0, &map_k) && pool_map(v_pool, pool_rows, hd, page_size, 0, &map_v);
   }
-  if (!map_k || !map_v) return PKV_ERR_SIZE;
+  if (!mapped) return PKV_ERR_SIZE;
   int shift = -1;
   for (int i = 0; i < 31; ++i)
     if ((1 << i) == page_size) shift = i;
@@ -470,13 +477,13 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   cudaStream_t s = (cudaStream_t)stream;
   // tiles of 64 keys (two blocks to an SM) wherever a page fits one
   if (page_size <= 64) {
-    if (hd == 128 && wide) return launch_fa<128, 64, true>(map_q, *map_k, *map_v, p, n_work, s);
-    if (hd == 128) return launch_fa<128, 64, false>(map_q, *map_k, *map_v, p, n_work, s);
-    return launch_fa<64, 64, false>(map_q, *map_k, *map_v, p, n_work, s);
+    if (hd == 128 && wide) return launch_fa<128, 64, true>(map_q, map_k, map_v, p, n_work, s);
+    if (hd == 128) return launch_fa<128, 64, false>(map_q, map_k, map_v, p, n_work, s);
+    return launch_fa<64, 64, false>(map_q, map_k, map_v, p, n_work, s);
   }
-  if (hd == 128 && wide) return launch_fa<128, 128, true>(map_q, *map_k, *map_v, p, n_work, s);
-  if (hd == 128) return launch_fa<128, 128, false>(map_q, *map_k, *map_v, p, n_work, s);
-  return launch_fa<64, 128, false>(map_q, *map_k, *map_v, p, n_work, s);
+  if (hd == 128 && wide) return launch_fa<128, 128, true>(map_q, map_k, map_v, p, n_work, s);
+  if (hd == 128) return launch_fa<128, 128, false>(map_q, map_k, map_v, p, n_work, s);
+  return launch_fa<64, 128, false>(map_q, map_k, map_v, p, n_work, s);
 }
 
 // For comparisons and tests: non-zero makes the kernel fetch one copy per page and panel even

@@ -375,16 +375,25 @@ struct WeightMapKey {
   CUtensorMap map;
 };
 
-static const CUtensorMap* weight_map(const void* base, long long rows, long long cols, int box_rows) {
+static bool weight_map(const void* base, long long rows, long long cols, int box_rows, CUtensorMap* out) {
   static WeightMapKey cache[1024];
   static int used = 0;
   for (int i = 0; i < used; ++i)
-    if (cache[i].base == base && cache[i].rows == rows && cache[i].cols == cols && cache[i].box == box_rows) return &cache[i].map;
-  WeightMapKey& slot = cache[used < 1024 ? used : 1023];
-  if (make_tile_map(&slot.map, base, rows, cols, cols, box_rows)) return nullptr;
+    if (cache[i].base == base && cache[i].rows == rows && cache[i].cols == cols && cache[i].box == box_rows) {
+      *out = cache[i].map;
+      return true;
+    }
+  static int victim = 0;              // a full table gives up its entries in turn
+  WeightMapKey& slot = cache[used < 1024 ? used : victim];
+  if (make_tile_map(&slot.map, base, rows, cols, cols, box_rows)) {
+    slot.base = nullptr;
+    return false;
+  }
   slot.base = base; slot.rows = rows; slot.cols = cols; slot.box = box_rows;
   if (used < 1024) ++used;
-  return &slot.map;
+  else victim = (victim + 1) % 1024;
+  *out = slot.map;
+  return true;
 }
 
 static int gs_sm_count() {
@@ -479,22 +488,22 @@ PKV_EXPORT int pkv_gemm_stream(const void* x, int ldx, const void* w, void* out,
   p.status = status;
   if (sumsq_in && (sumsq_parts <= 0 || width <= 0 || sumsq_in_stride < M)) return PKV_ERR_SIZE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const CUtensorMap* mw = weight_map(w, N, K, epilogue == GS_SILU ? 256 : 128);
-  if (!mw) return PKV_ERR_SIZE;
+  alignas(64) CUtensorMap mw;
+  if (!weight_map(w, N, K, epilogue == GS_SILU ? 256 : 128, &mw)) return PKV_ERR_SIZE;
   switch (epilogue) {
     case GS_BF16:
     case GS_F32:
       p.tiles = (N + 127) / 128; p.ld_out = N;
-      return epilogue == GS_BF16 ? dispatch_stream<GS_BF16>(*mw, x, ldx, p, chained, s)
-                                 : dispatch_stream<GS_F32>(*mw, x, ldx, p, chained, s);
+      return epilogue == GS_BF16 ? dispatch_stream<GS_BF16>(mw, x, ldx, p, chained, s)
+                                 : dispatch_stream<GS_F32>(mw, x, ldx, p, chained, s);
     case GS_SILU:
       if (n_out <= 0 || n_out > N / 2) return PKV_ERR_SIZE;
       p.tiles = N / 256; p.ld_out = n_out;
-      return dispatch_stream<GS_SILU>(*mw, x, ldx, p, chained, s);
+      return dispatch_stream<GS_SILU>(mw, x, ldx, p, chained, s);
     case GS_RESIDUAL:
       if (!hidden || !norm_weight || !sumsq_out || sumsq_out_stride < M) return PKV_ERR_SIZE;
       p.tiles = (N + 127) / 128; p.ld_out = N;
-      return dispatch_stream<GS_RESIDUAL>(*mw, x, ldx, p, chained, s);
+      return dispatch_stream<GS_RESIDUAL>(mw, x, ldx, p, chained, s);
     default: return PKV_ERR_SIZE;
   }
 }

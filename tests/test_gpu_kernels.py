@@ -463,6 +463,53 @@ def test_attention_kernels_at_a_long_context(kernel):
     assert np.abs(got - want).max() <= tol("bfloat16", 2)
 
 
+@pytest.mark.parametrize("kernel", ["tma", "flat", "tcgen05"])
+def test_more_pools_than_the_kernels_remember_tensor_maps_for(kernel):
+    """The TMA kernels keep the tensor maps of the pools they have seen (a few hundred). A process
+    that has used more pools than that (many engines, one after the other) must still read keys
+    from the key pool and values from the value pool: 700 pairs of small pools, one launch each,
+    every answer checked."""
+    from paged_kv_serving_b200 import ops
+
+    heads, kv, hd, page = 2, 1, 64, 16
+    n_q = 32 if kernel == "tcgen05" else 1
+    context = 32
+    scale = 1.0 / math.sqrt(hd)
+    generator = torch.Generator(device="cuda").manual_seed(9)
+    table = dev(np.asarray([[1, 0]], dtype=np.int32))
+    starts, first = dev(np.asarray([0, n_q], dtype=np.int32)), dev(np.asarray([context - n_q], dtype=np.int32))
+    one = dev(np.asarray([0], dtype=np.int32))
+    units = dev(np.asarray([0, 1], dtype=np.int32))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    keep = []
+    worst = 0.0
+    for _ in range(700):
+        k_pool = torch.randn((2, kv, page, hd), device="cuda", generator=generator).to(torch.bfloat16)
+        v_pool = torch.randn((2, kv, page, hd), device="cuda", generator=generator).to(torch.bfloat16)
+        keep.append((k_pool, v_pool))                      # alive, so that every pool has an address of its own
+        qkv = torch.randn((n_q, (heads + 2 * kv) * hd), device="cuda", generator=generator).to(torch.bfloat16)
+        out = torch.zeros((n_q, heads * hd), dtype=torch.bfloat16, device="cuda")
+        if kernel == "tma":
+            ops.attention_decode_tma(qkv, out, k_pool, v_pool, table, starts, first, one, 1, heads, kv, hd, page, 0, scale, 1, status)
+        elif kernel == "flat":
+            ops.attention_decode_flat(qkv, out, k_pool, v_pool, table, starts, first, one, units, 1, heads, kv, hd, page, 0, scale,
+                                      1, status)
+        else:
+            ops.attention_prefill_tcgen05(qkv, out, k_pool, v_pool, table, starts, first, one, one, heads, kv, hd, page, 0, scale,
+                                          status)
+        keys = torch.cat([k_pool[1, 0], k_pool[0, 0]]).float()            # logical order: page 1, then page 0
+        values = torch.cat([v_pool[1, 0], v_pool[0, 0]]).float()
+        q = qkv[:, :heads * hd].float().view(n_q, heads, hd)
+        scores = torch.einsum("qhd,kd->qhk", q, keys) * scale
+        positions = torch.arange(context, device="cuda")
+        visible = positions[None, :] <= (context - n_q + torch.arange(n_q, device="cuda"))[:, None]
+        scores = scores.masked_fill(~visible[:, None, :], float("-inf"))
+        want = torch.einsum("qhk,kd->qhd", torch.softmax(scores, dim=-1), values).reshape(n_q, heads * hd)
+        worst = max(worst, float((out.float() - want).abs().max()))
+    assert int(status.item()) == 0
+    assert worst <= tol("bfloat16", 2), worst
+
+
 def test_attention_refuses_what_it_cannot_do():
     from paged_kv_serving_b200 import ops
 
