@@ -234,7 +234,7 @@ def test_engine_tokens_do_not_depend_on_scheduling(tmp_path):
 
 def test_engine_never_steps_empty_while_work_is_queued():
     rng = np.random.default_rng(0)
-    for trial in range(20):
+    for trial in range(150):
         config = make_config(num_blocks=int(rng.integers(10, 20)), max_batched_tokens=int(rng.integers(2, 24)),
                              max_running_seqs=int(rng.integers(1, 6)), max_prompt_tokens=30, max_new_tokens=10,
                              max_context_tokens=40, watermark=float(rng.choice([0.0, 0.1, 0.3])),
