@@ -339,6 +339,7 @@ class ModelRunner:
 
     GRAPH_BATCH_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     GRAPH_TABLE_STEP = 32     # block tables of a graph are this many pages wide, or a multiple
+    MAX_GRAPHS = 96           # captured graphs kept; the least recently replayed one goes first
 
     def _step_graph(self, batch: ExecutionBatch, feedback: dict[str, int] | None = None) -> StepResult:
         count = len(batch.entries)
@@ -363,6 +364,8 @@ class ModelRunner:
         self._last_graph_step = (batch, key)
         rows = rows[:count]
         entry = self._graphs.get(key)
+        if entry is not None:
+            self._graphs[key] = self._graphs.pop(key)          # most recently used last
         if entry is not None and entry["signature"] == ctx.arena.signature():
             ctx.arena.upload(self.model.device, into=entry["ints"], views=False)
             entry["graph"].replay()
@@ -404,8 +407,11 @@ class ModelRunner:
         main.wait_stream(self._capture_stream)
         launches = ops.launch_count() - before
         ops.LAUNCHES["count"] = before                     # a capture records launches, it runs none
+        self._graphs.pop(key, None)
         self._graphs[key] = {"graph": graph, "ints": ints, "logits": captured, "signature": ctx.arena.signature(),
                              "launches": launches}
+        while len(self._graphs) > self.MAX_GRAPHS:             # a long-lived server meets many (rows, width) classes
+            self._graphs.pop(next(iter(self._graphs)))
         return StepResult(logits[:count], rows, count, ctx.arena.bytes_uploaded)
 
     def prepare_next(self) -> None:

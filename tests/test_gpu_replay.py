@@ -254,6 +254,44 @@ def test_captured_decode_steps_equal_eager_ones(dtype):
     assert np.abs(outputs[0] - outputs[1]).max() <= (1e-5 if dtype == "float32" else helpers.bf16_atol(outputs[1]))
 
 
+def test_only_so_many_captured_graphs_are_kept():
+    """A runner keeps a bounded number of captured graphs and drops the one replayed longest ago;
+    a size class whose graph was dropped is captured again and gives the right logits."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    dtype = "bfloat16"
+    tensors = helpers.tensors_for("C", dtype)
+    model = helpers.build_model(helpers.TINY_C, tensors, dtype)
+    prompts = {name: helpers.random_tokens(helpers.TINY_C, 60, seed=170 + i) for i, name in enumerate("abcde")}
+    wants = {name: plain_model.forward(helpers.TINY_C, tensors, p) for name, p in prompts.items()}
+    session = ReplaySession(model, max_tokens=512, block_size=16)
+    session.runner.MAX_GRAPHS = 2
+    at = {}
+
+    def start(names):
+        session.step([{"id": n, "tokens": prompts[n][:20], "want": []} for n in names])
+        at.update({n: 20 for n in names})
+
+    def decode(names, steps, end=()):
+        for step in range(steps):
+            got = session.step([{"id": n, "tokens": [prompts[n][at[n]]], "want": [0]} for n in names],
+                               end=list(end) if step == steps - 1 else [])
+            helpers.assert_close(got, np.stack([wants[n][at[n]] for n in names]), dtype, f"{names} at {at[names[0]]}")
+            for n in names:
+                at[n] += 1
+            assert len(session.runner._graphs) <= 2
+
+    start("abc")
+    decode("abc", 3, end="c")          # three rows: the four-row class
+    decode("ab", 3, end="b")           # the two-row class
+    classes = set(session.runner._graphs)
+    decode("a", 3)                     # the one-row class: the four-row graph goes
+    assert len(session.runner._graphs) == 2 and set(session.runner._graphs) != classes
+    start("de")
+    decode("ade", 3)                   # three rows again: captured again, the two-row graph goes
+    session.runner.check_status()
+
+
 @pytest.mark.parametrize("use_graphs", [True, False])
 def test_even_shares_decode_attention_in_the_engine(monkeypatch, use_graphs):
     """Decode steps of config D in bfloat16 with the even-shares decode kernel forced: three
