@@ -254,6 +254,58 @@ def test_captured_decode_steps_equal_eager_ones(dtype):
     assert np.abs(outputs[0] - outputs[1]).max() <= (1e-5 if dtype == "float32" else helpers.bf16_atol(outputs[1]))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("B", "D"))
+def test_random_traces(name, dtype):
+    """Seeded random traces: up to four live requests of 2 to 300 tokens, each step a random subset
+    of them with portions of random size (half of them a single token), wanted places anywhere,
+    a pool that only just holds four requests, so pages pass from request to request."""
+    from paged_kv_serving_b200.engine.replay import ReplaySession
+
+    config = helpers.CONFIGS[name]
+    longest = min(300, config["max_seq_len"])
+    tensors = helpers.tensors_for(name, dtype)
+    model = helpers.build_model(config, tensors, dtype)
+    for seed in range(12):
+        rng = np.random.default_rng(10_000 + seed)
+        session = ReplaySession(model, max_tokens=4 * (-(-longest // 64) * 64), block_size=helpers.PAGE_SIZE[name])
+        todo = [helpers.random_tokens(config, int(rng.integers(2, longest + 1)), seed=int(rng.integers(0, 10 ** 6)))
+                for _ in range(int(rng.integers(3, 9)))]
+        wants, live, started, steps = {}, {}, 0, 0
+        while todo or live:
+            while todo and len(live) < 4 and (not live or rng.random() < 0.5):
+                tokens = todo.pop()
+                live[f"r{started}"] = [tokens, 0]
+                wants[f"r{started}"] = plain_model.forward(config, tensors, np.asarray(tokens))
+                started += 1
+            entries, expect, ended = [], [], []
+            for request, state in live.items():
+                if len(live) > 1 and rng.random() < 0.25:
+                    continue                                  # left out of this step
+                tokens, done = state
+                left = len(tokens) - done
+                size = 1 if rng.random() < 0.4 else int(rng.integers(1, 1 + min(left, 160)))
+                want = sorted({int(x) for x in rng.integers(0, size, size=int(rng.integers(0, 4)))})
+                if done + size == len(tokens) and size - 1 not in want:
+                    want.append(size - 1)
+                entries.append({"id": request, "tokens": tokens[done:done + size], "want": want})
+                expect += [wants[request][done + i] for i in want]
+                state[1] = done + size
+                if state[1] == len(tokens):
+                    ended.append(request)
+            if not entries:
+                continue
+            got = session.step(entries, end=ended)
+            for request in ended:
+                del live[request]
+            steps += 1
+            if expect:
+                helpers.assert_close(got, np.stack(expect), dtype, f"random trace {seed} of {name}, step {steps}: "
+                                     f"{[(e['id'], len(e['tokens']), e['want']) for e in entries]}")
+        session.check_invariants()
+        session.runner.check_status()
+
+
 def test_only_so_many_captured_graphs_are_kept():
     """A runner keeps a bounded number of captured graphs and drops the one replayed longest ago;
     a size class whose graph was dropped is captured again and gives the right logits."""
