@@ -510,6 +510,50 @@ def test_more_pools_than_the_kernels_remember_tensor_maps_for(kernel):
     assert worst <= tol("bfloat16", 2), worst
 
 
+@pytest.mark.parametrize("seed", range(3))
+def test_attention_kernels_on_random_shapes(seed):
+    """Seeded draws of head counts, groupings, head sizes, page sizes, windows, context lengths,
+    query counts and split counts (also more splits than key tiles): each goes to the kernel that
+    takes it (float32-arithmetic, mma.sync, or the TMA / tcgen05 pair, the even-shares decode
+    kernel for steps that hold decode entries only) and is compared with the plain attention."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(500 + seed)
+    ran = set()
+    for _ in range(25):
+        kv = int(rng.choice([1, 2, 3, 4, 8]))
+        group = int(rng.choice([1, 2, 3, 4, 8]))
+        heads = kv * group
+        kind = str(rng.choice(["generic", "mma", "tensor"]))
+        if kind == "generic":
+            hd, page, dtype = 2 * int(rng.integers(1, 65)), int(rng.integers(1, 40)), str(rng.choice(["float32", "bfloat16"]))
+        elif kind == "mma":
+            hd, page, dtype = 16 * int(rng.integers(1, 9)), int(rng.choice([1, 2, 3, 4, 5, 8, 16, 24, 32])), "bfloat16"
+        else:
+            hd, page, dtype = int(rng.choice([64, 128])), int(rng.choice([8, 16, 32, 64, 128])), "bfloat16"
+        window = None if rng.random() < 0.6 else int(rng.integers(1, 200))
+        contexts = [int(rng.integers(1, 260)) for _ in range(int(rng.integers(1, 5)))]
+        queries = [int(min(c, rng.choice([1, 1, 1, 2, 3, int(rng.integers(1, c + 1))]))) for c in contexts]
+        case = dict(heads=heads, kv=kv, hd=hd, page=page, window=window, contexts=contexts, queries=queries, dtype=dtype,
+                    spike=bool(rng.integers(0, 2)))
+        splits = int(rng.integers(1, 9))
+        if kind == "generic":
+            got, want = _attention_case(rng, **case)
+        elif kind == "mma":
+            got, want = _attention_case(rng, fast=True, splits=splits, **case)
+        else:
+            only_decode = all(q * group <= 16 for q in queries)
+            flat = int(rng.integers(1, 300)) if only_decode and rng.random() < 0.5 and \
+                ops.attention_decode_flat_supports(hd, page, (heads + 2 * kv) * hd) else None
+            got, want = _attention_case(rng, fast=True, tcgen05=True, splits=splits, deep_ring=bool(rng.integers(0, 2)),
+                                        flat_blocks=flat, **case)
+            kind = "even shares" if flat else kind
+        ran.add(kind)
+        assert np.isfinite(got).all(), case
+        assert np.abs(got - want).max() <= tol(dtype, 2), (case, splits)
+    assert {"generic", "mma", "tensor"} <= ran
+
+
 def test_attention_refuses_what_it_cannot_do():
     from paged_kv_serving_b200 import ops
 
