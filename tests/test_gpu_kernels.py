@@ -628,6 +628,75 @@ def test_gemm_tcgen05_silu_mul_epilogue(m, ff, k, pairs):
     assert np.abs(as_np(out) - want).max() <= 2 ** -8 * np.abs(want).max() + 1e-6
 
 
+def test_products_on_random_shapes():
+    """Seeded draws of row counts, widths and inner sizes for the three product kernels and their
+    fused activation epilogues, against float64 products of the same operands."""
+    from paged_kv_serving_b200 import ops
+
+    rng = np.random.default_rng(77)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ran = {"few rows": 0, "streamed": 0, "tcgen05": 0, "few rows + activation": 0, "streamed + activation": 0,
+           "tcgen05 + activation": 0}
+
+    def check(kind, out, want, bound, what):
+        ran[kind] += 1
+        assert float((out.double() - want).abs().max()) <= bound and int(status.item()) == 0, (kind, what)
+
+    def fused(ff, k):
+        blocks = -(-ff // 128)
+        gate = (torch.randn(ff, k, device="cuda") * 0.3).to(torch.bfloat16)
+        up = (torch.randn(ff, k, device="cuda") * 0.3).to(torch.bfloat16)
+        both = torch.zeros((blocks, 2, 128, k), dtype=torch.bfloat16, device="cuda")
+        for b in range(blocks):
+            rows = min(128, ff - 128 * b)
+            both[b, 0, :rows] = gate[128 * b:128 * b + rows]
+            both[b, 1, :rows] = up[128 * b:128 * b + rows]
+        return gate, up, both.view(-1, k)
+
+    def activation(a, gate, up):
+        g, u = (a.float() @ gate.float().t()).cpu().numpy(), (a.float() @ up.float().t()).cpu().numpy()
+        return torch.from_numpy(plain_model.silu(g) * u).cuda().double()
+
+    torch.manual_seed(77)
+    for _ in range(120):
+        m, k = int(rng.integers(1, 33)), 32 * int(rng.integers(1, 200))
+        n = int(rng.integers(1, 12000)) if rng.random() < 0.8 else int(rng.integers(9000, 40000))
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        b = torch.randn(n, k, device="cuda").to(torch.bfloat16)
+        want = a.double() @ b.double().t()
+        scale = float(want.abs().max()) + 1e-9
+        for epilogue in ("bf16", "f32"):
+            if ops.gemm_small_m_supports(a, b, epilogue):
+                out = ops.gemm_small_m(a, b, epilogue, chained=bool(rng.integers(0, 2)))
+                check("few rows", out, want, (1e-5 if epilogue == "f32" else 2 ** -8) * scale * max(1.0, (k / 2048) ** 0.5), (m, n, k))
+        if k % 64 == 0 and ops.gemm_stream_supports(a, b, "bf16"):
+            check("streamed", ops.gemm_stream(a, b, status, "bf16", chained=bool(rng.integers(0, 2))), want, 2 ** -8 * scale, (m, n, k))
+        m2, k2, n2 = int(rng.integers(1, 3000)), 8 * int(rng.integers(8, 300)), 8 * int(rng.integers(1, 800))
+        a2 = torch.randn(m2, k2, device="cuda").to(torch.bfloat16)
+        b2 = torch.randn(n2, k2, device="cuda").to(torch.bfloat16)
+        if ops.gemm_tcgen05_supports(a2, b2):
+            want2 = a2.double() @ b2.double().t()
+            for pairs in (True, False):
+                check("tcgen05", ops.gemm_tcgen05(a2, b2, status, "bf16", pairs=pairs), want2,
+                      2 ** -8 * (float(want2.abs().max()) + 1e-9), (m2, n2, k2, pairs))
+        ff, k3, m3 = int(rng.integers(1, 4000)), 64 * int(rng.integers(1, 40)), int(rng.integers(1, 33))
+        gate, up, w = fused(ff, k3)
+        a3 = torch.randn(m3, k3, device="cuda").to(torch.bfloat16)
+        want3 = activation(a3, gate, up)
+        bound3 = 2 ** -8 * float(want3.abs().max()) + 1e-6
+        if ops.gemm_small_m_supports(a3, w, "silu_mul"):
+            check("few rows + activation", ops.gemm_small_m(a3, w, "silu_mul", n_out=ff), want3, bound3, (m3, ff, k3))
+        if ops.gemm_stream_supports(a3, w, "silu_mul"):
+            check("streamed + activation", ops.gemm_stream(a3, w, status, "silu_mul", n_out=ff), want3, bound3, (m3, ff, k3))
+        if ff % 8 == 0:
+            a4 = torch.randn(int(rng.integers(128, 700)), k3, device="cuda").to(torch.bfloat16)
+            if ops.gemm_tcgen05_supports(a4, w):
+                want4 = activation(a4, gate, up)
+                check("tcgen05 + activation", ops.gemm_tcgen05(a4, w, status, "silu_mul", n_out=ff, pairs=bool(rng.integers(0, 2))),
+                      want4, 2 ** -8 * float(want4.abs().max()) + 1e-6, (a4.shape[0], ff, k3))
+    assert all(count > 0 for count in ran.values()), ran
+
+
 def test_gemm_tcgen05_refuses_unaligned_operands():
     from paged_kv_serving_b200 import ops
 
