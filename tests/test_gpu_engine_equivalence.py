@@ -159,3 +159,60 @@ def test_every_sampled_row_matches_the_plain_implementation(name, longest, scena
     assert totals["mixed_steps"] > 0, "portions must have run beside decoded tokens"
     if dtype == "bfloat16":
         assert totals["graph_steps"] > 0, "decode steps must have been replayed as graphs"
+
+
+@pytest.mark.parametrize("overlap", [True, False])
+def test_requests_aborted_between_steps_leave_the_others_right_and_the_pool_whole(overlap):
+    """Drawn scenarios on tiny D in bfloat16 in which requests are aborted at random moments (with
+    overlapped steps: while a step that holds their tokens is in flight). Every other request
+    finishes with all its tokens, every row sampled for it is the plain implementation's, the
+    books balance after every call and the pool is whole at the end."""
+    from dataclasses import replace
+
+    from paged_kv_serving_b200.engine.engine import Engine
+
+    name, dtype = "D", "bfloat16"
+    config = helpers.CONFIGS[name]
+    tensors = helpers.tensors_for(name, dtype)
+    model = helpers.build_model(config, tensors, dtype)
+    rng = np.random.default_rng(50_001)
+    aborts = 0
+    for scenario in range(16):
+        requests, engine_config = _draw_scenario(rng, config, helpers.PAGE_SIZE[name], 300, scenario)
+        engine = Engine(model, replace(engine_config, dtype=dtype), overlap=overlap)
+        recorder = Recorder(engine.runner)
+        engine.runner.step = recorder
+        for request in requests:
+            assert engine.submit(request).admitted
+        outputs, gone = {}, set()
+        for _ in range(20_000):
+            if not engine.has_work:
+                break
+            if rng.random() < 0.1:
+                victim = requests[int(rng.integers(0, len(requests)))].request_id
+                if victim not in gone and victim not in outputs:
+                    engine.abort(victim)
+                    gone.add(victim)
+                    aborts += 1
+                    engine.check_invariants()
+            step = engine.step()
+            engine.check_invariants()
+            outputs.update({o.request_id: o for o in step.finished})
+        assert not engine.has_work
+        engine.runner.check_status()
+        final = {}
+        for request in requests:
+            if request.request_id in gone:
+                continue
+            assert request.request_id in outputs, "a request that was not aborted must finish"
+            for sample in outputs[request.request_id].samples:
+                assert len(sample.token_ids) == request.sampling.max_new_tokens
+                final[f"{request.request_id}#{sample.sample_index}"] = list(request.prompt_token_ids) + list(sample.token_ids)
+        plain = {seq_id: plain_model.forward(config, tensors, tokens[:-1]) for seq_id, tokens in final.items()}
+        for seq_id, context_len, row in recorder.records:
+            if seq_id in plain:
+                helpers.assert_close(row[None], plain[seq_id][context_len - 1][None], dtype, f"scenario {scenario}: {seq_id} at {context_len}")
+        engine.flush_prefix_cache()
+        engine.check_invariants()
+        assert engine.cache.num_free_blocks == engine_config.num_blocks, "the pool is whole after the flush"
+    assert aborts >= 5, "the scenarios must abort requests"
